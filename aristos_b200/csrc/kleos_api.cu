@@ -1,0 +1,626 @@
+// Host layer and C ABI of the B200-native MoE forward pass.
+//
+// Stands in for the reference's inline host API: kleos::initialize / finalize / getRank
+// (csrc/include/kleos/bootstrap.cuh:532-588) and moe::forwardHost / forwardHostBench
+// (csrc/include/kleos/moe/moe.cuh:146-205).  The reference allocates an NVSHMEM symmetric
+// heap plus flags (bootstrap.cuh:348-362) and eleven bookkeeping buffers (:365-397); here the
+// symmetric arena is an ordinary device allocation whose CUDA IPC handle is all-gathered once
+// over NCCL and mapped by every peer, after which all traffic is in-kernel stores and flags.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <dlfcn.h>
+#include <nccl.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "config.hpp"
+#include "gemm_simt.cuh"
+#include "gemm_tc.cuh"
+#include "route.cuh"
+#include "transport.cuh"
+
+namespace kleos {
+namespace {
+
+constexpr int kPhases = 8;  // route, slots, dispatch, plan, gemm1, gemm2, combine, total
+
+struct NcclApi {
+    void* handle = nullptr;
+    ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+    ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    const char* (*GetErrorString)(ncclResult_t) = nullptr;
+};
+
+struct State {
+    bool initialised = false;
+    int device = -1;
+    int sm_count = 0;
+    LayerConfig cfg;
+    int rank = 0, world = 1, nLx = 0;
+    uint32_t epoch = 0;
+    long long wait_cycles = 4000000000LL;  // about two seconds of SM clock
+    bool use_tc = false;
+
+    // symmetric arena
+    ArenaLayout lay{};
+    char* arena = nullptr;
+    PeerTable peers{};
+    bool peer_opened[kMaxWorld] = {};
+
+    // local bookkeeping
+    void* y1 = nullptr;
+    int *topk = nullptr, *slots = nullptr, *cell_tokens = nullptr, *refine_list = nullptr,
+        *refine_count = nullptr, *le_start = nullptr;
+    float *mcw = nullptr, *bias = nullptr;
+    unsigned *counts = nullptr, *done_dispatch = nullptr, *done_gemm2 = nullptr,
+             *cell_counts = nullptr;
+    PanelEntry* panels = nullptr;
+    DeviceStatus* status = nullptr;
+
+    // tensor maps (rebuilt when the caller's weight pointer changes)
+    const void* maps_for_iP = nullptr;
+    CUtensorMap map_x{}, map_w1{}, map_y1{}, map_w2{};
+
+    ncclComm_t comm = nullptr;
+    cudaEvent_t ev[kPhases + 1] = {};
+    float phase_ms[kPhases] = {};
+    std::string last_error;
+};
+
+State g;
+NcclApi nccl;
+int g_device_request = -1;
+
+int fail(int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    g.last_error = buf;
+    std::fprintf(stderr, "[kleos_b200] %s\n", buf);
+    return code;
+}
+
+#define KLEOS_CUDA(expr)                                                                  \
+    do {                                                                                  \
+        cudaError_t err__ = (expr);                                                       \
+        if (err__ != cudaSuccess)                                                         \
+            return fail(KLEOS_E_CUDA, "%s failed: %s (%s:%d)", #expr,                     \
+                        cudaGetErrorString(err__), __FILE__, __LINE__);                   \
+    } while (0)
+
+#define KLEOS_NCCL(expr)                                                                  \
+    do {                                                                                  \
+        ncclResult_t r__ = (expr);                                                        \
+        if (r__ != ncclSuccess)                                                           \
+            return fail(KLEOS_E_BOOTSTRAP, "%s failed: %s", #expr,                        \
+                        nccl.GetErrorString ? nccl.GetErrorString(r__) : "nccl error");   \
+    } while (0)
+
+int load_nccl() {
+    if (nccl.handle) return KLEOS_OK;
+    const char* names[] = {"libnccl.so.2", "libnccl.so"};
+    for (const char* n : names) {
+        nccl.handle = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+        if (nccl.handle) break;
+    }
+    if (!nccl.handle) return fail(KLEOS_E_BOOTSTRAP, "cannot load libnccl: %s", dlerror());
+    auto sym = [&](const char* s) { return dlsym(nccl.handle, s); };
+    nccl.GetUniqueId = reinterpret_cast<decltype(nccl.GetUniqueId)>(sym("ncclGetUniqueId"));
+    nccl.CommInitRank = reinterpret_cast<decltype(nccl.CommInitRank)>(sym("ncclCommInitRank"));
+    nccl.AllGather = reinterpret_cast<decltype(nccl.AllGather)>(sym("ncclAllGather"));
+    nccl.CommDestroy = reinterpret_cast<decltype(nccl.CommDestroy)>(sym("ncclCommDestroy"));
+    nccl.GetErrorString = reinterpret_cast<decltype(nccl.GetErrorString)>(sym("ncclGetErrorString"));
+    if (!nccl.GetUniqueId || !nccl.CommInitRank || !nccl.AllGather || !nccl.CommDestroy)
+        return fail(KLEOS_E_BOOTSTRAP, "libnccl lacks a required symbol");
+    return KLEOS_OK;
+}
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+template <typename T>
+int dev_alloc(T** p, size_t count) {
+    KLEOS_CUDA(cudaMalloc(reinterpret_cast<void**>(p), count * sizeof(T)));
+    KLEOS_CUDA(cudaMemset(*p, 0, count * sizeof(T)));
+    return KLEOS_OK;
+}
+
+// All-gather `bytes` bytes per rank through a temporary device buffer.
+int all_gather_bytes(const void* mine, void* all, size_t bytes) {
+    char* d = nullptr;
+    KLEOS_CUDA(cudaMalloc(&d, bytes * (g.world + 1)));
+    KLEOS_CUDA(cudaMemcpy(d, mine, bytes, cudaMemcpyHostToDevice));
+    KLEOS_NCCL(nccl.AllGather(d, d + bytes, bytes, ncclChar, g.comm, cudaStreamPerThread));
+    KLEOS_CUDA(cudaStreamSynchronize(cudaStreamPerThread));
+    KLEOS_CUDA(cudaMemcpy(all, d + bytes, bytes * g.world, cudaMemcpyDeviceToHost));
+    KLEOS_CUDA(cudaFree(d));
+    return KLEOS_OK;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+// bf16 matrix [rows][cols] with cols contiguous; box = 64 columns x box_rows rows, 128-byte
+// swizzle (64 bf16 = 128 bytes, the swizzle span).
+int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    if (!g_encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        KLEOS_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+        if (!fn || q != cudaDriverEntryPointSuccess)
+            return fail(KLEOS_E_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+        g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * 2};
+    const cuuint32_t box[2] = {64, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base),
+                                dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(KLEOS_E_CUDA, "cuTensorMapEncodeTiled failed: %d", (int)r);
+    return KLEOS_OK;
+}
+
+struct Sections {
+    const char *A, *Wg, *W1, *W2, *b1, *b2;
+    char *probs, *out;
+};
+
+Sections slice(const void* iP, void* oP) {
+    const LayerConfig& c = g.cfg;
+    const size_t eb = c.elem_bytes;
+    Sections s;
+    s.A = static_cast<const char*>(iP);
+    s.Wg = s.A + (size_t)c.S * c.H * eb;
+    s.W1 = s.Wg + (size_t)c.PX * c.H * eb;
+    s.W2 = s.W1 + (size_t)g.nLx * c.I * c.H * eb;
+    s.b1 = s.W2 + (size_t)g.nLx * c.H * c.I * eb;
+    s.b2 = s.b1 + (size_t)g.nLx * c.I * eb;
+    s.probs = static_cast<char*>(oP);
+    s.out = s.probs + (size_t)c.S * c.PX * eb;
+    return s;
+}
+
+int ensure_maps(const Sections& s) {
+    if (!g.use_tc || g.maps_for_iP == s.A) return KLEOS_OK;
+    const LayerConfig& c = g.cfg;
+    const uint64_t cell_rows = (uint64_t)g.world * g.nLx * c.pEC;
+    int rc;
+    if ((rc = make_map(&g.map_x, g.arena + g.lay.xcell, cell_rows, c.H, tc::BM))) return rc;
+    if ((rc = make_map(&g.map_w1, s.W1, (uint64_t)g.nLx * c.I, c.H, tc::BN))) return rc;
+    if ((rc = make_map(&g.map_y1, g.y1, cell_rows, c.I, tc::BM))) return rc;
+    if ((rc = make_map(&g.map_w2, s.W2, (uint64_t)g.nLx * c.H, c.I, tc::BN))) return rc;
+    g.maps_for_iP = s.A;
+    return KLEOS_OK;
+}
+
+template <typename T>
+int launch_route(const RouteArgs& ra, cudaStream_t st) {
+    const int grid = (ra.S + 63) / 64;
+    if (ra.PX == 64) {
+        route_kernel<T, 64><<<grid, 256, route_smem_bytes<64>(), st>>>(ra);
+    } else if (ra.PX == 128) {
+        route_kernel<T, 128><<<grid, 256, route_smem_bytes<128>(), st>>>(ra);
+    } else if (ra.PX == 256) {
+        static bool attr_set = false;
+        if (!attr_set) {
+            KLEOS_CUDA(cudaFuncSetAttribute(route_kernel<T, 256>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            (int)route_smem_bytes<256>()));
+            attr_set = true;
+        }
+        route_kernel<T, 256><<<grid, 256, route_smem_bytes<256>(), st>>>(ra);
+    } else {
+        return fail(KLEOS_E_UNSUPPORTED, "more than 256 experts are not supported by the router");
+    }
+    refine_kernel<T><<<64, 128, sizeof(double) * ra.E, st>>>(ra);
+    return KLEOS_OK;
+}
+
+template <typename T>
+int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed) {
+    const LayerConfig& c = g.cfg;
+    const Sections s = slice(iP, oP);
+    int rc = ensure_maps(s);
+    if (rc) return rc;
+    g.epoch += 1;
+    int evi = 0;
+    auto mark = [&]() -> cudaError_t { return timed ? cudaEventRecord(g.ev[evi++], st) : cudaSuccess; };
+    KLEOS_CUDA(mark());
+
+    // 1. router
+    KLEOS_CUDA(cudaMemsetAsync(g.refine_count, 0, sizeof(int), st));
+    RouteArgs ra{};
+    ra.A = s.A; ra.Wg = s.Wg; ra.bias = g.bias; ra.probs = s.probs; ra.topk = g.topk;
+    ra.mcw = g.mcw; ra.refine_list = g.refine_list; ra.refine_count = g.refine_count;
+    ra.S = c.S; ra.H = c.H; ra.E = c.E; ra.K = c.K; ra.PX = c.PX; ra.tie_eps = 1e-4f;
+    if ((rc = launch_route<T>(ra, st))) return rc;
+    KLEOS_CUDA(mark());
+
+    // 2. slots
+    SlotArgs sa{g.topk, g.slots, g.cell_tokens, g.counts, c.S, c.K, c.E, c.EC, c.pEC};
+    slot_kernel<<<c.E, 256, 0, st>>>(sa);
+    KLEOS_CUDA(mark());
+
+    // 3. dispatch
+    DispatchArgs da{};
+    da.A = s.A; da.cell_tokens = g.cell_tokens; da.counts = g.counts; da.peers = g.peers;
+    da.lay = g.lay; da.done_counter = g.done_dispatch; da.H = c.H; da.E = c.E; da.EC = c.EC;
+    da.pEC = c.pEC; da.nLx = g.nLx; da.rank = g.rank; da.world = g.world; da.epoch = g.epoch;
+    da.elem_bytes = c.elem_bytes;
+    dispatch_kernel<<<g.sm_count * 4, 256, 0, st>>>(da);
+    KLEOS_CUDA(mark());
+
+    // 4. plan: wait for every source's counts, list the panels
+    PlanArgs pa{};
+    pa.arena = g.arena; pa.lay = g.lay; pa.panels = g.panels; pa.le_start = g.le_start;
+    pa.cell_counts = g.cell_counts; pa.status = g.status; pa.world = g.world; pa.nLx = g.nLx;
+    pa.pEC = c.pEC; pa.epoch = g.epoch; pa.wait_cycles = g.wait_cycles;
+    plan_kernel<<<1, 1024, 0, st>>>(pa);
+    KLEOS_CUDA(mark());
+
+    // 5./6. expert FFN
+    GemmArgs ga{};
+    ga.panels = g.panels; ga.le_start = g.le_start; ga.y1 = g.y1; ga.peers = g.peers;
+    ga.lay = g.lay; ga.status = g.status; ga.wait_cycles = g.wait_cycles;
+    ga.hidden_act = c.hidden_act; ga.nLx = g.nLx; ga.pEC = c.pEC; ga.rank = g.rank;
+    ga.elem_bytes = c.elem_bytes; ga.epoch = g.epoch;
+    ga.ret.peers = g.peers; ga.ret.lay = g.lay; ga.ret.done_counter = g.done_gemm2;
+    ga.ret.rank = g.rank; ga.ret.world = g.world; ga.ret.epoch = g.epoch;
+
+    GemmArgs g1 = ga;
+    g1.A = g.arena + g.lay.xcell; g1.B = s.W1; g1.bias = s.b1; g1.N = c.I; g1.Kd = c.H; g1.mode = 0;
+    GemmArgs g2 = ga;
+    g2.A = g.y1; g2.B = s.W2; g2.bias = s.b2; g2.N = c.H; g2.Kd = c.I; g2.mode = 1;
+    if (g.use_tc) {
+        if constexpr (sizeof(T) == 2) {
+            ffn_gemm_tc<<<g.sm_count, 256, tc::SMEM_BYTES, st>>>(g.map_x, g.map_w1, g1);
+            KLEOS_CUDA(mark());
+            ffn_gemm_tc<<<g.sm_count, 256, tc::SMEM_BYTES, st>>>(g.map_y1, g.map_w2, g2);
+            KLEOS_CUDA(mark());
+        }
+    } else {
+        ffn_gemm_simt<T><<<g.sm_count * 2, 256, 0, st>>>(g1);
+        KLEOS_CUDA(mark());
+        ffn_gemm_simt<T><<<g.sm_count * 2, 256, 0, st>>>(g2);
+        KLEOS_CUDA(mark());
+    }
+
+    // 7. combine
+    CombineArgs ca{};
+    ca.arena = g.arena; ca.lay = g.lay; ca.probs = s.probs; ca.topk = g.topk; ca.slots = g.slots;
+    ca.mcw = g.mcw; ca.out = s.out; ca.status = g.status; ca.S = c.S; ca.H = c.H; ca.K = c.K;
+    ca.PX = c.PX; ca.pEC = c.pEC; ca.world = g.world; ca.epoch = g.epoch;
+    ca.wait_cycles = g.wait_cycles;
+    combine_kernel<T><<<g.sm_count * 4, 256, 0, st>>>(ca);
+    KLEOS_CUDA(mark());
+    KLEOS_CUDA(cudaGetLastError());
+    return KLEOS_OK;
+}
+
+int forward_any(const void* iP, void* oP, cudaStream_t st, bool timed) {
+    if (!g.initialised) return fail(KLEOS_E_STATE, "kleos_forward before kleos_initialize");
+    if (!iP || !oP) return fail(KLEOS_E_ARG, "null buffer");
+    if (g.cfg.torch_dtype == 0) return forward_typed<float>(iP, oP, st, timed);
+    return forward_typed<__nv_bfloat16>(iP, oP, st, timed);
+}
+
+void release_all() {
+    for (int r = 0; r < g.world; ++r)
+        if (g.peer_opened[r]) cudaIpcCloseMemHandle(g.peers.arena[r]);
+    cudaFree(g.arena);
+    cudaFree(g.y1); cudaFree(g.topk); cudaFree(g.slots); cudaFree(g.cell_tokens);
+    cudaFree(g.refine_list); cudaFree(g.refine_count); cudaFree(g.le_start); cudaFree(g.mcw);
+    cudaFree(g.bias); cudaFree(g.counts); cudaFree(g.done_dispatch); cudaFree(g.done_gemm2);
+    cudaFree(g.cell_counts); cudaFree(g.panels); cudaFree(g.status);
+    for (auto& e : g.ev)
+        if (e) cudaEventDestroy(e);
+    if (g.comm && nccl.CommDestroy) nccl.CommDestroy(g.comm);
+    g = State();
+}
+
+}  // namespace
+}  // namespace kleos
+
+using namespace kleos;
+
+extern "C" {
+
+const char* kleos_error_string(int code) {
+    switch (code) {
+        case KLEOS_OK: return "ok";
+        case KLEOS_E_CONFIG: return "invalid configuration";
+        case KLEOS_E_STATE: return "wrong call order";
+        case KLEOS_E_CUDA: return "CUDA call failed";
+        case KLEOS_E_BOOTSTRAP: return "bootstrap failed";
+        case KLEOS_E_MISMATCH: return "ranks disagree on the configuration";
+        case KLEOS_E_DEVICE: return "device reported a timeout or bounds error";
+        case KLEOS_E_UNSUPPORTED: return "unsupported dtype or shape";
+        case KLEOS_E_ARG: return "bad argument";
+        default: return "unknown";
+    }
+}
+
+int kleos_get_unique_id(void* out_id128) {
+    if (!out_id128) return fail(KLEOS_E_ARG, "null id buffer");
+    int rc = load_nccl();
+    if (rc) return rc;
+    static_assert(sizeof(ncclUniqueId) == 128, "NCCL unique id is 128 bytes");
+    ncclUniqueId id;
+    KLEOS_NCCL(nccl.GetUniqueId(&id));
+    std::memcpy(out_id128, &id, sizeof(id));
+    return KLEOS_OK;
+}
+
+int kleos_config_probe(const char* config_json_path, int world, kleos_layer_info* out) {
+    if (!config_json_path || !out) return fail(KLEOS_E_ARG, "null argument");
+    LayerConfig c;
+    const std::string err = load_config(config_json_path, &c);
+    if (!err.empty()) return fail(KLEOS_E_CONFIG, "%s: %s", config_json_path, err.c_str());
+    if (world < 1 || world > kMaxWorld || c.E % world)
+        return fail(KLEOS_E_CONFIG, "num_experts %d does not divide over %d ranks", c.E, world);
+    const int nlx = c.E / world;
+    out->rank = 0; out->world = world; out->local_experts = nlx;
+    out->S = c.S; out->H = c.H; out->I = c.I; out->E = c.E; out->K = c.K; out->EC = c.EC;
+    out->pEC = c.pEC; out->PX = c.PX; out->torch_dtype = c.torch_dtype;
+    out->hidden_act = c.hidden_act; out->elem_bytes = c.elem_bytes;
+    out->input_elems = (int64_t)c.S * c.H + (int64_t)c.PX * c.H + 2LL * nlx * c.I * c.H +
+                       (int64_t)nlx * (c.I + c.H);
+    out->output_elems = (int64_t)c.S * c.PX + (int64_t)c.S * c.H;
+    return KLEOS_OK;
+}
+
+int kleos_set_device(int device) {
+    if (g.initialised) return fail(KLEOS_E_STATE, "kleos_set_device after kleos_initialize");
+    g_device_request = device;
+    return KLEOS_OK;
+}
+
+int kleos_initialize(const char* config_json_path, int rank, int world, const void* nccl_id) {
+    if (g.initialised) return fail(KLEOS_E_STATE, "already initialised");
+    if (!config_json_path) return fail(KLEOS_E_ARG, "null config path");
+    if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world)
+        return fail(KLEOS_E_ARG, "rank %d / world %d out of range (max world %d)", rank, world, kMaxWorld);
+    LayerConfig cfg;
+    const std::string err = load_config(config_json_path, &cfg);
+    if (!err.empty()) return fail(KLEOS_E_CONFIG, "%s: %s", config_json_path, err.c_str());
+    if (cfg.E % world) return fail(KLEOS_E_CONFIG, "num_experts %d does not divide over %d ranks", cfg.E, world);
+    if (cfg.torch_dtype != 0 && cfg.torch_dtype != 2)
+        return fail(KLEOS_E_UNSUPPORTED, "torch_dtype %d: only 0 (float) and 2 (bf16) are implemented", cfg.torch_dtype);
+    if (cfg.K > kMaxTopK) return fail(KLEOS_E_UNSUPPORTED, "expert_top_k > %d", kMaxTopK);
+    if (cfg.E > 256) return fail(KLEOS_E_UNSUPPORTED, "num_experts > 256");
+    if (world > 1 && !nccl_id) return fail(KLEOS_E_ARG, "world > 1 needs an NCCL unique id");
+
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0)
+        return fail(KLEOS_E_CUDA, "no CUDA device: this library has no CPU path");
+    g.device = g_device_request >= 0 ? g_device_request : rank % ndev;
+    KLEOS_CUDA(cudaSetDevice(g.device));
+    cudaDeviceProp prop;
+    KLEOS_CUDA(cudaGetDeviceProperties(&prop, g.device));
+    if (prop.major != 10)
+        return fail(KLEOS_E_UNSUPPORTED, "device is sm_%d%d; this library is built for sm_100a only",
+                    prop.major, prop.minor);
+    g.sm_count = prop.multiProcessorCount;
+    g.cfg = cfg;
+    g.rank = rank;
+    g.world = world;
+    g.nLx = cfg.E / world;
+    g.epoch = 0;
+    if (const char* w = std::getenv("KLEOS_WAIT_MS")) {
+        // device wait budget in milliseconds (converted with the SM clock rate)
+        g.wait_cycles = (long long)(std::atof(w) * 1e-3 * prop.clockRate * 1e3);
+    }
+    const char* simt = std::getenv("KLEOS_DEBUG_SIMT_GEMM");
+    g.use_tc = (cfg.torch_dtype == 2) && !(simt && simt[0] == '1');
+
+    const size_t eb = cfg.elem_bytes;
+    const size_t cell_bytes = (size_t)cfg.E * cfg.pEC * cfg.H * eb;  // world*nLx == E
+    g.lay.xcell = 0;
+    g.lay.ycell = align_up(g.lay.xcell + cell_bytes, 1024);
+    g.lay.xflag = align_up(g.lay.ycell + cell_bytes, 1024);
+    g.lay.yflag = align_up(g.lay.xflag + (size_t)cfg.E * 8, 1024);
+    g.lay.bytes = align_up(g.lay.yflag + (size_t)kMaxWorld * 8, 1024);
+
+    int rc;
+    if ((rc = dev_alloc(&g.arena, g.lay.bytes))) return rc;
+    char* y1 = nullptr;
+    if ((rc = dev_alloc(&y1, (size_t)cfg.E * cfg.pEC * cfg.I * eb))) return rc;
+    g.y1 = y1;
+    if ((rc = dev_alloc(&g.topk, (size_t)cfg.S * cfg.K))) return rc;
+    if ((rc = dev_alloc(&g.slots, (size_t)cfg.S * cfg.K))) return rc;
+    if ((rc = dev_alloc(&g.cell_tokens, (size_t)cfg.E * cfg.pEC))) return rc;
+    if ((rc = dev_alloc(&g.refine_list, (size_t)cfg.S))) return rc;
+    if ((rc = dev_alloc(&g.refine_count, 1))) return rc;
+    if ((rc = dev_alloc(&g.le_start, (size_t)g.nLx + 1))) return rc;
+    if ((rc = dev_alloc(&g.mcw, (size_t)cfg.S))) return rc;
+    if ((rc = dev_alloc(&g.bias, (size_t)cfg.E))) return rc;
+    if ((rc = dev_alloc(&g.counts, (size_t)cfg.E))) return rc;
+    if ((rc = dev_alloc(&g.done_dispatch, 1))) return rc;
+    if ((rc = dev_alloc(&g.done_gemm2, 1))) return rc;
+    if ((rc = dev_alloc(&g.cell_counts, (size_t)cfg.E))) return rc;
+    if ((rc = dev_alloc(&g.panels, (size_t)cfg.E * cfg.pEC / kTileM))) return rc;
+    if ((rc = dev_alloc(&g.status, 1))) return rc;
+    for (auto& e : g.ev) KLEOS_CUDA(cudaEventCreate(&e));
+
+    if (g.use_tc)
+        KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        tc::SMEM_BYTES));
+
+    for (int r = 0; r < kMaxWorld; ++r) g.peers.arena[r] = nullptr;
+    g.peers.arena[rank] = g.arena;
+    if (world > 1) {
+        if ((rc = load_nccl())) return rc;
+        ncclUniqueId id;
+        std::memcpy(&id, nccl_id, sizeof(id));
+        KLEOS_NCCL(nccl.CommInitRank(&g.comm, world, id, rank));
+        // every rank must have read the same layer
+        struct Hello {
+            int v[12];
+            cudaIpcMemHandle_t h;
+        } mine{}, all[kMaxWorld];
+        const int fields[12] = {cfg.S, cfg.H, cfg.I, cfg.E, cfg.K, cfg.EC, cfg.pEC, cfg.PX,
+                                cfg.torch_dtype, cfg.hidden_act, world, (int)(g.lay.bytes >> 10)};
+        std::memcpy(mine.v, fields, sizeof(fields));
+        KLEOS_CUDA(cudaIpcGetMemHandle(&mine.h, g.arena));
+        if ((rc = all_gather_bytes(&mine, all, sizeof(Hello)))) return rc;
+        for (int r = 0; r < world; ++r)
+            if (std::memcmp(all[r].v, mine.v, sizeof(mine.v)) != 0)
+                return fail(KLEOS_E_MISMATCH, "rank %d read a different layer configuration than rank %d", r, rank);
+        for (int r = 0; r < world; ++r) {
+            if (r == rank) continue;
+            void* p = nullptr;
+            const cudaError_t e = cudaIpcOpenMemHandle(&p, all[r].h, cudaIpcMemLazyEnablePeerAccess);
+            if (e != cudaSuccess)
+                return fail(KLEOS_E_BOOTSTRAP, "cannot map the cells of rank %d: %s", r, cudaGetErrorString(e));
+            g.peers.arena[r] = static_cast<char*>(p);
+            g.peer_opened[r] = true;
+        }
+        // second exchange doubles as a barrier: nobody stores into a peer before it is mapped
+        int token = rank, tokens[kMaxWorld];
+        if ((rc = all_gather_bytes(&token, tokens, sizeof(int)))) return rc;
+    }
+    KLEOS_CUDA(cudaDeviceSynchronize());
+    g.initialised = true;
+    return KLEOS_OK;
+}
+
+int kleos_set_gate_bias(const float* host_bias, int n) {
+    if (!g.initialised) return fail(KLEOS_E_STATE, "not initialised");
+    if (!host_bias) {
+        KLEOS_CUDA(cudaMemset(g.bias, 0, sizeof(float) * g.cfg.E));
+        return KLEOS_OK;
+    }
+    if (n != g.cfg.E) return fail(KLEOS_E_ARG, "gate bias needs %d values, got %d", g.cfg.E, n);
+    KLEOS_CUDA(cudaMemcpy(g.bias, host_bias, sizeof(float) * n, cudaMemcpyHostToDevice));
+    return KLEOS_OK;
+}
+
+int kleos_forward(const void* iP, void* oP, void* stream) {
+    cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : cudaStreamPerThread;
+    return forward_any(iP, oP, st, false);
+}
+
+int kleos_forward_bench(const void* iP, void* oP, int skip, int trials, float* ms) {
+    if (!ms || trials < 1 || skip < 0) return fail(KLEOS_E_ARG, "bad bench arguments");
+    cudaStream_t st = cudaStreamPerThread;
+    int rc;
+    for (int i = 0; i < skip; ++i)
+        if ((rc = forward_any(iP, oP, st, false))) return rc;
+    KLEOS_CUDA(cudaStreamSynchronize(st));
+    float acc[kPhases] = {};
+    // timed trials record per-phase events; the total is first event to last event
+    for (int i = 0; i < trials; ++i) {
+        if ((rc = forward_any(iP, oP, st, true))) return rc;
+        KLEOS_CUDA(cudaStreamSynchronize(st));
+        for (int p = 0; p < kPhases - 1; ++p) {
+            float v = 0;
+            KLEOS_CUDA(cudaEventElapsedTime(&v, g.ev[p], g.ev[p + 1]));
+            acc[p] += v;
+        }
+        float v = 0;
+        KLEOS_CUDA(cudaEventElapsedTime(&v, g.ev[0], g.ev[kPhases - 1]));
+        acc[kPhases - 1] += v;
+    }
+    for (int p = 0; p < kPhases; ++p) g.phase_ms[p] = acc[p] / trials;
+    // back-to-back launches between one pair of events, as the reference times it
+    cudaEvent_t a = g.ev[0], b = g.ev[kPhases];
+    KLEOS_CUDA(cudaEventRecord(a, st));
+    for (int i = 0; i < trials; ++i)
+        if ((rc = forward_any(iP, oP, st, false))) return rc;
+    KLEOS_CUDA(cudaEventRecord(b, st));
+    KLEOS_CUDA(cudaStreamSynchronize(st));
+    float total = 0;
+    KLEOS_CUDA(cudaEventElapsedTime(&total, a, b));
+    *ms = total / trials;
+    kleos_status s;
+    if ((rc = kleos_last_status(&s))) return rc;
+    if (s.code) return fail(KLEOS_E_DEVICE, "device status: where=%d detail=%d epoch=%d", s.where, s.detail, s.epoch);
+    return KLEOS_OK;
+}
+
+int kleos_forward_host(const void* host_activations, void* iP, void* oP, void* host_output) {
+    if (!g.initialised) return fail(KLEOS_E_STATE, "not initialised");
+    if (!host_activations || !iP || !oP || !host_output) return fail(KLEOS_E_ARG, "null buffer");
+    const LayerConfig& c = g.cfg;
+    cudaStream_t st = cudaStreamPerThread;
+    const size_t act_bytes = (size_t)c.S * c.H * c.elem_bytes;
+    KLEOS_CUDA(cudaMemcpyAsync(iP, host_activations, act_bytes, cudaMemcpyHostToDevice, st));
+    int rc = forward_any(iP, oP, st, false);
+    if (rc) return rc;
+    const char* out = static_cast<const char*>(oP) + (size_t)c.S * c.PX * c.elem_bytes;
+    KLEOS_CUDA(cudaMemcpyAsync(host_output, out, act_bytes, cudaMemcpyDeviceToHost, st));
+    KLEOS_CUDA(cudaStreamSynchronize(st));
+    return KLEOS_OK;
+}
+
+int kleos_get_rank(void) { return g.initialised ? g.rank : KLEOS_E_STATE; }
+int kleos_local_experts(void) { return g.initialised ? g.nLx : KLEOS_E_STATE; }
+
+int kleos_get_info(kleos_layer_info* out) {
+    if (!g.initialised) return fail(KLEOS_E_STATE, "not initialised");
+    if (!out) return fail(KLEOS_E_ARG, "null info");
+    const LayerConfig& c = g.cfg;
+    out->rank = g.rank; out->world = g.world; out->local_experts = g.nLx;
+    out->S = c.S; out->H = c.H; out->I = c.I; out->E = c.E; out->K = c.K; out->EC = c.EC;
+    out->pEC = c.pEC; out->PX = c.PX; out->torch_dtype = c.torch_dtype;
+    out->hidden_act = c.hidden_act; out->elem_bytes = c.elem_bytes;
+    out->input_elems = (int64_t)c.S * c.H + (int64_t)c.PX * c.H + 2LL * g.nLx * c.I * c.H +
+                       (int64_t)g.nLx * (c.I + c.H);
+    out->output_elems = (int64_t)c.S * c.PX + (int64_t)c.S * c.H;
+    return KLEOS_OK;
+}
+
+int kleos_last_status(kleos_status* out) {
+    if (!g.initialised) return fail(KLEOS_E_STATE, "not initialised");
+    if (!out) return fail(KLEOS_E_ARG, "null status");
+    KLEOS_CUDA(cudaStreamSynchronize(cudaStreamPerThread));
+    DeviceStatus d;
+    KLEOS_CUDA(cudaMemcpy(&d, g.status, sizeof(d), cudaMemcpyDeviceToHost));
+    out->code = d.code; out->where = d.where; out->detail = d.detail; out->epoch = d.epoch;
+    return KLEOS_OK;
+}
+
+int kleos_debug_routing(int32_t* topk, int32_t* slots, uint32_t* counts, float* mcw) {
+    if (!g.initialised) return fail(KLEOS_E_STATE, "not initialised");
+    const LayerConfig& c = g.cfg;
+    KLEOS_CUDA(cudaStreamSynchronize(cudaStreamPerThread));
+    const size_t sk = (size_t)c.S * c.K;
+    if (topk) KLEOS_CUDA(cudaMemcpy(topk, g.topk, sk * 4, cudaMemcpyDeviceToHost));
+    if (slots) KLEOS_CUDA(cudaMemcpy(slots, g.slots, sk * 4, cudaMemcpyDeviceToHost));
+    if (counts) KLEOS_CUDA(cudaMemcpy(counts, g.counts, (size_t)c.E * 4, cudaMemcpyDeviceToHost));
+    if (mcw) KLEOS_CUDA(cudaMemcpy(mcw, g.mcw, (size_t)c.S * 4, cudaMemcpyDeviceToHost));
+    return KLEOS_OK;
+}
+
+int kleos_phase_times(float* ms, int n) {
+    if (!ms || n < kPhases) return fail(KLEOS_E_ARG, "need room for %d floats", kPhases);
+    for (int p = 0; p < kPhases; ++p) ms[p] = g.phase_ms[p];
+    return KLEOS_OK;
+}
+
+int kleos_finalize(void) {
+    if (!g.initialised) return fail(KLEOS_E_STATE, "not initialised");
+    cudaDeviceSynchronize();
+    if (g.world > 1) {
+        // nobody unmaps while a peer may still be storing into its cells
+        int token = g.rank, tokens[kMaxWorld];
+        all_gather_bytes(&token, tokens, sizeof(int));
+    }
+    release_all();
+    return KLEOS_OK;
+}
+
+}  // extern "C"

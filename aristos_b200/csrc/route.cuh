@@ -1,0 +1,276 @@
+// Router: gate GEMM + softmax + top-k, near-tie refinement, slot assignment.
+//
+// Semantics follow the reference gate (moe/gate.cuh:470-720): logits = A * Wg^T with fp32
+// accumulation, softmax over the E real experts, k rounds of masked arg-max with ties to the
+// lowest expert id (:654-670), mCw = sum of the k winning probabilities (:669), slot per
+// (expert, token) kept iff slot < EC (:689-718).  Two deliberate differences: slots are
+// handed out in ascending token order (the reference uses atomicAdd arrival order,
+// :698-700), and tokens whose k-th / (k+1)-th logits are closer than fp32 summation error
+// are re-evaluated in fp64 so the selected set does not depend on accumulation order.
+#pragma once
+
+#include "common.cuh"
+
+namespace kleos {
+
+struct RouteArgs {
+    const void* A;        // [S,H] activations
+    const void* Wg;       // [PX,H] gate weight, row e = expert e
+    const float* bias;    // [E] logit bias (zeros when unused)
+    void* probs;          // [S,PX] gate probabilities (element type)
+    int* topk;            // [S,K]
+    float* mcw;           // [S]
+    int* refine_list;     // token ids needing fp64 re-evaluation
+    int* refine_count;
+    int S, H, E, K, PX;
+    float tie_eps;
+};
+
+// Softmax + top-k for one token from fp32 logits held in shared memory (stride ld).
+// Returns the margin between the k-th and (k+1)-th logit.
+__device__ __forceinline__ float select_topk_row(const float* l, int E, int K, int* sel,
+                                                  float* kth_val) {
+    float kth = 0.f;
+    for (int j = 0; j < K; ++j) {
+        int best = 0;
+        float bv = -INFINITY;
+        for (int e = 0; e < E; ++e) {
+            bool taken = false;
+            for (int q = 0; q < j; ++q) taken |= (sel[q] == e);
+            if (!taken && l[e] > bv) {
+                bv = l[e];
+                best = e;
+            }
+        }
+        sel[j] = best;
+        kth = bv;
+    }
+    float next = -INFINITY;
+    for (int e = 0; e < E; ++e) {
+        bool taken = false;
+        for (int q = 0; q < K; ++q) taken |= (sel[q] == e);
+        if (!taken && l[e] > next) next = l[e];
+    }
+    *kth_val = kth;
+    return kth - next;
+}
+
+// One block = 64 tokens x PXT experts, 256 threads, each thread a 4 x (PXT/16) register tile.
+template <typename T, int PXT>
+__global__ void __launch_bounds__(256) route_kernel(RouteArgs a) {
+    constexpr int BM = 64, BK = 32, TN = PXT / 16;
+    constexpr int LDA = BM + 1, LDB = PXT + 1, LDL = PXT + 1;
+    extern __shared__ float smem[];
+    float* As = smem;                  // [BK][LDA]
+    float* Bs = smem + BK * LDA;       // [BK][LDB]
+    float* Ls = smem;                  // [BM][LDL], reused after the K loop
+    float* rowmax = smem + BM * LDL;   // [BM]
+    float* rowden = rowmax + BM;       // [BM]
+
+    const T* A = static_cast<const T*>(a.A);
+    const T* Wg = static_cast<const T*>(a.Wg);
+    const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+    const int row0 = blockIdx.x * BM;
+    const int H = a.H;
+
+    float acc[4][TN];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
+
+    const int lrow = tid >> 2, lk = (tid & 3) * 8;
+    for (int k0 = 0; k0 < H; k0 += BK) {
+        {
+            const int gr = row0 + lrow;
+            float v[8];
+            if (gr < a.S) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = Elem<T>::to_f(A[(size_t)gr * H + k0 + lk + i]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = 0.f;
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) As[(lk + i) * LDA + lrow] = v[i];
+        }
+#pragma unroll
+        for (int it = 0; it < PXT / 64; ++it) {
+            const int br = lrow + it * 64;
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                Bs[(lk + i) * LDB + br] = Elem<T>::to_f(Wg[(size_t)br * H + k0 + lk + i]);
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int k = 0; k < BK; ++k) {
+            float av[4], bv[TN];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) av[i] = As[k * LDA + ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < TN; ++j) bv[j] = Bs[k * LDB + tx + 16 * j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+    // logits (+bias) into shared memory
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+            const int e = tx + 16 * j;
+            Ls[(ty * 4 + i) * LDL + e] = acc[i][j] + (e < a.E ? a.bias[e] : 0.f);
+        }
+    __syncthreads();
+
+    // one thread per token: softmax statistics, top-k, near-tie detection
+    if (tid < BM && row0 + tid < a.S) {
+        const float* l = Ls + tid * LDL;
+        float m = -INFINITY;
+        for (int e = 0; e < a.E; ++e) m = fmaxf(m, l[e]);
+        float d = 0.f;
+        for (int e = 0; e < a.E; ++e) d += __expf(l[e] - m);
+        rowmax[tid] = m;
+        rowden[tid] = d;
+        int sel[kMaxTopK];
+        float kth;
+        const float margin = select_topk_row(l, a.E, a.K, sel, &kth);
+        float w = 0.f;
+        for (int j = 0; j < a.K; ++j) {
+            a.topk[(size_t)(row0 + tid) * a.K + j] = sel[j];
+            w += __expf(l[sel[j]] - m) / d;
+        }
+        a.mcw[row0 + tid] = w;
+        if (a.K < a.E && margin < a.tie_eps * fmaxf(1.f, fabsf(kth))) {
+            const int pos = atomicAdd(a.refine_count, 1);
+            a.refine_list[pos] = row0 + tid;  // list has room for every token
+        }
+    }
+    __syncthreads();
+    // probabilities, coalesced, padding columns zero
+    T* probs = static_cast<T*>(a.probs);
+    for (int idx = tid; idx < BM * a.PX; idx += 256) {
+        const int r = idx / a.PX, e = idx - r * a.PX;
+        if (row0 + r >= a.S) break;
+        float p = 0.f;
+        if (e < a.E) p = __expf(Ls[r * LDL + e] - rowmax[r]) / rowden[r];
+        probs[(size_t)(row0 + r) * a.PX + e] = Elem<T>::from_f(p);
+    }
+}
+
+template <int PXT>
+constexpr size_t route_smem_bytes() {
+    constexpr int BM = 64, BK = 32;
+    constexpr size_t k_loop = sizeof(float) * (BK * (BM + 1) + BK * (PXT + 1));
+    constexpr size_t epi = sizeof(float) * (BM * (PXT + 1) + 2 * BM);
+    return k_loop > epi ? k_loop : epi;
+}
+
+// fp64 re-evaluation of the tokens on the refine list: one block per listed token.
+template <typename T>
+__global__ void __launch_bounds__(128) refine_kernel(RouteArgs a) {
+    extern __shared__ double l64[];  // [E]
+    const T* A = static_cast<const T*>(a.A);
+    const T* Wg = static_cast<const T*>(a.Wg);
+    const int n = *a.refine_count;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int i = blockIdx.x; i < n; i += gridDim.x) {
+        const int t = a.refine_list[i];
+        for (int e = warp; e < a.E; e += 4) {
+            double s = 0.0;
+            for (int h = lane; h < a.H; h += 32)
+                s += (double)Elem<T>::to_f(A[(size_t)t * a.H + h]) *
+                     (double)Elem<T>::to_f(Wg[(size_t)e * a.H + h]);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            if (lane == 0) l64[e] = s + (double)a.bias[e];
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int sel[kMaxTopK];
+            for (int j = 0; j < a.K; ++j) {
+                int best = 0;
+                double bv = -INFINITY;
+                for (int e = 0; e < a.E; ++e) {
+                    bool taken = false;
+                    for (int q = 0; q < j; ++q) taken |= (sel[q] == e);
+                    if (!taken && l64[e] > bv) {
+                        bv = l64[e];
+                        best = e;
+                    }
+                }
+                sel[j] = best;
+            }
+            float m = -INFINITY;
+            for (int e = 0; e < a.E; ++e) m = fmaxf(m, (float)l64[e]);
+            float d = 0.f;
+            for (int e = 0; e < a.E; ++e) d += __expf((float)l64[e] - m);
+            float w = 0.f;
+            for (int j = 0; j < a.K; ++j) {
+                a.topk[(size_t)t * a.K + j] = sel[j];
+                w += __expf((float)l64[sel[j]] - m) / d;
+            }
+            a.mcw[t] = w;
+            T* probs = static_cast<T*>(a.probs);
+            for (int e = 0; e < a.E; ++e)
+                probs[(size_t)t * a.PX + e] = Elem<T>::from_f(__expf((float)l64[e] - m) / d);
+        }
+        __syncthreads();
+    }
+}
+
+struct SlotArgs {
+    const int* topk;        // [S,K]
+    int* slots;             // [S,K] slot or kDropped
+    int* cell_tokens;       // [E,pEC] token id held by each slot
+    unsigned* counts;       // [E] unclamped
+    int S, K, E, EC, pEC;
+};
+
+// One block per expert; slots in ascending token order.
+__global__ void __launch_bounds__(256) slot_kernel(SlotArgs a) {
+    __shared__ int warp_sums[8];
+    __shared__ int base_s;
+    const int e = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int chunk = (a.S + 255) / 256;
+    const int t0 = tid * chunk, t1 = min(a.S, t0 + chunk);
+    int mine = 0;
+    for (int t = t0; t < t1; ++t)
+        for (int j = 0; j < a.K; ++j) mine += (a.topk[(size_t)t * a.K + j] == e);
+    int incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+    }
+    if (lane == 31) warp_sums[warp] = incl;
+    __syncthreads();
+    if (tid == 0) {
+        int run = 0;
+        for (int w = 0; w < 8; ++w) {
+            const int v = warp_sums[w];
+            warp_sums[w] = run;
+            run += v;
+        }
+        base_s = run;
+        a.counts[e] = (unsigned)run;
+    }
+    __syncthreads();
+    int pos = warp_sums[warp] + incl - mine;
+    for (int t = t0; t < t1; ++t)
+        for (int j = 0; j < a.K; ++j)
+            if (a.topk[(size_t)t * a.K + j] == e) {
+                if (pos < a.EC) {
+                    a.slots[(size_t)t * a.K + j] = pos;
+                    a.cell_tokens[(size_t)e * a.pEC + pos] = t;
+                } else {
+                    a.slots[(size_t)t * a.K + j] = kDropped;
+                }
+                ++pos;
+            }
+}
+
+}  // namespace kleos

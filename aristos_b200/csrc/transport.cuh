@@ -1,0 +1,262 @@
+// Token dispatch into the expert ranks' cells, the tile plan built from the arrived counts,
+// and the gate-weighted combine of the returned rows.
+//
+// Roles follow the reference: packet::dispatch (os/packet.cuh:35-286) copies the routed,
+// unscaled rows into cell [source rank][local expert] on the expert's rank and raises one
+// flag per (source, expert) carrying the routed count, also when the count is zero
+// (:240-259); the decoder turns arrived packets into 128-row tasks (:304-398); combine
+// (os/processor/processor.cuh:27-205) scales returned rows and accumulates them per token.
+// Here every peer is reached with plain 16-byte stores into its mapped cells over NVLink and
+// the combine is a deterministic gather-sum instead of element-wise atomics.
+#pragma once
+
+#include "common.cuh"
+
+namespace kleos {
+
+// Offsets of the regions inside each rank's symmetric arena (identical on every rank).
+struct ArenaLayout {
+    size_t xcell;  // [world*nLx][pEC][H] dispatched token rows, by (source rank, local expert)
+    size_t ycell;  // [E][pEC][H] returned FFN rows, by global expert
+    size_t xflag;  // [world*nLx] u64: (epoch<<32)|routed count
+    size_t yflag;  // [world] u64: (epoch<<32)|1 when that expert rank has returned everything
+    size_t bytes;
+};
+
+struct DispatchArgs {
+    const void* A;             // [S,H]
+    const int* cell_tokens;    // [E,pEC]
+    const unsigned* counts;    // [E]
+    PeerTable peers;
+    ArenaLayout lay;
+    unsigned* done_counter;    // zero between launches
+    int H, E, EC, pEC, nLx, rank, world;
+    uint32_t epoch;
+    int elem_bytes;
+};
+
+// Warp per routed row; rows are spread over the whole grid.
+__global__ void __launch_bounds__(256) dispatch_kernel(DispatchArgs a) {
+    __shared__ unsigned prefix[257];  // E <= 256
+    __shared__ bool last_block;
+    const int tid = threadIdx.x;
+    if (tid == 0) {
+        unsigned run = 0;
+        for (int e = 0; e < a.E; ++e) {
+            prefix[e] = run;
+            run += min(a.counts[e], (unsigned)a.EC);
+        }
+        prefix[a.E] = run;
+    }
+    __syncthreads();
+    const unsigned total = prefix[a.E];
+    const int lane = tid & 31;
+    const unsigned warps = gridDim.x * (blockDim.x >> 5);
+    const unsigned row_chunks = (unsigned)((size_t)a.H * a.elem_bytes / 16);
+    for (unsigned g = blockIdx.x * (blockDim.x >> 5) + (tid >> 5); g < total; g += warps) {
+        int lo = 0, hi = a.E;  // last e with prefix[e] <= g
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (prefix[mid] <= g) lo = mid; else hi = mid;
+        }
+        const int e = lo;
+        const unsigned slot = g - prefix[e];
+        const int owner = e / a.nLx, le = e - owner * a.nLx;
+        const int tok = a.cell_tokens[(size_t)e * a.pEC + slot];
+        const uint4* src = reinterpret_cast<const uint4*>(
+            static_cast<const char*>(a.A) + (size_t)tok * a.H * a.elem_bytes);
+        uint4* dst = reinterpret_cast<uint4*>(
+            a.peers.arena[owner] + a.lay.xcell +
+            (((size_t)a.rank * a.nLx + le) * a.pEC + slot) * a.H * a.elem_bytes);
+        for (unsigned c = lane; c < row_chunks; c += 32) dst[c] = __ldg(src + c);
+    }
+    // publish: every block fences its peer stores, the last block to finish raises the flags
+    __threadfence_system();
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned prev = atomicAdd(a.done_counter, 1u);
+        last_block = (prev == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (last_block) {
+        __threadfence_system();
+        for (int e = tid; e < a.E; e += blockDim.x) {
+            const int owner = e / a.nLx, le = e - owner * a.nLx;
+            unsigned long long* f = reinterpret_cast<unsigned long long*>(
+                a.peers.arena[owner] + a.lay.xflag) + ((size_t)a.rank * a.nLx + le);
+            st_release_sys(f, make_flag(a.epoch, min(a.counts[e], (unsigned)a.EC)));
+        }
+        if (tid == 0) *a.done_counter = 0u;
+    }
+}
+
+// One 128-row panel of one cell: what a GEMM m-tile works on.
+struct PanelEntry {
+    int row_base;  // first row in the xcell / y1cell row space
+    int rows;      // valid rows (1..128)
+    int le;        // local expert
+    int src;       // source rank
+};
+
+struct PlanArgs {
+    const char* arena;       // this rank's arena
+    ArenaLayout lay;
+    PanelEntry* panels;      // [world*nLx*pEC/128]
+    int* le_start;           // [nLx+1] panels of local expert le are [le_start[le], le_start[le+1])
+    unsigned* cell_counts;   // [world*nLx] routed count per (source, local expert)
+    DeviceStatus* status;
+    int world, nLx, pEC;
+    uint32_t epoch;
+    long long wait_cycles;
+};
+
+// Single block.  Waits (bounded) for the count flag of every (source, local expert) cell, then
+// lists the panels grouped by local expert so that tiles sharing a weight tile run together.
+__global__ void __launch_bounds__(1024) plan_kernel(PlanArgs a) {
+    __shared__ int failed;
+    const int cells = a.world * a.nLx;
+    if (threadIdx.x == 0) failed = 0;
+    __syncthreads();
+    const unsigned long long* flags =
+        reinterpret_cast<const unsigned long long*>(a.arena + a.lay.xflag);
+    for (int c = threadIdx.x; c < cells; c += blockDim.x) {
+        unsigned long long v = 0;
+        if (!wait_flag(flags + c, a.epoch, a.wait_cycles, &v)) {
+            report_error(a.status, KLEOS_AT_PLAN_WAIT, c, (int)a.epoch);
+            atomicExch(&failed, 1);
+            a.cell_counts[c] = 0;
+        } else {
+            a.cell_counts[c] = min((unsigned)(v & 0xffffffffu), (unsigned)a.pEC);
+        }
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int n = 0;
+        for (int le = 0; le < a.nLx; ++le) {
+            a.le_start[le] = n;
+            if (failed) continue;
+            for (int src = 0; src < a.world; ++src) {
+                const int c = src * a.nLx + le;
+                const int cnt = (int)a.cell_counts[c];
+                for (int r = 0; r < cnt; r += kTileM)
+                    a.panels[n++] = PanelEntry{c * a.pEC + r, min(kTileM, cnt - r), le, src};
+            }
+        }
+        a.le_start[a.nLx] = n;
+    }
+}
+
+struct CombineArgs {
+    const char* arena;   // this rank's arena (ycell, yflag)
+    ArenaLayout lay;
+    const void* probs;   // [S,PX] element-rounded gate probabilities
+    const int* topk;     // [S,K]
+    const int* slots;    // [S,K]
+    const float* mcw;    // [S]
+    void* out;           // [S,H]
+    DeviceStatus* status;
+    int S, H, K, PX, pEC, world;
+    uint32_t epoch;
+    long long wait_cycles;
+};
+
+// out[t] = sum_j Element(prob[t,e_j]) * Element(y2[e_j][slot_j] / mCw[t]) over kept choices
+// (reference processor.cuh:110-168); with k == 1 the row is copied unscaled (:170-204).
+// Rows of tokens whose every choice was dropped are written as zeros.  Warp per token.
+template <typename T>
+__global__ void __launch_bounds__(256) combine_kernel(CombineArgs a) {
+    __shared__ int failed;
+    if (threadIdx.x == 0) failed = 0;
+    __syncthreads();
+    if (threadIdx.x < a.world) {
+        const unsigned long long* f =
+            reinterpret_cast<const unsigned long long*>(a.arena + a.lay.yflag) + threadIdx.x;
+        unsigned long long v;
+        if (!wait_flag(f, a.epoch, a.wait_cycles, &v)) {
+            report_error(a.status, KLEOS_AT_COMBINE_WAIT, threadIdx.x, (int)a.epoch);
+            atomicExch(&failed, 1);
+        }
+    }
+    __syncthreads();
+    if (failed) return;
+
+    constexpr int VEC = 16 / sizeof(T);
+    const int lane = threadIdx.x & 31;
+    const int warps = gridDim.x * (blockDim.x >> 5);
+    const T* probs = static_cast<const T*>(a.probs);
+    const char* ycell = a.arena + a.lay.ycell;
+    const int chunks = a.H / VEC;
+    for (int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); t < a.S; t += warps) {
+        int e[kMaxTopK], sl[kMaxTopK];
+        float p[kMaxTopK];
+#pragma unroll
+        for (int j = 0; j < kMaxTopK; ++j)
+            if (j < a.K) {
+                e[j] = a.topk[(size_t)t * a.K + j];
+                sl[j] = a.slots[(size_t)t * a.K + j];
+                p[j] = Elem<T>::to_f(probs[(size_t)t * a.PX + e[j]]);
+            }
+        const float w = a.mcw[t];
+        T* orow = static_cast<T*>(a.out) + (size_t)t * a.H;
+        for (int c = lane; c < chunks; c += 32) {
+            float acc[VEC];
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
+#pragma unroll
+            for (int j = 0; j < kMaxTopK; ++j)
+                if (j < a.K && sl[j] != kDropped) {
+                    const T* yrow = reinterpret_cast<const T*>(ycell) +
+                                    ((size_t)e[j] * a.pEC + sl[j]) * a.H;
+                    const uint4 raw = ld_cg_v4(yrow + (size_t)c * VEC);
+                    const T* yv = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) {
+                        if (a.K > 1) {
+                            const float v = Elem<T>::round(Elem<T>::to_f(yv[i]) / w);
+                            const float s = Elem<T>::round(p[j] * v);
+                            acc[i] = Elem<T>::round(acc[i] + s);
+                        } else {
+                            acc[i] = Elem<T>::to_f(yv[i]);
+                        }
+                    }
+                }
+            uint4 o;
+            T* ov = reinterpret_cast<T*>(&o);
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) ov[i] = Elem<T>::from_f(acc[i]);
+            *reinterpret_cast<uint4*>(orow + (size_t)c * VEC) = o;
+        }
+    }
+}
+
+// Flag raised by the last GEMM2 block: tells every source rank that this expert rank has
+// stored all of its result rows.
+struct ReturnFlagArgs {
+    PeerTable peers;
+    ArenaLayout lay;
+    unsigned* done_counter;
+    int rank, world;
+    uint32_t epoch;
+};
+
+__device__ __forceinline__ void publish_return_flags(const ReturnFlagArgs& r, bool* smem_last) {
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned prev = atomicAdd(r.done_counter, 1u);
+        *smem_last = (prev == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (*smem_last) {
+        __threadfence_system();
+        if ((int)threadIdx.x < r.world) {
+            unsigned long long* f = reinterpret_cast<unsigned long long*>(
+                r.peers.arena[threadIdx.x] + r.lay.yflag) + r.rank;
+            st_release_sys(f, make_flag(r.epoch, 1u));
+        }
+        if (threadIdx.x == 0) *r.done_counter = 0u;
+    }
+}
+
+}  // namespace kleos

@@ -1,0 +1,203 @@
+"""Host-side mirror of the reference's API for the MoE forward path, on top of the C ABI.
+
+Function names and argument meaning follow the reference's host functions:
+``initialize`` / ``finalize`` / ``get_rank`` (csrc/include/kleos/bootstrap.cuh:532-588) and
+``moe::forwardHost`` / ``forwardHostBench`` (csrc/include/kleos/moe/moe.cuh:146-205).  The
+packed device buffers are the reference's (moe.cuh:92-98).  Errors raise ``KleosError``
+instead of terminating the process (reference: debug.cuh:19-43).
+
+There is no CPU path: loading fails loudly if ``libkleos_b200.so`` has not been built, and
+``initialize`` fails if no sm_100 GPU is present.
+"""
+from __future__ import annotations
+
+import ctypes
+import json
+import os
+import tempfile
+from dataclasses import asdict
+
+from .config import KleosConfig
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libkleos_b200.so")
+
+EXPORTS = (
+    "kleos_get_unique_id", "kleos_config_probe", "kleos_set_device", "kleos_initialize", "kleos_set_gate_bias",
+    "kleos_forward", "kleos_forward_bench", "kleos_forward_host", "kleos_get_rank",
+    "kleos_local_experts", "kleos_get_info", "kleos_last_status", "kleos_debug_routing",
+    "kleos_phase_times", "kleos_finalize", "kleos_error_string",
+)
+
+PHASE_NAMES = ("route", "slots", "dispatch", "plan", "gemm1", "gemm2", "combine", "total")
+
+
+class KleosError(RuntimeError):
+    def __init__(self, code: int, what: str):
+        super().__init__(f"{what}: {code}")
+        self.code = code
+
+
+class Status(ctypes.Structure):
+    _fields_ = [("code", ctypes.c_int32), ("where", ctypes.c_int32),
+                ("detail", ctypes.c_int32), ("epoch", ctypes.c_int32)]
+
+
+class LayerInfo(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int32) for n in
+                ("rank", "world", "local_experts", "S", "H", "I", "E", "K", "EC", "pEC", "PX",
+                 "torch_dtype", "hidden_act", "elem_bytes")] + \
+               [("input_elems", ctypes.c_int64), ("output_elems", ctypes.c_int64)]
+
+
+_lib = None
+
+
+def load_library() -> ctypes.CDLL:
+    """dlopen the in-tree CUDA library.  Raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise FileNotFoundError(
+                f"{LIB_PATH} is missing: build it with `python -m aristos_b200.build` "
+                "(this package has no CPU fallback)")
+        lib = ctypes.CDLL(LIB_PATH)
+        lib.kleos_error_string.restype = ctypes.c_char_p
+        lib.kleos_initialize.argtypes = [ctypes.c_char_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+        lib.kleos_forward.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+        lib.kleos_forward_bench.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int,
+                                            ctypes.c_int, ctypes.POINTER(ctypes.c_float)]
+        lib.kleos_forward_host.argtypes = [ctypes.c_void_p] * 4
+        lib.kleos_set_gate_bias.argtypes = [ctypes.c_void_p, ctypes.c_int]
+        lib.kleos_debug_routing.argtypes = [ctypes.c_void_p] * 4
+        lib.kleos_phase_times.argtypes = [ctypes.POINTER(ctypes.c_float), ctypes.c_int]
+        lib.kleos_get_unique_id.argtypes = [ctypes.c_void_p]
+        _lib = lib
+    return _lib
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != 0:
+        msg = load_library().kleos_error_string(rc).decode()
+        raise KleosError(rc, f"{what}: {msg}")
+
+
+def get_unique_id() -> bytes:
+    """128-byte bootstrap id created on rank 0 and handed to every rank's ``initialize``."""
+    buf = ctypes.create_string_buffer(128)
+    _check(load_library().kleos_get_unique_id(buf), "kleos_get_unique_id")
+    return buf.raw
+
+
+def set_device(device: int) -> None:
+    _check(load_library().kleos_set_device(device), "kleos_set_device")
+
+
+def initialize(config, rank: int = 0, world: int = 1, unique_id: bytes | None = None) -> LayerInfo:
+    """``config`` is a path to a kleos_config.json or a KleosConfig (written to a temp file,
+    since the C ABI reads the same JSON file the reference's build reads)."""
+    lib = load_library()
+    tmp = None
+    if isinstance(config, KleosConfig):
+        tmp = tempfile.NamedTemporaryFile("w", suffix=".json", delete=False)
+        json.dump(asdict(config), tmp)
+        tmp.close()
+        path = tmp.name
+    else:
+        path = str(config)
+    try:
+        idbuf = ctypes.create_string_buffer(unique_id, 128) if unique_id is not None else None
+        _check(lib.kleos_initialize(path.encode(), rank, world, idbuf), "kleos_initialize")
+    finally:
+        if tmp is not None:
+            os.unlink(tmp.name)
+    return get_info()
+
+
+def config_probe(path: str, world: int = 1) -> LayerInfo:
+    """Sizes the C++ host layer derives from a kleos_config.json; needs no GPU."""
+    info = LayerInfo()
+    _check(load_library().kleos_config_probe(str(path).encode(), world, ctypes.byref(info)),
+           "kleos_config_probe")
+    return info
+
+
+def get_info() -> LayerInfo:
+    info = LayerInfo()
+    _check(load_library().kleos_get_info(ctypes.byref(info)), "kleos_get_info")
+    return info
+
+
+def get_rank() -> int:
+    return load_library().kleos_get_rank()
+
+
+def local_experts() -> int:
+    return load_library().kleos_local_experts()
+
+
+def set_gate_bias(bias) -> None:
+    lib = load_library()
+    if bias is None:
+        _check(lib.kleos_set_gate_bias(None, 0), "kleos_set_gate_bias")
+        return
+    import numpy as np
+    b = np.ascontiguousarray(bias, dtype=np.float32)
+    _check(lib.kleos_set_gate_bias(b.ctypes.data, b.size), "kleos_set_gate_bias")
+
+
+def forward_host(iP, oP, stream=None) -> None:
+    """Asynchronous layer forward on packed DEVICE buffers (torch tensors or raw pointers)."""
+    _check(load_library().kleos_forward(_ptr(iP), _ptr(oP), stream), "kleos_forward")
+
+
+def forward_host_bench(iP, oP, skip: int = 32, trials: int = 32) -> float:
+    """Mean milliseconds per forward over ``trials`` launches after ``skip`` warm-ups."""
+    ms = ctypes.c_float(0)
+    _check(load_library().kleos_forward_bench(_ptr(iP), _ptr(oP), skip, trials, ctypes.byref(ms)),
+           "kleos_forward_bench")
+    return ms.value
+
+
+def forward_from_host(host_activations, iP, oP, host_output) -> None:
+    """End-to-end step with host buffers: H2D activations, forward, D2H layer output, sync."""
+    _check(load_library().kleos_forward_host(_ptr(host_activations), _ptr(iP), _ptr(oP),
+                                             _ptr(host_output)), "kleos_forward_host")
+
+
+def phase_times() -> dict:
+    arr = (ctypes.c_float * 8)()
+    _check(load_library().kleos_phase_times(arr, 8), "kleos_phase_times")
+    return dict(zip(PHASE_NAMES, [float(v) for v in arr]))
+
+
+def last_status() -> Status:
+    st = Status()
+    _check(load_library().kleos_last_status(ctypes.byref(st)), "kleos_last_status")
+    return st
+
+
+def debug_routing(info: LayerInfo) -> dict:
+    import numpy as np
+    topk = np.empty((info.S, info.K), dtype=np.int32)
+    slots = np.empty((info.S, info.K), dtype=np.int32)
+    counts = np.empty(info.E, dtype=np.uint32)
+    mcw = np.empty(info.S, dtype=np.float32)
+    _check(load_library().kleos_debug_routing(topk.ctypes.data, slots.ctypes.data,
+                                              counts.ctypes.data, mcw.ctypes.data),
+           "kleos_debug_routing")
+    return dict(topk=topk, slots=slots, counts=counts, mcw=mcw)
+
+
+def finalize() -> None:
+    _check(load_library().kleos_finalize(), "kleos_finalize")
+
+
+def _ptr(x):
+    if x is None or isinstance(x, int):
+        return x
+    if hasattr(x, "data_ptr"):
+        return x.data_ptr()
+    if hasattr(x, "ctypes"):
+        return x.ctypes.data
+    raise TypeError(type(x))

@@ -1,0 +1,131 @@
+/*
+ * kleos_b200 — C ABI of the B200-native distributed MoE layer forward pass.
+ *
+ * Every entry point below replaces one inline C++ host function of the reference project
+ * (namespace kleos); the reference file:line each one stands in for is cited beside it.
+ * All functions return 0 on success or a negative KLEOS_E_* code; none of them exits the
+ * process (the reference prints and calls exit()/quick_exit(), debug.cuh:19-43).
+ *
+ * Threading model is the reference's: one host thread per process, one process per GPU,
+ * global state, not re-entrant (types.cuh:440,1011-1013).
+ */
+#ifndef KLEOS_B200_H
+#define KLEOS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    KLEOS_OK = 0,
+    KLEOS_E_CONFIG = -1,      /* unreadable or invalid kleos_config.json            */
+    KLEOS_E_STATE = -2,       /* call order: not initialised / already initialised  */
+    KLEOS_E_CUDA = -3,        /* a CUDA runtime or driver call failed               */
+    KLEOS_E_BOOTSTRAP = -4,   /* NCCL bootstrap or peer mapping failed              */
+    KLEOS_E_MISMATCH = -5,    /* ranks disagree on the configuration                */
+    KLEOS_E_DEVICE = -6,      /* the device reported a timeout or a bounds error    */
+    KLEOS_E_UNSUPPORTED = -7, /* dtype / shape outside what the kernels implement   */
+    KLEOS_E_ARG = -8          /* null pointer or out-of-range argument              */
+};
+
+/* Where a device-side problem was detected (kleos_status.where). */
+enum {
+    KLEOS_AT_NONE = 0,
+    KLEOS_AT_PLAN_WAIT = 1,     /* waiting for dispatch flags from the source ranks */
+    KLEOS_AT_COMBINE_WAIT = 2,  /* waiting for result flags from the expert ranks   */
+    KLEOS_AT_GEMM_PRODUCER = 3, /* TMA producer waiting for a free pipeline stage   */
+    KLEOS_AT_GEMM_MMA = 4,      /* MMA issuer waiting for operands or accumulator   */
+    KLEOS_AT_GEMM_EPILOGUE = 5, /* epilogue waiting for an accumulator              */
+    KLEOS_AT_BOUNDS = 6         /* an index outside its table                       */
+};
+
+typedef struct kleos_status {
+    int32_t code;   /* 0, or KLEOS_E_DEVICE */
+    int32_t where;  /* KLEOS_AT_*           */
+    int32_t detail; /* rank / cell / tile the detector was looking at */
+    int32_t epoch;  /* forward-call counter when it happened */
+} kleos_status;
+
+typedef struct kleos_layer_info {
+    int32_t rank, world, local_experts;
+    int32_t S, H, I, E, K, EC, pEC, PX;
+    int32_t torch_dtype, hidden_act, elem_bytes;
+    int64_t input_elems;  /* elements in the packed input buffer  iP */
+    int64_t output_elems; /* elements in the packed output buffer oP */
+} kleos_layer_info;
+
+/* Bootstrap helper: rank 0 creates the 128-byte NCCL unique id that every rank passes to
+ * kleos_initialize.  The reference bootstraps through nvshmem_init() under an MPI/PMI
+ * launcher instead (bootstrap.cuh:295). */
+int kleos_get_unique_id(void* out_id128);
+
+/* Select the CUDA device before kleos_initialize (reference: setDevice(),
+ * bootstrap.cuh:549-553).  Default is rank % device count. */
+int kleos_set_device(int device);
+
+/* Read kleos_config.json (same keys as kleos_config.schema.json:5-89, parsed at run time
+ * instead of being baked in by CMake), allocate the symmetric cells, flags and bookkeeping,
+ * and map every peer's cells.  Replaces kleos::initialize() (bootstrap.cuh:532-547).
+ * nccl_id may be NULL when world == 1. */
+int kleos_initialize(const char* config_json_path, int rank, int world, const void* nccl_id);
+
+/* Parse a kleos_config.json and report the derived sizes for a given world size without
+ * touching the GPU (rank is reported as 0).  Same derivations as the reference's compile-time
+ * ACC struct (types.cuh:442-513). */
+int kleos_config_probe(const char* config_json_path, int world, kleos_layer_info* out);
+
+/* Optional per-expert logit bias (E floats, host memory).  The reference gate has no bias
+ * (moe/gate.cuh:87-88); the load-imbalanced benchmark layer needs one.  NULL clears it. */
+int kleos_set_gate_bias(const float* host_bias, int n);
+
+/* One layer forward, asynchronous on `stream` (a cudaStream_t, or NULL for the per-thread
+ * default stream the reference uses, types.cuh:1013).  iP and oP are DEVICE pointers to the
+ * packed buffers of moe.cuh:92-98:
+ *   iP = [A S*H][Wg PX*H][W1 nLx*I*H][W2 nLx*H*I][b1 nLx*I][b2 nLx*H]
+ *   oP = [gate probabilities S*PX][layer output S*H]
+ * Replaces kleos::moe::forwardHost(iP, oP) (moe/moe.cuh:186-205). */
+int kleos_forward(const void* iP, void* oP, void* stream);
+
+/* skip warm-up forwards, then trials forwards between two CUDA events; *ms = mean per
+ * forward.  Synchronises.  Replaces forwardHostBench<skip,trials> (moe/moe.cuh:146-184). */
+int kleos_forward_bench(const void* iP, void* oP, int skip, int trials, float* ms);
+
+/* End-to-end call with HOST buffers: copies S*H activations host->device into the A section
+ * of iP, runs one forward, copies the S*H layer output device->host, and synchronises.
+ * Weights stay resident in iP.  The reference driver does the same copies by hand
+ * (main.cu:64-66). */
+int kleos_forward_host(const void* host_activations, void* iP, void* oP, void* host_output);
+
+/* Reference: getRank() (bootstrap.cuh:555-559) and hostBookkeeping.nLx (main.cu:22). */
+int kleos_get_rank(void);
+int kleos_local_experts(void);
+int kleos_get_info(kleos_layer_info* out);
+
+/* Device-side status of the last forward calls; synchronises the library's stream.
+ * The reference has no equivalent: its device waits spin forever (atomics.cuh:96-138). */
+int kleos_last_status(kleos_status* out);
+
+/* Routing results of the last forward, copied to host memory (any pointer may be NULL):
+ * topk [S*K] expert ids, slots [S*K] slot inside the expert cell or -1 when dropped,
+ * counts [E] unclamped tokens per expert, mcw [S] sum of the k winning probabilities.
+ * The reference keeps these in its bookkeeping arena (types.cuh:697-1008) without an
+ * accessor; parity tests need them. */
+int kleos_debug_routing(int32_t* topk, int32_t* slots, uint32_t* counts, float* mcw);
+
+/* Per-phase device time of the most recent kleos_forward_bench, in milliseconds averaged over
+ * its trials: [0] route, [1] slots, [2] dispatch, [3] plan(wait), [4] GEMM1, [5] GEMM2,
+ * [6] combine, [7] whole forward.  n = number of floats the caller provides (>= 8). */
+int kleos_phase_times(float* ms, int n);
+
+/* Free everything.  Replaces kleos::finalize() (bootstrap.cuh:561-588). */
+int kleos_finalize(void);
+
+const char* kleos_error_string(int code);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KLEOS_B200_H */

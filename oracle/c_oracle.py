@@ -1,0 +1,90 @@
+"""ctypes loader for the C oracle (``moe_oracle.c``).  Test infrastructure only."""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+
+
+class OracleCfg(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int) for n in
+                ("S", "H", "I", "E", "K", "EC", "PX", "dtype", "hidden_act", "world")]
+
+
+def build(force: bool = False) -> str:
+    so = os.path.join(_HERE, "libmoe_oracle.so")
+    src = os.path.join(_HERE, "moe_oracle.c")
+    if force or not os.path.exists(so) or os.path.getmtime(so) < os.path.getmtime(src):
+        subprocess.check_call(["make", "-s", "-C", _HERE, "-B", "libmoe_oracle.so"])
+    return so
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        _LIB = ctypes.CDLL(build())
+        _LIB.oracle_num_threads.restype = ctypes.c_int
+    return _LIB
+
+
+def _cfg(cfg, world):
+    return OracleCfg(cfg.S, cfg.H, cfg.I, cfg.E, cfg.K, cfg.EC, cfg.PX, cfg.torch_dtype,
+                     cfg.hidden_act, world)
+
+
+def _fp(a):
+    return a.ctypes.data_as(ctypes.POINTER(ctypes.c_float))
+
+
+def num_threads() -> int:
+    return lib().oracle_num_threads()
+
+
+def moe_forward_rank(cfg, world, rank, inputs, gate_bias=None, tokens=None, accum64=True):
+    """Layer output for the tokens of one source rank; same result keys as the NumPy twin."""
+    L = lib()
+    c = _cfg(cfg, world)
+    nlx = cfg.E // world
+    me = inputs[rank]
+    A = np.ascontiguousarray(me["A"], dtype=np.float32)
+    Wg = np.ascontiguousarray(me["Wg"], dtype=np.float32)
+    keep = []
+
+    def ptrs(key):
+        arr = (ctypes.POINTER(ctypes.c_float) * cfg.E)()
+        for e in range(cfg.E):
+            owner, le = divmod(e, nlx)
+            a = np.ascontiguousarray(inputs[owner][key][le], dtype=np.float32)
+            keep.append(a)
+            arr[e] = _fp(a)
+        return arr
+
+    W1, W2, b1, b2 = ptrs("W1"), ptrs("W2"), ptrs("b1"), ptrs("b2")
+    bias = None if gate_bias is None else np.ascontiguousarray(gate_bias, dtype=np.float32)
+    tok = None if tokens is None else np.ascontiguousarray(tokens, dtype=np.int32)
+    nt = cfg.S if tok is None else len(tok)
+    probs = np.zeros((cfg.S, cfg.PX), dtype=np.float32)
+    topk = np.zeros((cfg.S, cfg.K), dtype=np.int32)
+    mcw = np.zeros(cfg.S, dtype=np.float32)
+    slots = np.zeros((cfg.S, cfg.K), dtype=np.int32)
+    counts = np.zeros(cfg.E, dtype=np.uint32)
+    margin = ctypes.c_double(0)
+    out = np.zeros((nt, cfg.H), dtype=np.float32)
+    rc = L.oracle_moe_forward_rank(
+        ctypes.byref(c), _fp(A), _fp(Wg), W1, W2, b1, b2,
+        None if bias is None else _fp(bias),
+        None if tok is None else tok.ctypes.data_as(ctypes.POINTER(ctypes.c_int)),
+        ctypes.c_int(nt), ctypes.c_int(1 if accum64 else 0), _fp(probs),
+        topk.ctypes.data_as(ctypes.POINTER(ctypes.c_int)), _fp(mcw),
+        slots.ctypes.data_as(ctypes.POINTER(ctypes.c_int)),
+        counts.ctypes.data_as(ctypes.POINTER(ctypes.c_uint32)), ctypes.byref(margin), _fp(out))
+    if rc:
+        raise RuntimeError(f"oracle_moe_forward_rank failed: {rc}")
+    return dict(probs=probs, topk=topk, mcw=mcw, slots=slots, counts=counts,
+                routed=np.minimum(counts, cfg.EC).astype(np.uint32), margin=margin.value,
+                out=out)

@@ -1,0 +1,80 @@
+"""Parity of the CUDA layer (through the C ABI, one GPU) against the CPU oracle."""
+import numpy as np
+import pytest
+
+from aristos_b200.config import KleosConfig, baseline_config
+from aristos_b200 import synth
+from oracle import c_oracle, moe_oracle
+from tests import moe_harness as hz
+
+pytestmark = pytest.mark.gpu
+
+
+def _small(dtype, **kw):
+    base = dict(sequence_len=256, hidden_size=512, intermediate_size=1024, num_experts=8,
+                torch_dtype=dtype)
+    base.update(kw)
+    return KleosConfig(**base)
+
+
+@pytest.mark.parametrize("dtype", [0, 2])
+def test_c1_shape_full_parity(dtype):
+    cfg = _small(dtype)
+    packed, views = hz.make_inputs(cfg, 1)
+    ref = moe_oracle.moe_forward(cfg, 1, views)[0]
+    probs, out, routing = hz.run_layer_single_gpu(cfg, packed[0])
+    hz.check_against_oracle(cfg, ref, probs, out, routing)
+
+
+@pytest.mark.parametrize("dtype", [0, 2])
+def test_repeat_forwards_and_host_path(dtype):
+    """Flags carry an epoch, so back-to-back forwards need no clearing; the host-buffer entry
+    point returns the same rows as the device path."""
+    cfg = _small(dtype)
+    packed, views = hz.make_inputs(cfg, 1)
+    ref = moe_oracle.moe_forward(cfg, 1, views)[0]
+    probs, out, routing = hz.run_layer_single_gpu(cfg, packed[0], forwards=3, via_host=True)
+    hz.check_against_oracle(cfg, ref, probs, out, routing)
+
+
+@pytest.mark.parametrize("dtype,kw", [
+    (2, dict(num_experts=128, sequence_len=512, hidden_size=256, intermediate_size=320,
+             capacity_factor=1.25)),          # PX = 128, fractional capacity, N tail (320 % 256)
+    (0, dict(num_experts=16, sequence_len=384, hidden_size=192, intermediate_size=192)),
+    (2, dict(num_experts=4, sequence_len=128, hidden_size=64, intermediate_size=64, expert_top_k=1)),
+    (2, dict(num_experts=8, sequence_len=256, hidden_size=256, intermediate_size=512, expert_top_k=4)),
+    (2, dict(hidden_act=1)),                  # GELU
+    (0, dict(hidden_act=1)),
+    (2, dict(drop_tokens=0, sequence_len=128, hidden_size=128, intermediate_size=128)),
+])
+def test_shapes_and_modes(dtype, kw):
+    cfg = _small(dtype, **kw)
+    packed, views = hz.make_inputs(cfg, 1)
+    ref = moe_oracle.moe_forward(cfg, 1, views)[0]
+    probs, out, routing = hz.run_layer_single_gpu(cfg, packed[0])
+    hz.check_against_oracle(cfg, ref, probs, out, routing)
+
+
+def test_zipf_bias_hot_experts_and_drops():
+    """Skewed routing: hot experts overflow their capacity, cold experts receive nothing."""
+    cfg = _small(2, num_experts=32, sequence_len=1024, hidden_size=256, intermediate_size=256,
+                 capacity_factor=1.25)
+    bias = synth.zipf_gate_bias(cfg, 1.2) * 2.0
+    packed, views = hz.make_inputs(cfg, 1)
+    ref = moe_oracle.moe_forward(cfg, 1, views, gate_bias=bias)[0]
+    assert (ref["slots"] < 0).sum() > 0 and (ref["counts"] == 0).sum() >= 0
+    probs, out, routing = hz.run_layer_single_gpu(cfg, packed[0], gate_bias=bias)
+    hz.check_against_oracle(cfg, ref, probs, out, routing)
+
+
+@pytest.mark.parametrize("name", ["C2", "C3"])
+def test_baseline_config_sampled(name):
+    """Full-size benchmark layers on one GPU: routing checked for every token, layer output
+    for a seeded sample of tokens (the oracle's FFN is evaluated only for those)."""
+    cfg, _ = baseline_config(name)
+    packed, views = hz.make_inputs(cfg, 1)
+    rng = np.random.default_rng(0)
+    rows = np.sort(rng.choice(cfg.S, size=96, replace=False)).astype(np.int32)
+    ref = c_oracle.moe_forward_rank(cfg, 1, 0, views, tokens=rows)
+    probs, out, routing = hz.run_layer_single_gpu(cfg, packed[0])
+    hz.check_against_oracle(cfg, ref, probs, out, routing, rows=rows)
