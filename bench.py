@@ -1,0 +1,339 @@
+#!/usr/bin/env python
+"""Benchmark of the MoE layer forward pass.
+
+  python bench.py --gpus N --steps K --warmup W            the CUDA path (this repository)
+  python bench.py --impl reference --steps K --warmup W     the CPU restatement of the reference
+
+One "step" is one forward pass of the layer over one batch of synthetic tokens on every rank.
+Workload: the 64-expert, 8192-tokens-per-GPU, H = I = 2048, top-2, bf16 layer (benchmark layer
+C3), experts sharded evenly over the N ranks; at N = 1 all 64 experts are local.  Prints one
+JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from aristos_b200.config import baseline_config  # noqa: E402
+
+METRIC = "moe_layer_fwd_tokens_per_s"
+KERNELS_PER_FORWARD = 8  # route, refine, slots, dispatch, plan, GEMM1, GEMM2, combine
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(tflops=float(p["bf16_tflops"]), hbm=float(p["hbm_gbs"]), source="measured")
+    return dict(tflops=1590.0, hbm=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "50"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) == 6:
+                self.rows.append(parts)
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                "sw_power_cap"), r[2:]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return dict(sm_mhz=statistics.median(sm) if sm else None,
+                    sm_max_mhz=max(mx) if mx else None, reasons=sorted(reasons),
+                    samples=len(sm))
+
+
+def synth_on_device(cfg, rank, world, device):
+    """Packed bf16 input of one rank, generated on the GPU: activations N(0,1) seeded by rank,
+    gate and expert weights N(0, 1/sqrt(fan_in)) seeded per global expert, zero biases."""
+    import torch
+    off = cfg.input_offsets(world)
+    nlx = cfg.local_experts(world)
+    buf = torch.zeros(off["end"], dtype=torch.bfloat16, device=device)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(1000 + rank)
+    buf[off["A"]:off["Wg"]] = torch.randn(cfg.S * cfg.H, generator=gen, device=device).bfloat16()
+    gen.manual_seed(7)
+    buf[off["Wg"]:off["Wg"] + cfg.E * cfg.H] = (
+        torch.randn(cfg.E * cfg.H, generator=gen, device=device) / cfg.H ** 0.5).bfloat16()
+    ih = cfg.I * cfg.H
+    for le in range(nlx):
+        e = rank * nlx + le
+        gen.manual_seed(100000 + e)
+        buf[off["W1"] + le * ih: off["W1"] + (le + 1) * ih] = (
+            torch.randn(ih, generator=gen, device=device) / cfg.H ** 0.5).bfloat16()
+        buf[off["W2"] + le * ih: off["W2"] + (le + 1) * ih] = (
+            torch.randn(ih, generator=gen, device=device) / cfg.I ** 0.5).bfloat16()
+    return buf
+
+
+def cpu_sample_tokens_per_s(cfg, views, sample_tokens: int, repeats: int = 1):
+    """Times the C restatement of the reference's math (fp32 accumulation, all host threads)
+    on the first `sample_tokens` tokens of one rank; routing covers all S tokens."""
+    from oracle import c_oracle
+    rows = np.arange(sample_tokens, dtype=np.int32)
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        c_oracle.moe_forward_rank(cfg, 1, 0, views, tokens=rows, accum64=False)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return sample_tokens / best, best, c_oracle.num_threads()
+
+
+def host_views_from_device(cfg, buf, world):
+    from aristos_b200 import synth
+    host = buf.float().cpu().numpy()
+    return [synth.split_packed(cfg, host, world)]
+
+
+def run_reference(args):
+    """The reference's own path restated for the CPU (the reference has no CPU implementation
+    and cannot be built for sm_100), timed on the host cores; rank 0 only."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+    from aristos_b200 import synth
+    cfg, _ = baseline_config("C3")
+    torch.manual_seed(0)
+    off = cfg.input_offsets(1)
+    buf = torch.zeros(off["end"], dtype=torch.float32)
+    buf[off["A"]:off["Wg"]] = torch.randn(cfg.S * cfg.H)
+    buf[off["Wg"]:off["Wg"] + cfg.E * cfg.H] = torch.randn(cfg.E * cfg.H) / cfg.H ** 0.5
+    n = 2 * cfg.E * cfg.I * cfg.H
+    buf[off["W1"]:off["W1"] + n] = torch.randn(n) / cfg.H ** 0.5  # fan_in H = I for this layer
+    host = buf.bfloat16().float().numpy()
+    views = [synth.split_packed(cfg, host, 1)]
+    sample = args.cpu_sample
+    for _ in range(args.warmup):
+        cpu_sample_tokens_per_s(cfg, views, sample)
+    t0 = time.perf_counter()
+    threads = 1
+    for _ in range(args.steps):
+        _, _, threads = cpu_sample_tokens_per_s(cfg, views, sample)
+    dt = time.perf_counter() - t0
+    value = sample * args.steps / dt
+    line = dict(
+        impl="reference", metric=METRIC, value=value, unit="tokens/s", n_gpus=args.gpus,
+        steps=args.steps, warmup=args.warmup, ms_per_step=1e3 * dt / args.steps,
+        higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16", data="synthetic",
+        config=dict(workload="C3: S=8192 tokens/rank, H=I=2048, E=64, top-2, CF=1, bf16",
+                    note="CPU restatement of the reference math; the reference has no CPU path "
+                         "and does not compile for sm_100"),
+        cpu_baseline=dict(value=value, unit="tokens/s", cores=threads, kind="port",
+                          sample=f"each step: first {sample} of 8192 tokens of one rank through "
+                                 "all 64 experts, routing over all 8192 tokens, fp32 accumulation"),
+        e2e=dict(value=value, unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
+        gpu_launches=0,
+    )
+    print(json.dumps(line), flush=True)
+
+
+def run_cuda(args):
+    import torch
+    import torch.distributed as dist
+    from aristos_b200 import kleos
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    uid = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+        idt = torch.zeros(128, dtype=torch.uint8, device=device)
+        if rank == 0:
+            idt.copy_(torch.frombuffer(bytearray(kleos.get_unique_id()), dtype=torch.uint8))
+        dist.broadcast(idt, 0)
+        uid = bytes(idt.cpu().numpy().tobytes())
+
+    cfg, _ = baseline_config("C3")
+    kleos.set_device(local_rank)
+    info = kleos.initialize(cfg, rank, world, uid)
+    iP = synth_on_device(cfg, rank, world, device)
+    oP = torch.zeros(info.output_elems, dtype=torch.bfloat16, device=device)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(v: float) -> float:
+        if world == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---------------------------------------------------------------- device-resident timing
+    for _ in range(args.warmup):
+        kleos.forward_host(iP, oP, stream)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        kleos.forward_host(iP, oP, stream)
+    e1.record()
+    barrier()
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    st = kleos.last_status()
+    if st.code:
+        raise SystemExit(f"device status: where={st.where} detail={st.detail}")
+
+    # ---------------------------------------------------------------- end to end, host buffers
+    act_elems = cfg.S * cfg.H
+    host_in = torch.empty(act_elems, dtype=torch.bfloat16).pin_memory()
+    host_in.copy_(iP[:act_elems].cpu())
+    host_out = torch.empty(act_elems, dtype=torch.bfloat16).pin_memory()
+    for _ in range(max(1, args.warmup // 2)):
+        kleos.forward_from_host(host_in, iP, oP, host_out)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        kleos.forward_from_host(host_in, iP, oP, host_out)
+    barrier()
+    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---------------------------------------------------------------- per-phase times, roofline
+    kleos.forward_host_bench(iP, oP, skip=2, trials=max(4, min(args.steps, 16)))
+    phases = kleos.phase_times()
+    routing = kleos.debug_routing(info)
+    routed_here = int(np.minimum(routing["counts"], info.EC).sum())  # pairs this rank dispatched
+    # pairs this rank's experts processed: under even sharding and random routing this equals
+    # the pairs it dispatched to within sampling noise; the all-rank sum is identical
+    pairs = torch.tensor([routed_here], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(pairs)
+    pairs_per_rank = float(pairs.item()) / world
+    peaks = load_peaks()
+    gemm_flops = 2.0 * pairs_per_rank * cfg.H * cfg.I  # one of the two FFN GEMM launches
+    gemm_ms = 0.5 * (phases["gemm1"] + phases["gemm2"])
+    gemm_ms = max_over_ranks(gemm_ms)
+    achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12
+    total_flops = 2.0 * cfg.S * cfg.H * cfg.E + 4.0 * cfg.H * cfg.I * pairs_per_rank
+    remote_pairs = pairs_per_rank * (world - 1) / world
+    link_bytes = 2.0 * remote_pairs * cfg.H * 2
+    t_roof_ms = max(total_flops / (peaks["tflops"] * 1e12), link_bytes / 770e9) * 1e3
+    ms_per_step = ms_total / args.steps
+
+    if rank == 0:
+        tokens = cfg.S * world
+        line = dict(
+            metric=METRIC, value=tokens / (ms_per_step * 1e-3), unit="tokens/s", n_gpus=world,
+            steps=args.steps, warmup=args.warmup, ms_per_step=ms_per_step,
+            higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16",
+            data="synthetic",
+            config=dict(workload="C3: S=8192 tokens/rank, H=I=2048, E=64, top-2, CF=1, bf16",
+                        experts_per_rank=info.local_experts, parallelism=f"ep{world}",
+                        l2="working set per step (weights + cells + activations) exceeds L2"),
+            e2e=dict(value=tokens * args.steps / e2e_s, unit="tokens/s",
+                     h2d_bytes_per_step=act_elems * 2, d2h_bytes_per_step=act_elems * 2),
+            gpu_launches=KERNELS_PER_FORWARD * args.steps,
+            clocks=clocks,
+            roofline=dict(bound="tensor", achieved=achieved, peak=peaks["tflops"], unit="TFLOP/s",
+                          frac=achieved / peaks["tflops"], traffic=None,
+                          kernel="ffn_gemm_tc (mean of the GEMM1 and GEMM2 launches)",
+                          peak_source=peaks["source"]),
+            layer_roofline=dict(t_roof_ms=t_roof_ms, frac=t_roof_ms / ms_per_step,
+                                flops=total_flops, link_bytes_each_way=link_bytes),
+            phases_ms=phases,
+            routed_pairs_per_rank=pairs_per_rank,
+        )
+        if args.cpu_baseline and world == 1:
+            views = host_views_from_device(cfg, iP, world)
+            v, dt, threads = cpu_sample_tokens_per_s(cfg, views, args.cpu_sample)
+            line["cpu_baseline"] = dict(
+                value=v, unit="tokens/s", cores=threads, kind="port",
+                sample=f"first {args.cpu_sample} of 8192 tokens of rank 0 through all 64 experts "
+                       f"(routing over all 8192 tokens), fp32 accumulation, {dt:.1f} s")
+        print(json.dumps(line), flush=True)
+    kleos.finalize()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
+    ap.add_argument("--cpu-sample", type=int, default=0,
+                    help="tokens in the CPU baseline sample")
+    ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.cpu_sample <= 0:
+        # reference arm: a quarter of one rank's batch per step; CUDA arm: the whole batch once
+        args.cpu_sample = 2048 if args.impl == "reference" else 8192
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_cuda(args)
+
+
+if __name__ == "__main__":
+    main()
