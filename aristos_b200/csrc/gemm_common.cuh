@@ -24,6 +24,7 @@ struct GemmArgs {
     ArenaLayout lay;
     ReturnFlagArgs ret;   // mode 1: flags raised by the last block
     DeviceStatus* status;
+    long long* stats;     // optional [grid][8] per-role stall counters (cycles), or null
     long long wait_cycles;
     int N, Kd, mode, hidden_act;
     int nLx, pEC, rank, elem_bytes;

@@ -1,0 +1,320 @@
+// Expert-FFN GEMM with paired blocks (tcgen05 cta_group::2): a cluster of two blocks on
+// neighbouring SMs computes a 256 x 256 output tile -- two 128-row panels of the same local
+// expert against the same 256 weight rows.  Each block TMA-loads its own panel (A) and only
+// HALF of the weight tile (B), so the bytes pulled into an SM per FLOP drop by a third compared
+// with one block per 128 x 256 tile, and the freed shared memory deepens the pipeline to six
+// stages.  No load is multicast: every block fetches exactly the bytes it keeps.
+//
+// Per block, 256 threads:
+//   warp 0      TMA producer (one lane): waits on its own `empty`, loads into its own shared
+//               memory, credits the bytes to the LEADER's `full` barrier
+//   warp 1      leader only: issues tcgen05.mma.cta_group::2, commits to `empty` and
+//               `acc_full` of BOTH blocks
+//   warp 2      tensor-memory allocation / release (both blocks, cta_group::2 forms)
+//   warps 4..7  epilogue of the block's own 128 accumulator rows; arrives on the LEADER's
+//               `acc_empty`
+// Work and epilogue semantics are those of gemm_tc.cuh (reference
+// os/processor/processor.cuh:350-489,706-741).  Every wait is bounded.
+#pragma once
+
+#include <cuda.h>
+
+#include "gemm_common.cuh"
+#include "tc_common.cuh"
+
+namespace kleos {
+namespace gemm_tc2 {
+
+constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16, STAGES = 6;
+constexpr int A_STAGE_BYTES = BM * BK * 2;        // 16 KiB: this block's panel
+constexpr int B_STAGE_BYTES = (BN / 2) * BK * 2;  // 16 KiB: this block's half of the weight tile
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int TMEM_COLS = 512;  // two accumulators of 256 fp32 columns
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 12288;
+constexpr uint32_t kInstrDesc = tc::make_instr_desc_bf16(2 * BM, BN);
+
+struct Control {
+    unsigned long long full[STAGES];   // used on the leader
+    unsigned long long empty[STAGES];  // one per block
+    unsigned long long acc_full[2];    // one per block
+    unsigned long long acc_empty[2];   // used on the leader, 8 arrivals (4 warps x 2 blocks)
+    uint32_t tmem_base;
+    int abort;
+    int le_start[257];
+    __align__(16) float bias_s[2][4][256];  // bias of the tile being read back: [accumulator][epilogue warp]
+};
+
+struct PairTile {
+    int panel0, n_panels_left, nt, le;
+};
+
+// Tiles ordered by local expert, then N tile, then panel pair.
+__device__ __forceinline__ bool decode_pair_tile(int t, const int* le_start, int nLx, int NT,
+                                                 PairTile* c) {
+    for (int le = 0; le < nLx; ++le) {
+        const int p0 = le_start[le], np = le_start[le + 1] - p0;
+        const int npair = (np + 1) >> 1;
+        const int tiles = npair * NT;
+        if (t < tiles) {
+            const int nt = t / npair, pi = t - nt * npair;
+            c->le = le;
+            c->nt = nt;
+            c->panel0 = p0 + 2 * pi;
+            c->n_panels_left = np - 2 * pi;  // 1 when the pair's second panel does not exist
+            return true;
+        }
+        t -= tiles;
+    }
+    return false;
+}
+
+__device__ __forceinline__ int total_pair_tiles(const int* le_start, int nLx, int NT) {
+    int total = 0;
+    for (int le = 0; le < nLx; ++le) total += ((le_start[le + 1] - le_start[le] + 1) >> 1) * NT;
+    return total;
+}
+
+}  // namespace gemm_tc2
+
+// kEpi selects the fused epilogue at compile time (0: bias + ReLU, 1: bias + GELU, 2: bias only)
+// so the read-back loop stays a short straight-line sequence.
+template <int kEpi>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(256, 1)
+ffn_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+             GemmArgs g) {
+    using namespace tc;
+    using namespace gemm_tc2;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* tiles = reinterpret_cast<uint8_t*>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    Control* ctl = reinterpret_cast<Control*>(tiles + STAGES * STAGE_BYTES);
+    __shared__ bool last_block;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t cta_rank = cluster_ctarank();
+    const bool leader = cta_rank == 0;
+    volatile int* abort_flag = &ctl->abort;
+
+    for (int i = tid; i <= g.nLx; i += blockDim.x) ctl->le_start[i] = g.le_start[i];
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&ctl->full[s], 1);
+            mbar_init(&ctl->empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&ctl->acc_full[b], 1);
+            mbar_init(&ctl->acc_empty[b], 8);
+        }
+        ctl->abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 2) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&ctl->tmem_base)), "r"(TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();  // both blocks' barriers exist before anything remote touches them
+    tc_fence_after();
+    const uint32_t tmem_base = ctl->tmem_base;
+
+    const int NT = (g.N + BN - 1) / BN;
+    const int total = total_pair_tiles(ctl->le_start, g.nLx, NT);
+    const int KB = g.Kd / BK;
+    const int n_clusters = gridDim.x >> 1, cluster_id = blockIdx.x >> 1;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer (both blocks)
+        if (lane == 0) {
+            asm volatile("fence.proxy.async;" ::: "memory");
+            uint32_t it = 0;
+            long long w_empty = 0;
+            const long long t_begin = clock64();
+            for (int t = cluster_id; t < total && !*abort_flag; t += n_clusters) {
+                PairTile pt;
+                if (!decode_pair_tile(t, ctl->le_start, g.nLx, NT, &pt)) break;
+                // the block without a panel of its own re-reads the first one and discards
+                const int my_panel = pt.panel0 + ((int)cta_rank < pt.n_panels_left ? (int)cta_rank : 0);
+                const PanelEntry p = g.panels[my_panel];
+                const int brow = pt.le * g.N + pt.nt * BN + (int)cta_rank * (BN / 2);
+                for (int kb = 0; kb < KB; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait_timed(&ctl->empty[s], ph ^ 1, g.wait_cycles, abort_flag, &w_empty)) {
+                        report_error(g.status, KLEOS_AT_GEMM_PRODUCER, t, (int)g.epoch);
+                        *abort_flag = 1;
+                        break;
+                    }
+                    // the leader announces the bytes of both blocks on its own barrier
+                    if (leader) mbar_expect_tx(&ctl->full[s], 2 * STAGE_BYTES);
+                    const uint32_t full_leader = map_to_cta(smem_u32(&ctl->full[s]), 0);
+                    uint8_t* sa = tiles + s * STAGE_BYTES;
+                    tma_load_2d_pair(sa, &map_a, kb * BK, p.row_base, full_leader);
+                    tma_load_2d_pair(sa + A_STAGE_BYTES, &map_b, kb * BK, brow, full_leader);
+                }
+            }
+            if (g.stats) {
+                g.stats[blockIdx.x * 8 + 0] = w_empty;
+                g.stats[blockIdx.x * 8 + 1] = clock64() - t_begin;
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer (leader only)
+        if (leader && lane == 0) {
+            uint32_t it = 0, tile_n = 0;
+            long long w_acc = 0, w_full = 0;
+            const long long t_begin = clock64();
+            for (int t = cluster_id; t < total && !*abort_flag; t += n_clusters, ++tile_n) {
+                const uint32_t buf = tile_n & 1, use = tile_n >> 1;
+                if (!mbar_wait_timed(&ctl->acc_empty[buf], (use & 1) ^ 1, g.wait_cycles, abort_flag, &w_acc)) {
+                    report_error(g.status, KLEOS_AT_GEMM_MMA, t, (int)g.epoch);
+                    *abort_flag = 1;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                bool ok = true;
+                for (int kb = 0; kb < KB; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait_timed(&ctl->full[s], ph, g.wait_cycles, abort_flag, &w_full)) {
+                        report_error(g.status, KLEOS_AT_GEMM_MMA, t, (int)g.epoch);
+                        *abort_flag = 1;
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(tiles + s * STAGE_BYTES);
+                    const uint64_t da = make_smem_desc(sa);
+                    const uint64_t db = make_smem_desc(sa + A_STAGE_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        umma_bf16_pair(d_tmem, da + 2 * k, db + 2 * k, kInstrDesc,
+                                       (kb | k) != 0 ? 1u : 0u);
+                    // the stage is free in both blocks once these MMAs have read it
+                    const uint32_t e_local = smem_u32(&ctl->empty[s]);
+                    umma_commit_pair(map_to_cta(e_local, 0));
+                    umma_commit_pair(map_to_cta(e_local, 1));
+                }
+                if (!ok) break;
+                const uint32_t f_local = smem_u32(&ctl->acc_full[buf]);
+                umma_commit_pair(map_to_cta(f_local, 0));
+                umma_commit_pair(map_to_cta(f_local, 1));
+            }
+            if (g.stats) {
+                g.stats[blockIdx.x * 8 + 2] = w_acc;
+                g.stats[blockIdx.x * 8 + 3] = w_full;
+                g.stats[blockIdx.x * 8 + 4] = clock64() - t_begin;
+            }
+        }
+        __syncwarp();
+    } else if (warp >= 4) {
+        // ------------------------------------------------------------ epilogue (both blocks)
+        const int q = warp - 4;
+        const int row = q * 32 + lane;
+        const __nv_bfloat16* bias = static_cast<const __nv_bfloat16*>(g.bias);
+        uint32_t tile_n = 0;
+        long long w_accfull = 0, w_tmem = 0;
+        const long long t_begin = clock64();
+        for (int t = cluster_id; t < total; t += n_clusters, ++tile_n) {
+            PairTile pt;
+            if (!decode_pair_tile(t, ctl->le_start, g.nLx, NT, &pt)) break;
+            const bool have_panel = (int)cta_rank < pt.n_panels_left;
+            const PanelEntry p = g.panels[pt.panel0 + (have_panel ? (int)cta_rank : 0)];
+            const int rows = have_panel ? p.rows : 0;
+            const uint32_t buf = tile_n & 1, use = tile_n >> 1;
+            if (*abort_flag) break;
+            {
+                // stage this tile's 256 bias values in shared memory (one private copy per warp,
+                // one 16-byte load per lane) while the main loop of the tile is still running:
+                // global loads issued later would queue behind the operand traffic streaming
+                // into this SM
+                const int nb = pt.nt * BN + 8 * lane;
+                float* bs = &ctl->bias_s[buf][q][8 * lane];
+                if (nb < g.N) {
+                    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(
+                        bias + (size_t)pt.le * g.N + nb));
+                    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float2 f = __bfloat1622float2(h2[j]);
+                        bs[2 * j] = f.x;
+                        bs[2 * j + 1] = f.y;
+                    }
+                }
+                __syncwarp();
+            }
+            if (!mbar_wait_timed(&ctl->acc_full[buf], use & 1, g.wait_cycles, abort_flag, &w_accfull)) {
+                if (lane == 0) report_error(g.status, KLEOS_AT_GEMM_EPILOGUE, t, (int)g.epoch);
+                *abort_flag = 1;
+                break;
+            }
+            tc_fence_after();
+            const int n0 = pt.nt * BN;
+            const uint32_t taddr = tmem_base + buf * BN + (static_cast<uint32_t>(q * 32) << 16);
+            __nv_bfloat16* orow = (row < rows) ? out_ptr<__nv_bfloat16>(g, p, row, n0) : nullptr;
+            // accumulator read-back, two 32-column chunks in flight; bias fetched as 16-byte
+            // broadcast loads
+            uint32_t r[2][32];
+            tmem_ld_32x32(taddr, r[0]);
+#pragma unroll
+            for (int c = 0; c < BN / 32; ++c) {
+                const long long tq = clock64();
+                tmem_ld_wait();
+                w_tmem += clock64() - tq;
+                if (c + 1 < BN / 32) tmem_ld_32x32(taddr + (c + 1) * 32, r[(c + 1) & 1]);
+                if (orow != nullptr && n0 + c * 32 < g.N) {
+                    const uint32_t* rc = r[c & 1];
+                    const float4* bq = reinterpret_cast<const float4*>(&ctl->bias_s[buf][q][c * 32]);
+                    uint32_t packed[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const float4 bf = bq[j >> 1];
+                        float v0 = __uint_as_float(rc[2 * j]) + ((j & 1) ? bf.z : bf.x);
+                        float v1 = __uint_as_float(rc[2 * j + 1]) + ((j & 1) ? bf.w : bf.y);
+                        if constexpr (kEpi == 0) {
+                            v0 = fmaxf(v0, 0.f);
+                            v1 = fmaxf(v1, 0.f);
+                        } else if constexpr (kEpi == 1) {
+                            v0 = apply_act(v0, 1);
+                            v1 = apply_act(v1, 1);
+                        }
+                        const __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
+                        packed[j] = *reinterpret_cast<const uint32_t*>(&h);
+                    }
+                    uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        dst[j] = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2],
+                                            packed[4 * j + 3]);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&ctl->acc_empty[buf]), 0));
+        }
+        if (g.stats && warp == 4 && lane == 0) {
+            g.stats[blockIdx.x * 8 + 5] = w_accfull;
+            g.stats[blockIdx.x * 8 + 6] = clock64() - t_begin;
+            g.stats[blockIdx.x * 8 + 7] = w_tmem;
+        }
+    }
+
+    // teardown: neither block may leave while its partner can still touch its shared memory,
+    // barriers or tensor memory
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 2) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                     "r"(TMEM_COLS)
+                     : "memory");
+    }
+    if (g.mode == 1) publish_return_flags(g.ret, &last_block);
+}
+
+}  // namespace kleos

@@ -20,7 +20,9 @@
 #include "config.hpp"
 #include "gemm_simt.cuh"
 #include "gemm_tc.cuh"
+#include "gemm_tc2.cuh"
 #include "route.cuh"
+#include "route_tc.cuh"
 #include "transport.cuh"
 
 namespace kleos {
@@ -46,6 +48,7 @@ struct State {
     uint32_t epoch = 0;
     long long wait_cycles = 4000000000LL;  // about two seconds of SM clock
     bool use_tc = false;
+    bool use_pair = true;  // cta_group::2 GEMM (two blocks per 256x256 tile)
 
     // symmetric arena
     ArenaLayout lay{};
@@ -56,16 +59,18 @@ struct State {
     // local bookkeeping
     void* y1 = nullptr;
     int *topk = nullptr, *slots = nullptr, *cell_tokens = nullptr, *refine_list = nullptr,
-        *refine_count = nullptr, *le_start = nullptr;
+        *refine_count = nullptr, *le_start = nullptr, *refine_done = nullptr;
+    double* refine_logits = nullptr;
     float *mcw = nullptr, *bias = nullptr;
     unsigned *counts = nullptr, *done_dispatch = nullptr, *done_gemm2 = nullptr,
              *cell_counts = nullptr;
     PanelEntry* panels = nullptr;
     DeviceStatus* status = nullptr;
+    long long* gemm_stats = nullptr;  // [2][grid][8] when KLEOS_GEMM_STATS=1
 
     // tensor maps (rebuilt when the caller's weight pointer changes)
     const void* maps_for_iP = nullptr;
-    CUtensorMap map_x{}, map_w1{}, map_y1{}, map_w2{};
+    CUtensorMap map_x{}, map_w1{}, map_y1{}, map_w2{}, map_act{}, map_wg{}, map_w1h{}, map_w2h{};
 
     ncclComm_t comm = nullptr;
     cudaEvent_t ev[kPhases + 1] = {};
@@ -198,10 +203,16 @@ int ensure_maps(const Sections& s) {
     const LayerConfig& c = g.cfg;
     const uint64_t cell_rows = (uint64_t)g.world * g.nLx * c.pEC;
     int rc;
-    if ((rc = make_map(&g.map_x, g.arena + g.lay.xcell, cell_rows, c.H, tc::BM))) return rc;
-    if ((rc = make_map(&g.map_w1, s.W1, (uint64_t)g.nLx * c.I, c.H, tc::BN))) return rc;
-    if ((rc = make_map(&g.map_y1, g.y1, cell_rows, c.I, tc::BM))) return rc;
-    if ((rc = make_map(&g.map_w2, s.W2, (uint64_t)g.nLx * c.H, c.I, tc::BN))) return rc;
+    if ((rc = make_map(&g.map_x, g.arena + g.lay.xcell, cell_rows, c.H, gemm_tc::BM))) return rc;
+    if ((rc = make_map(&g.map_w1, s.W1, (uint64_t)g.nLx * c.I, c.H, gemm_tc::BN))) return rc;
+    if ((rc = make_map(&g.map_y1, g.y1, cell_rows, c.I, gemm_tc::BM))) return rc;
+    if ((rc = make_map(&g.map_w2, s.W2, (uint64_t)g.nLx * c.H, c.I, gemm_tc::BN))) return rc;
+    if ((rc = make_map(&g.map_w1h, s.W1, (uint64_t)g.nLx * c.I, c.H, gemm_tc2::BN / 2))) return rc;
+    if ((rc = make_map(&g.map_w2h, s.W2, (uint64_t)g.nLx * c.H, c.I, gemm_tc2::BN / 2))) return rc;
+    if (c.PX <= 128) {
+        if ((rc = make_map(&g.map_act, s.A, c.S, c.H, route_tc::BM))) return rc;
+        if ((rc = make_map(&g.map_wg, s.Wg, c.PX, c.H, c.PX))) return rc;
+    }
     g.maps_for_iP = s.A;
     return KLEOS_OK;
 }
@@ -225,7 +236,7 @@ int launch_route(const RouteArgs& ra, cudaStream_t st) {
     } else {
         return fail(KLEOS_E_UNSUPPORTED, "more than 256 experts are not supported by the router");
     }
-    refine_kernel<T><<<64, 128, sizeof(double) * ra.E, st>>>(ra);
+    refine_kernel<T><<<148, 256, 0, st>>>(ra);
     return KLEOS_OK;
 }
 
@@ -245,8 +256,22 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed) {
     RouteArgs ra{};
     ra.A = s.A; ra.Wg = s.Wg; ra.bias = g.bias; ra.probs = s.probs; ra.topk = g.topk;
     ra.mcw = g.mcw; ra.refine_list = g.refine_list; ra.refine_count = g.refine_count;
+    ra.refine_logits = g.refine_logits; ra.refine_done = g.refine_done;
     ra.S = c.S; ra.H = c.H; ra.E = c.E; ra.K = c.K; ra.PX = c.PX; ra.tie_eps = 1e-4f;
-    if ((rc = launch_route<T>(ra, st))) return rc;
+    if (g.use_tc && c.PX <= 128) {
+        if constexpr (sizeof(T) == 2) {
+            const int grid = (c.S + route_tc::BM - 1) / route_tc::BM;
+            if (c.PX == 64)
+                route_tc_kernel<64><<<grid, 256, route_tc::Shape<64>::SMEM_BYTES, st>>>(
+                    g.map_act, g.map_wg, ra, g.status, g.wait_cycles, (int)g.epoch);
+            else
+                route_tc_kernel<128><<<grid, 256, route_tc::Shape<128>::SMEM_BYTES, st>>>(
+                    g.map_act, g.map_wg, ra, g.status, g.wait_cycles, (int)g.epoch);
+            refine_kernel<T><<<148, 256, 0, st>>>(ra);
+        }
+    } else if ((rc = launch_route<T>(ra, st))) {
+        return rc;
+    }
     KLEOS_CUDA(mark());
 
     // 2. slots
@@ -274,7 +299,7 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed) {
     // 5./6. expert FFN
     GemmArgs ga{};
     ga.panels = g.panels; ga.le_start = g.le_start; ga.y1 = g.y1; ga.peers = g.peers;
-    ga.lay = g.lay; ga.status = g.status; ga.wait_cycles = g.wait_cycles;
+    ga.lay = g.lay; ga.status = g.status; ga.wait_cycles = g.wait_cycles; ga.stats = nullptr;
     ga.hidden_act = c.hidden_act; ga.nLx = g.nLx; ga.pEC = c.pEC; ga.rank = g.rank;
     ga.elem_bytes = c.elem_bytes; ga.epoch = g.epoch;
     ga.ret.peers = g.peers; ga.ret.lay = g.lay; ga.ret.done_counter = g.done_gemm2;
@@ -284,12 +309,30 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed) {
     g1.A = g.arena + g.lay.xcell; g1.B = s.W1; g1.bias = s.b1; g1.N = c.I; g1.Kd = c.H; g1.mode = 0;
     GemmArgs g2 = ga;
     g2.A = g.y1; g2.B = s.W2; g2.bias = s.b2; g2.N = c.H; g2.Kd = c.I; g2.mode = 1;
+    if (g.gemm_stats) {
+        g1.stats = g.gemm_stats;
+        g2.stats = g.gemm_stats + (size_t)g.sm_count * 8;
+    }
     if (g.use_tc) {
         if constexpr (sizeof(T) == 2) {
-            ffn_gemm_tc<<<g.sm_count, 256, tc::SMEM_BYTES, st>>>(g.map_x, g.map_w1, g1);
-            KLEOS_CUDA(mark());
-            ffn_gemm_tc<<<g.sm_count, 256, tc::SMEM_BYTES, st>>>(g.map_y1, g.map_w2, g2);
-            KLEOS_CUDA(mark());
+            if (g.use_pair) {
+                const int grid = g.sm_count & ~1;
+                if (c.hidden_act == 0)
+                    ffn_gemm_tc2<0><<<grid, 256, gemm_tc2::SMEM_BYTES, st>>>(g.map_x, g.map_w1h, g1);
+                else
+                    ffn_gemm_tc2<1><<<grid, 256, gemm_tc2::SMEM_BYTES, st>>>(g.map_x, g.map_w1h, g1);
+                KLEOS_CUDA(mark());
+                ffn_gemm_tc2<2><<<grid, 256, gemm_tc2::SMEM_BYTES, st>>>(g.map_y1, g.map_w2h, g2);
+                KLEOS_CUDA(mark());
+            } else {
+                if (c.hidden_act == 0)
+                    ffn_gemm_tc<0><<<g.sm_count, 256, gemm_tc::SMEM_BYTES, st>>>(g.map_x, g.map_w1, g1);
+                else
+                    ffn_gemm_tc<1><<<g.sm_count, 256, gemm_tc::SMEM_BYTES, st>>>(g.map_x, g.map_w1, g1);
+                KLEOS_CUDA(mark());
+                ffn_gemm_tc<2><<<g.sm_count, 256, gemm_tc::SMEM_BYTES, st>>>(g.map_y1, g.map_w2, g2);
+                KLEOS_CUDA(mark());
+            }
         }
     } else {
         ffn_gemm_simt<T><<<g.sm_count * 2, 256, 0, st>>>(g1);
@@ -304,7 +347,12 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed) {
     ca.mcw = g.mcw; ca.out = s.out; ca.status = g.status; ca.S = c.S; ca.H = c.H; ca.K = c.K;
     ca.PX = c.PX; ca.pEC = c.pEC; ca.world = g.world; ca.epoch = g.epoch;
     ca.wait_cycles = g.wait_cycles;
-    combine_kernel<T><<<g.sm_count * 4, 256, 0, st>>>(ca);
+    if (c.K == 2)
+        combine_kernel<T, 2><<<g.sm_count * 4, 256, 0, st>>>(ca);
+    else if (c.K == 1)
+        combine_kernel<T, 1><<<g.sm_count * 4, 256, 0, st>>>(ca);
+    else
+        combine_kernel<T, 0><<<g.sm_count * 4, 256, 0, st>>>(ca);
     KLEOS_CUDA(mark());
     KLEOS_CUDA(cudaGetLastError());
     return KLEOS_OK;
@@ -322,9 +370,9 @@ void release_all() {
         if (g.peer_opened[r]) cudaIpcCloseMemHandle(g.peers.arena[r]);
     cudaFree(g.arena);
     cudaFree(g.y1); cudaFree(g.topk); cudaFree(g.slots); cudaFree(g.cell_tokens);
-    cudaFree(g.refine_list); cudaFree(g.refine_count); cudaFree(g.le_start); cudaFree(g.mcw);
+    cudaFree(g.refine_list); cudaFree(g.refine_count); cudaFree(g.refine_done); cudaFree(g.refine_logits); cudaFree(g.le_start); cudaFree(g.mcw);
     cudaFree(g.bias); cudaFree(g.counts); cudaFree(g.done_dispatch); cudaFree(g.done_gemm2);
-    cudaFree(g.cell_counts); cudaFree(g.panels); cudaFree(g.status);
+    cudaFree(g.cell_counts); cudaFree(g.panels); cudaFree(g.status); cudaFree(g.gemm_stats);
     for (auto& e : g.ev)
         if (e) cudaEventDestroy(e);
     if (g.comm && nccl.CommDestroy) nccl.CommDestroy(g.comm);
@@ -444,6 +492,8 @@ int kleos_initialize(const char* config_json_path, int rank, int world, const vo
     if ((rc = dev_alloc(&g.cell_tokens, (size_t)cfg.E * cfg.pEC))) return rc;
     if ((rc = dev_alloc(&g.refine_list, (size_t)cfg.S))) return rc;
     if ((rc = dev_alloc(&g.refine_count, 1))) return rc;
+    if ((rc = dev_alloc(&g.refine_done, (size_t)cfg.S))) return rc;
+    if ((rc = dev_alloc(&g.refine_logits, (size_t)cfg.S * cfg.E))) return rc;
     if ((rc = dev_alloc(&g.le_start, (size_t)g.nLx + 1))) return rc;
     if ((rc = dev_alloc(&g.mcw, (size_t)cfg.S))) return rc;
     if ((rc = dev_alloc(&g.bias, (size_t)cfg.E))) return rc;
@@ -454,10 +504,25 @@ int kleos_initialize(const char* config_json_path, int rank, int world, const vo
     if ((rc = dev_alloc(&g.panels, (size_t)cfg.E * cfg.pEC / kTileM))) return rc;
     if ((rc = dev_alloc(&g.status, 1))) return rc;
     for (auto& e : g.ev) KLEOS_CUDA(cudaEventCreate(&e));
+    if (const char* gs = std::getenv("KLEOS_GEMM_STATS"))
+        if (gs[0] == '1' && (rc = dev_alloc(&g.gemm_stats, (size_t)2 * g.sm_count * 8))) return rc;
 
+    if (g.use_tc) {
+        KLEOS_CUDA(cudaFuncSetAttribute(route_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        route_tc::Shape<64>::SMEM_BYTES));
+        KLEOS_CUDA(cudaFuncSetAttribute(route_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        route_tc::Shape<128>::SMEM_BYTES));
+    }
+    if (const char* pr = std::getenv("KLEOS_GEMM_PAIR")) g.use_pair = pr[0] != '0';
     if (g.use_tc)
-        KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        tc::SMEM_BYTES));
+    {
+        KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm_tc2::SMEM_BYTES));
+        KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm_tc2::SMEM_BYTES));
+        KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm_tc2::SMEM_BYTES));
+        KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm_tc::SMEM_BYTES));
+        KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm_tc::SMEM_BYTES));
+        KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm_tc::SMEM_BYTES));
+    }
 
     for (int r = 0; r < kMaxWorld; ++r) g.peers.arena[r] = nullptr;
     g.peers.arena[rank] = g.arena;
@@ -603,6 +668,16 @@ int kleos_debug_routing(int32_t* topk, int32_t* slots, uint32_t* counts, float* 
     if (counts) KLEOS_CUDA(cudaMemcpy(counts, g.counts, (size_t)c.E * 4, cudaMemcpyDeviceToHost));
     if (mcw) KLEOS_CUDA(cudaMemcpy(mcw, g.mcw, (size_t)c.S * 4, cudaMemcpyDeviceToHost));
     return KLEOS_OK;
+}
+
+int kleos_debug_gemm_stats(long long* out, int max_values) {
+    if (!g.initialised) return fail(KLEOS_E_STATE, "not initialised");
+    if (!g.gemm_stats) return fail(KLEOS_E_STATE, "set KLEOS_GEMM_STATS=1 before kleos_initialize");
+    const int n = 2 * g.sm_count * 8;
+    if (!out || max_values < n) return fail(KLEOS_E_ARG, "need room for %d values", n);
+    KLEOS_CUDA(cudaStreamSynchronize(cudaStreamPerThread));
+    KLEOS_CUDA(cudaMemcpy(out, g.gemm_stats, sizeof(long long) * n, cudaMemcpyDeviceToHost));
+    return n;
 }
 
 int kleos_phase_times(float* ms, int n) {

@@ -22,6 +22,8 @@ struct RouteArgs {
     float* mcw;           // [S]
     int* refine_list;     // token ids needing fp64 re-evaluation
     int* refine_count;
+    double* refine_logits;  // [S,E] fp64 logits of listed tokens
+    int* refine_done;       // [S] per listed token: logits finished (zero between forwards)
     int S, H, E, K, PX;
     float tie_eps;
 };
@@ -169,56 +171,77 @@ constexpr size_t route_smem_bytes() {
     return k_loop > epi ? k_loop : epi;
 }
 
-// fp64 re-evaluation of the tokens on the refine list: one block per listed token.
+// fp64 re-evaluation of the tokens on the refine list.  One warp per (listed token, expert)
+// dot product; the warp that completes a token's last logit redoes that token's selection.
 template <typename T>
-__global__ void __launch_bounds__(128) refine_kernel(RouteArgs a) {
-    extern __shared__ double l64[];  // [E]
+__global__ void __launch_bounds__(256) refine_kernel(RouteArgs a) {
+    constexpr int VEC = 16 / sizeof(T);
     const T* A = static_cast<const T*>(a.A);
     const T* Wg = static_cast<const T*>(a.Wg);
     const int n = *a.refine_count;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int i = blockIdx.x; i < n; i += gridDim.x) {
+    const int lane = threadIdx.x & 31;
+    const int warps = gridDim.x * (blockDim.x >> 5);
+    for (int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); item < n * a.E;
+         item += warps) {
+        const int i = item / a.E, e = item - i * a.E;
         const int t = a.refine_list[i];
-        for (int e = warp; e < a.E; e += 4) {
-            double s = 0.0;
-            for (int h = lane; h < a.H; h += 32)
-                s += (double)Elem<T>::to_f(A[(size_t)t * a.H + h]) *
-                     (double)Elem<T>::to_f(Wg[(size_t)e * a.H + h]);
+        const T* x = A + (size_t)t * a.H;
+        const T* w = Wg + (size_t)e * a.H;
+        double s = 0.0;
+#pragma unroll 4
+        for (int h = lane * VEC; h < a.H; h += 32 * VEC) {
+            const uint4 xr = *reinterpret_cast<const uint4*>(x + h);
+            const uint4 wr = *reinterpret_cast<const uint4*>(w + h);
+            const T* xv = reinterpret_cast<const T*>(&xr);
+            const T* wv = reinterpret_cast<const T*>(&wr);
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-            if (lane == 0) l64[e] = s + (double)a.bias[e];
+            for (int q = 0; q < VEC; ++q)
+                s += (double)Elem<T>::to_f(xv[q]) * (double)Elem<T>::to_f(wv[q]);
         }
-        __syncthreads();
-        if (threadIdx.x == 0) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        int done = 0;
+        if (lane == 0) {
+            a.refine_logits[(size_t)i * a.E + e] = s + (double)a.bias[e];
+            __threadfence();
+            done = atomicAdd(a.refine_done + i, 1);
+        }
+        done = __shfl_sync(0xffffffffu, done, 0);
+        if (done != a.E - 1) continue;
+        // last logit of token i: select on the fp64 logits, ties to the lowest expert id
+        if (lane == 0) {
+            __threadfence();
+            const volatile double* l64 = a.refine_logits + (size_t)i * a.E;
             int sel[kMaxTopK];
             for (int j = 0; j < a.K; ++j) {
                 int best = 0;
                 double bv = -INFINITY;
-                for (int e = 0; e < a.E; ++e) {
+                for (int ee = 0; ee < a.E; ++ee) {
                     bool taken = false;
-                    for (int q = 0; q < j; ++q) taken |= (sel[q] == e);
-                    if (!taken && l64[e] > bv) {
-                        bv = l64[e];
-                        best = e;
+                    for (int q = 0; q < j; ++q) taken |= (sel[q] == ee);
+                    const double v = l64[ee];
+                    if (!taken && v > bv) {
+                        bv = v;
+                        best = ee;
                     }
                 }
                 sel[j] = best;
             }
             float m = -INFINITY;
-            for (int e = 0; e < a.E; ++e) m = fmaxf(m, (float)l64[e]);
+            for (int ee = 0; ee < a.E; ++ee) m = fmaxf(m, (float)l64[ee]);
             float d = 0.f;
-            for (int e = 0; e < a.E; ++e) d += __expf((float)l64[e] - m);
-            float w = 0.f;
+            for (int ee = 0; ee < a.E; ++ee) d += __expf((float)l64[ee] - m);
+            float wsum = 0.f;
             for (int j = 0; j < a.K; ++j) {
                 a.topk[(size_t)t * a.K + j] = sel[j];
-                w += __expf((float)l64[sel[j]] - m) / d;
+                wsum += __expf((float)l64[sel[j]] - m) / d;
             }
-            a.mcw[t] = w;
+            a.mcw[t] = wsum;
             T* probs = static_cast<T*>(a.probs);
-            for (int e = 0; e < a.E; ++e)
-                probs[(size_t)t * a.PX + e] = Elem<T>::from_f(__expf((float)l64[e] - m) / d);
+            for (int ee = 0; ee < a.E; ++ee)
+                probs[(size_t)t * a.PX + ee] = Elem<T>::from_f(__expf((float)l64[ee] - m) / d);
+            a.refine_done[i] = 0;  // ready for the next forward
         }
-        __syncthreads();
     }
 }
 

@@ -1,0 +1,192 @@
+// Router on the tensor cores (bf16 layers): gate GEMM with the whole padded expert dimension
+// as one tcgen05 N extent, softmax + top-k in the accumulator read-back.
+//
+// One block per 128 tokens.  The accumulator is 128 lanes x PX fp32 columns of tensor memory,
+// so every epilogue thread owns one token's full logit row and no cross-block exchange is
+// needed; the reference needs a ring of mailboxes between column-tile blocks once E > 64
+// (moe/gate.cuh:93-468).  Selection rules are those of route.cuh / moe/gate.cuh:556-718.
+#pragma once
+
+#include "route.cuh"
+#include "tc_common.cuh"
+
+namespace kleos {
+namespace route_tc {
+
+constexpr int BM = 128, BK = 64, UMMA_K = 16, MAX_STAGES = 6;
+constexpr int A_STAGE_BYTES = BM * BK * 2;
+
+template <int PXT>
+struct Shape {
+    static constexpr int STAGES = PXT <= 64 ? 6 : 4;  // what fits beside the logit tile
+    static constexpr int B_STAGE_BYTES = PXT * BK * 2;
+    static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+    static constexpr int LDL = PXT + 1;
+    static constexpr int LOGIT_BYTES = BM * LDL * 4 + 2 * BM * 4;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + LOGIT_BYTES + 1024 + 256;
+};
+
+struct Control {
+    unsigned long long full[MAX_STAGES];
+    unsigned long long empty[MAX_STAGES];
+    unsigned long long acc_full;
+    uint32_t tmem_base;
+    int abort;
+};
+
+}  // namespace route_tc
+
+template <int PXT>
+__global__ void __launch_bounds__(256, 1)
+route_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_wg,
+                RouteArgs a, DeviceStatus* status, long long wait_cycles, int epoch) {
+    using namespace tc;
+    using namespace route_tc;
+    using Sh = Shape<PXT>;
+    constexpr int STAGES = Sh::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* tiles = reinterpret_cast<uint8_t*>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    float* Ls = reinterpret_cast<float*>(tiles + STAGES * Sh::STAGE_BYTES);  // [BM][LDL]
+    float* rowmax = Ls + BM * Sh::LDL;
+    float* rowden = rowmax + BM;
+    Control* ctl = reinterpret_cast<Control*>(rowden + BM);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    volatile int* abort_flag = &ctl->abort;
+    const int row0 = blockIdx.x * BM;
+    const int KB = a.H / BK;
+    constexpr uint32_t idesc = make_instr_desc_bf16(BM, PXT);
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&ctl->full[s], 1);
+            mbar_init(&ctl->empty[s], 1);
+        }
+        mbar_init(&ctl->acc_full, 1);
+        ctl->abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 2) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&ctl->tmem_base)), "r"(PXT)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = ctl->tmem_base;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int kb = 0; kb < KB; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t ph = (kb / STAGES) & 1;
+                if (!mbar_wait(&ctl->empty[s], ph ^ 1, wait_cycles, abort_flag)) {
+                    report_error(status, KLEOS_AT_GEMM_PRODUCER, blockIdx.x, epoch);
+                    *abort_flag = 1;
+                    break;
+                }
+                mbar_expect_tx(&ctl->full[s], Sh::STAGE_BYTES);
+                uint8_t* sa = tiles + s * Sh::STAGE_BYTES;
+                tma_load_2d(sa, &map_a, kb * BK, row0, &ctl->full[s]);
+                tma_load_2d(sa + A_STAGE_BYTES, &map_wg, kb * BK, 0, &ctl->full[s]);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            bool ok = true;
+            for (int kb = 0; kb < KB; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t ph = (kb / STAGES) & 1;
+                if (!mbar_wait(&ctl->full[s], ph, wait_cycles, abort_flag)) {
+                    report_error(status, KLEOS_AT_GEMM_MMA, blockIdx.x, epoch);
+                    *abort_flag = 1;
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t sa = smem_u32(tiles + s * Sh::STAGE_BYTES);
+                const uint64_t da = make_smem_desc(sa);
+                const uint64_t db = make_smem_desc(sa + A_STAGE_BYTES);
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k)
+                    umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                umma_commit(&ctl->empty[s]);
+            }
+            if (ok) umma_commit(&ctl->acc_full);
+        }
+        __syncwarp();
+    } else if (warp >= 4) {
+        const int q = warp - 4;
+        const int r = q * 32 + lane;  // token row inside the tile = accumulator lane
+        bool ok = mbar_wait(&ctl->acc_full, 0, wait_cycles, abort_flag);
+        if (!ok) {
+            if (lane == 0) report_error(status, KLEOS_AT_GEMM_EPILOGUE, blockIdx.x, epoch);
+            *abort_flag = 1;
+        }
+        tc_fence_after();
+        if (ok) {
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < PXT / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld_32x32(taddr + c * 32, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const int e = c * 32 + j;
+                    Ls[r * Sh::LDL + e] = __uint_as_float(v[j]) + (e < a.E ? a.bias[e] : 0.f);
+                }
+            }
+            tc_fence_before();
+            if (row0 + r < a.S) {
+                const float* l = Ls + r * Sh::LDL;
+                float m = -INFINITY;
+                for (int e = 0; e < a.E; ++e) m = fmaxf(m, l[e]);
+                float d = 0.f;
+                for (int e = 0; e < a.E; ++e) d += __expf(l[e] - m);
+                rowmax[r] = m;
+                rowden[r] = d;
+                int sel[kMaxTopK];
+                float kth;
+                const float margin = select_topk_row(l, a.E, a.K, sel, &kth);
+                float w = 0.f;
+                for (int j = 0; j < a.K; ++j) {
+                    a.topk[(size_t)(row0 + r) * a.K + j] = sel[j];
+                    w += __expf(l[sel[j]] - m) / d;
+                }
+                a.mcw[row0 + r] = w;
+                if (a.K < a.E && margin < a.tie_eps * fmaxf(1.f, fabsf(kth))) {
+                    const int pos = atomicAdd(a.refine_count, 1);
+                    a.refine_list[pos] = row0 + r;
+                }
+            }
+        }
+        // the four epilogue warps share the logit tile: meet before the coalesced store
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (ok && !*abort_flag) {
+            __nv_bfloat16* probs = static_cast<__nv_bfloat16*>(a.probs);
+            const int et = tid - 128;
+            for (int idx = et; idx < BM * a.PX; idx += 128) {
+                const int rr = idx / a.PX, e = idx - rr * a.PX;
+                if (row0 + rr >= a.S) break;
+                float p = 0.f;
+                if (e < a.E) p = __expf(Ls[rr * Sh::LDL + e] - rowmax[rr]) / rowden[rr];
+                probs[(size_t)(row0 + rr) * a.PX + e] = __float2bfloat16_rn(p);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 2) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                     "r"(PXT)
+                     : "memory");
+    }
+}
+
+}  // namespace kleos

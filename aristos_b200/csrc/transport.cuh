@@ -163,8 +163,10 @@ struct CombineArgs {
 
 // out[t] = sum_j Element(prob[t,e_j]) * Element(y2[e_j][slot_j] / mCw[t]) over kept choices
 // (reference processor.cuh:110-168); with k == 1 the row is copied unscaled (:170-204).
-// Rows of tokens whose every choice was dropped are written as zeros.  Warp per token.
-template <typename T>
+// Rows of tokens whose every choice was dropped are written as zeros.  Warp per token; KT is
+// the compile-time top-k (0 = read it from the arguments), which lets the k row loads of
+// several 16-byte chunks be issued together.
+template <typename T, int KT>
 __global__ void __launch_bounds__(256) combine_kernel(CombineArgs a) {
     __shared__ int failed;
     if (threadIdx.x == 0) failed = 0;
@@ -182,50 +184,66 @@ __global__ void __launch_bounds__(256) combine_kernel(CombineArgs a) {
     if (failed) return;
 
     constexpr int VEC = 16 / sizeof(T);
+    constexpr int KMAX = KT > 0 ? KT : kMaxTopK;
+    constexpr int UNR = KT > 0 && KT <= 2 ? 4 : 1;
+    const int K = KT > 0 ? KT : a.K;
     const int lane = threadIdx.x & 31;
     const int warps = gridDim.x * (blockDim.x >> 5);
     const T* probs = static_cast<const T*>(a.probs);
-    const char* ycell = a.arena + a.lay.ycell;
+    const T* ycell = reinterpret_cast<const T*>(a.arena + a.lay.ycell);
     const int chunks = a.H / VEC;
     for (int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); t < a.S; t += warps) {
-        int e[kMaxTopK], sl[kMaxTopK];
-        float p[kMaxTopK];
+        const T* yrow[KMAX];
+        float p[KMAX];
 #pragma unroll
-        for (int j = 0; j < kMaxTopK; ++j)
-            if (j < a.K) {
-                e[j] = a.topk[(size_t)t * a.K + j];
-                sl[j] = a.slots[(size_t)t * a.K + j];
-                p[j] = Elem<T>::to_f(probs[(size_t)t * a.PX + e[j]]);
+        for (int j = 0; j < KMAX; ++j) {
+            yrow[j] = nullptr;
+            p[j] = 0.f;
+            if (j < K) {
+                const int e = a.topk[(size_t)t * K + j];
+                const int sl = a.slots[(size_t)t * K + j];
+                p[j] = Elem<T>::to_f(probs[(size_t)t * a.PX + e]);
+                if (sl != kDropped) yrow[j] = ycell + ((size_t)e * a.pEC + sl) * a.H;
             }
+        }
         const float w = a.mcw[t];
         T* orow = static_cast<T*>(a.out) + (size_t)t * a.H;
-        for (int c = lane; c < chunks; c += 32) {
-            float acc[VEC];
+        for (int c0 = lane; c0 < chunks; c0 += 32 * UNR) {
+            uint4 raw[UNR][KMAX];
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
+            for (int u = 0; u < UNR; ++u)
 #pragma unroll
-            for (int j = 0; j < kMaxTopK; ++j)
-                if (j < a.K && sl[j] != kDropped) {
-                    const T* yrow = reinterpret_cast<const T*>(ycell) +
-                                    ((size_t)e[j] * a.pEC + sl[j]) * a.H;
-                    const uint4 raw = ld_cg_v4(yrow + (size_t)c * VEC);
-                    const T* yv = reinterpret_cast<const T*>(&raw);
+                for (int j = 0; j < KMAX; ++j)
+                    if (j < K && yrow[j] != nullptr && c0 + 32 * u < chunks)
+                        raw[u][j] = ld_cg_v4(yrow[j] + (size_t)(c0 + 32 * u) * VEC);
 #pragma unroll
-                    for (int i = 0; i < VEC; ++i) {
-                        if (a.K > 1) {
-                            const float v = Elem<T>::round(Elem<T>::to_f(yv[i]) / w);
-                            const float s = Elem<T>::round(p[j] * v);
-                            acc[i] = Elem<T>::round(acc[i] + s);
-                        } else {
-                            acc[i] = Elem<T>::to_f(yv[i]);
+            for (int u = 0; u < UNR; ++u) {
+                const int c = c0 + 32 * u;
+                if (c >= chunks) break;
+                float acc[VEC];
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
+#pragma unroll
+                for (int j = 0; j < KMAX; ++j)
+                    if (j < K && yrow[j] != nullptr) {
+                        const T* yv = reinterpret_cast<const T*>(&raw[u][j]);
+#pragma unroll
+                        for (int i = 0; i < VEC; ++i) {
+                            if (K > 1) {
+                                const float v = Elem<T>::round(Elem<T>::to_f(yv[i]) / w);
+                                const float sc = Elem<T>::round(p[j] * v);
+                                acc[i] = Elem<T>::round(acc[i] + sc);
+                            } else {
+                                acc[i] = Elem<T>::to_f(yv[i]);
+                            }
                         }
                     }
-                }
-            uint4 o;
-            T* ov = reinterpret_cast<T*>(&o);
+                uint4 o;
+                T* ov = reinterpret_cast<T*>(&o);
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) ov[i] = Elem<T>::from_f(acc[i]);
-            *reinterpret_cast<uint4*>(orow + (size_t)c * VEC) = o;
+                for (int i = 0; i < VEC; ++i) ov[i] = Elem<T>::from_f(acc[i]);
+                *reinterpret_cast<uint4*>(orow + (size_t)c * VEC) = o;
+            }
         }
     }
 }

@@ -26,7 +26,7 @@ EXPORTS = (
     "kleos_get_unique_id", "kleos_config_probe", "kleos_set_device", "kleos_initialize", "kleos_set_gate_bias",
     "kleos_forward", "kleos_forward_bench", "kleos_forward_host", "kleos_get_rank",
     "kleos_local_experts", "kleos_get_info", "kleos_last_status", "kleos_debug_routing",
-    "kleos_phase_times", "kleos_finalize", "kleos_error_string",
+    "kleos_phase_times", "kleos_debug_gemm_stats", "kleos_finalize", "kleos_error_string",
 )
 
 PHASE_NAMES = ("route", "slots", "dispatch", "plan", "gemm1", "gemm2", "combine", "total")
@@ -169,6 +169,16 @@ def phase_times() -> dict:
     arr = (ctypes.c_float * 8)()
     _check(load_library().kleos_phase_times(arr, 8), "kleos_phase_times")
     return dict(zip(PHASE_NAMES, [float(v) for v in arr]))
+
+
+def gemm_stats():
+    """Per-block stall counters of the last two GEMM launches (needs KLEOS_GEMM_STATS=1)."""
+    import numpy as np
+    buf = np.zeros(2 * 256 * 8, dtype=np.int64)
+    n = load_library().kleos_debug_gemm_stats(buf.ctypes.data_as(ctypes.c_void_p), buf.size)
+    if n < 0:
+        _check(n, "kleos_debug_gemm_stats")
+    return buf[:n].reshape(2, -1, 8)
 
 
 def last_status() -> Status:

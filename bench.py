@@ -31,6 +31,20 @@ METRIC = "moe_layer_fwd_tokens_per_s"
 KERNELS_PER_FORWARD = 8  # route, refine, slots, dispatch, plan, GEMM1, GEMM2, combine
 
 
+def workload(name: str):
+    """(config, description).  C3 is the benchmark layer the headline metric is quoted on; C3q is
+    the same layer at a quarter of the tokens and experts (same tile shapes, about 0.4 GB on
+    the device) and exists so that profiler captures stay small."""
+    from aristos_b200.config import KleosConfig
+    if name == "C3q":
+        return (KleosConfig(sequence_len=2048, hidden_size=2048, intermediate_size=2048,
+                            num_experts=16, torch_dtype=2),
+                "C3q: S=2048 tokens/rank, H=I=2048, E=16, top-2, CF=1, bf16 (profiling size)")
+    cfg, _ = baseline_config(name)
+    return cfg, (f"{name}: S={cfg.S} tokens/rank, H={cfg.H}, I={cfg.I}, E={cfg.E}, "
+                 f"top-{cfg.K}, CF={cfg.capacity_factor}, {cfg.dtype_name}")
+
+
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -202,7 +216,9 @@ def run_cuda(args):
         dist.broadcast(idt, 0)
         uid = bytes(idt.cpu().numpy().tobytes())
 
-    cfg, _ = baseline_config("C3")
+    cfg, workload_desc = workload(args.workload)
+    if cfg.torch_dtype != 2:
+        raise SystemExit("bench.py drives the bf16 layers")
     kleos.set_device(local_rank)
     info = kleos.initialize(cfg, rank, world, uid)
     iP = synth_on_device(cfg, rank, world, device)
@@ -285,7 +301,7 @@ def run_cuda(args):
             steps=args.steps, warmup=args.warmup, ms_per_step=ms_per_step,
             higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16",
             data="synthetic",
-            config=dict(workload="C3: S=8192 tokens/rank, H=I=2048, E=64, top-2, CF=1, bf16",
+            config=dict(workload=workload_desc,
                         experts_per_rank=info.local_experts, parallelism=f"ep{world}",
                         l2="working set per step (weights + cells + activations) exceeds L2"),
             e2e=dict(value=tokens * args.steps / e2e_s, unit="tokens/s",
@@ -303,11 +319,12 @@ def run_cuda(args):
         )
         if args.cpu_baseline and world == 1:
             views = host_views_from_device(cfg, iP, world)
-            v, dt, threads = cpu_sample_tokens_per_s(cfg, views, args.cpu_sample)
+            sample = min(args.cpu_sample, cfg.S)
+            v, dt, threads = cpu_sample_tokens_per_s(cfg, views, sample)
             line["cpu_baseline"] = dict(
                 value=v, unit="tokens/s", cores=threads, kind="port",
-                sample=f"first {args.cpu_sample} of 8192 tokens of rank 0 through all 64 experts "
-                       f"(routing over all 8192 tokens), fp32 accumulation, {dt:.1f} s")
+                sample=f"first {sample} of {cfg.S} tokens of rank 0 through all {cfg.E} experts "
+                       f"(routing over all {cfg.S} tokens), fp32 accumulation, {dt:.1f} s")
         print(json.dumps(line), flush=True)
     kleos.finalize()
     if world > 1:
@@ -320,6 +337,7 @@ def main():
     ap.add_argument("--steps", type=int, default=32)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
+    ap.add_argument("--workload", default="C3", help="C3 (default), C3q (profiling size), C5")
     ap.add_argument("--cpu-sample", type=int, default=0,
                     help="tokens in the CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")

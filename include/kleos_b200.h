@@ -120,6 +120,13 @@ int kleos_debug_routing(int32_t* topk, int32_t* slots, uint32_t* counts, float* 
  * [6] combine, [7] whole forward.  n = number of floats the caller provides (>= 8). */
 int kleos_phase_times(float* ms, int n);
 
+/* Stall counters of the last GEMM1 and GEMM2 launches, only when the environment variable
+ * KLEOS_GEMM_STATS=1 was set at initialise time: [2][blocks][8] clock cycles per block
+ * {producer wait-empty, producer total, MMA wait-accumulator, MMA wait-operands, MMA total,
+ *  epilogue wait-accumulator, epilogue total, unused}.  Returns the number of values written.
+ * A tuning aid with no counterpart in the reference. */
+int kleos_debug_gemm_stats(long long* out, int max_values);
+
 /* Free everything.  Replaces kleos::finalize() (bootstrap.cuh:561-588). */
 int kleos_finalize(void);
 
