@@ -11,6 +11,7 @@
 #include <dlfcn.h>
 #include <nccl.h>
 
+#include <algorithm>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -157,7 +158,8 @@ EncodeTiledFn g_encode = nullptr;
 
 // bf16 matrix [rows][cols] with cols contiguous; box = 64 columns x box_rows rows, 128-byte
 // swizzle (64 bf16 = 128 bytes, the swizzle span).
-int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+             uint32_t box_cols = 64, bool swizzle = true) {
     if (!g_encode) {
         void* fn = nullptr;
         cudaDriverEntryPointQueryResult q;
@@ -168,11 +170,12 @@ int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, u
     }
     const cuuint64_t dims[2] = {cols, rows};
     const cuuint64_t strides[1] = {cols * 2};
-    const cuuint32_t box[2] = {64, box_rows};
+    const cuuint32_t box[2] = {box_cols, box_rows};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base),
                                 dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(KLEOS_E_CUDA, "cuTensorMapEncodeTiled failed: %d", (int)r);
     return KLEOS_OK;

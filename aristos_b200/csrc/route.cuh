@@ -28,33 +28,62 @@ struct RouteArgs {
     float tie_eps;
 };
 
-// Softmax + top-k for one token from fp32 logits held in shared memory (stride ld).
-// Returns the margin between the k-th and (k+1)-th logit.
-__device__ __forceinline__ float select_topk_row(const float* l, int E, int K, int* sel,
-                                                  float* kth_val) {
-    float kth = 0.f;
-    for (int j = 0; j < K; ++j) {
-        int best = 0;
-        float bv = -INFINITY;
-        for (int e = 0; e < E; ++e) {
-            bool taken = false;
-            for (int q = 0; q < j; ++q) taken |= (sel[q] == e);
-            if (!taken && l[e] > bv) {
-                bv = l[e];
-                best = e;
+// One token's routing decision from its fp32 logits (in shared memory):
+// a single ascending pass keeps the K+1 largest logits in order (strict '>' on insertion, so
+// equal values keep the lower expert id in front -- the reference's tie rule,
+// moe/gate.cuh:662-667), a second pass sums the exponentials.  Writes top-k ids and the sum of
+// the k winning probabilities, and returns the softmax statistics and the k-th / (k+1)-th
+// margin used to decide whether the token needs the fp64 re-evaluation.
+struct RowDecision {
+    float max, inv_den, kth, margin;
+};
+
+__device__ __forceinline__ RowDecision decide_row(const float* l, int E, int K, int* topk_out,
+                                                  float* mcw_out) {
+    float val[kMaxTopK + 1];
+    int idx[kMaxTopK + 1];
+#pragma unroll
+    for (int j = 0; j <= kMaxTopK; ++j) {
+        val[j] = -INFINITY;
+        idx[j] = 0;
+    }
+    for (int e = 0; e < E; ++e) {
+        float v = l[e];
+        int id = e;
+#pragma unroll
+        for (int j = 0; j <= kMaxTopK; ++j) {
+            if (j <= K && v > val[j]) {
+                const float tv = val[j];
+                const int ti = idx[j];
+                val[j] = v;
+                idx[j] = id;
+                v = tv;
+                id = ti;
             }
         }
-        sel[j] = best;
-        kth = bv;
     }
-    float next = -INFINITY;
-    for (int e = 0; e < E; ++e) {
-        bool taken = false;
-        for (int q = 0; q < K; ++q) taken |= (sel[q] == e);
-        if (!taken && l[e] > next) next = l[e];
+    const float m = val[0];
+    float d = 0.f;
+    for (int e = 0; e < E; ++e) d += __expf(l[e] - m);
+    const float inv = 1.f / d;
+    float w = 0.f, kth = 0.f, next = -INFINITY;
+#pragma unroll
+    for (int j = 0; j <= kMaxTopK; ++j) {
+        if (j < K) {
+            topk_out[j] = idx[j];
+            w += __expf(val[j] - m) * inv;
+            kth = val[j];
+        } else if (j == K) {
+            next = val[j];
+        }
     }
-    *kth_val = kth;
-    return kth - next;
+    *mcw_out = w;
+    RowDecision r;
+    r.max = m;
+    r.inv_den = inv;
+    r.kth = kth;
+    r.margin = (K < E) ? kth - next : INFINITY;
+    return r;
 }
 
 // One block = 64 tokens x PXT experts, 256 threads, each thread a 4 x (PXT/16) register tile.
@@ -130,36 +159,24 @@ __global__ void __launch_bounds__(256) route_kernel(RouteArgs a) {
 
     // one thread per token: softmax statistics, top-k, near-tie detection
     if (tid < BM && row0 + tid < a.S) {
-        const float* l = Ls + tid * LDL;
-        float m = -INFINITY;
-        for (int e = 0; e < a.E; ++e) m = fmaxf(m, l[e]);
-        float d = 0.f;
-        for (int e = 0; e < a.E; ++e) d += __expf(l[e] - m);
-        rowmax[tid] = m;
-        rowden[tid] = d;
-        int sel[kMaxTopK];
-        float kth;
-        const float margin = select_topk_row(l, a.E, a.K, sel, &kth);
-        float w = 0.f;
-        for (int j = 0; j < a.K; ++j) {
-            a.topk[(size_t)(row0 + tid) * a.K + j] = sel[j];
-            w += __expf(l[sel[j]] - m) / d;
-        }
-        a.mcw[row0 + tid] = w;
-        if (a.K < a.E && margin < a.tie_eps * fmaxf(1.f, fabsf(kth))) {
+        const RowDecision r = decide_row(Ls + tid * LDL, a.E, a.K,
+                                         a.topk + (size_t)(row0 + tid) * a.K, a.mcw + row0 + tid);
+        rowmax[tid] = r.max;
+        rowden[tid] = r.inv_den;
+        if (r.margin < a.tie_eps * fmaxf(1.f, fabsf(r.kth))) {
             const int pos = atomicAdd(a.refine_count, 1);
             a.refine_list[pos] = row0 + tid;  // list has room for every token
         }
     }
     __syncthreads();
-    // probabilities, coalesced, padding columns zero
+    // probabilities, coalesced, padding columns zero (PX == PXT: both are E rounded up to 64)
     T* probs = static_cast<T*>(a.probs);
-    for (int idx = tid; idx < BM * a.PX; idx += 256) {
-        const int r = idx / a.PX, e = idx - r * a.PX;
+    for (int idx = tid; idx < BM * PXT; idx += 256) {
+        const int r = idx / PXT, e = idx % PXT;
         if (row0 + r >= a.S) break;
         float p = 0.f;
-        if (e < a.E) p = __expf(Ls[r * LDL + e] - rowmax[r]) / rowden[r];
-        probs[(size_t)(row0 + r) * a.PX + e] = Elem<T>::from_f(p);
+        if (e < a.E) p = __expf(Ls[r * LDL + e] - rowmax[r]) * rowden[r];
+        probs[(size_t)(row0 + r) * PXT + e] = Elem<T>::from_f(p);
     }
 }
 
@@ -208,39 +225,68 @@ __global__ void __launch_bounds__(256) refine_kernel(RouteArgs a) {
         }
         done = __shfl_sync(0xffffffffu, done, 0);
         if (done != a.E - 1) continue;
-        // last logit of token i: select on the fp64 logits, ties to the lowest expert id
-        if (lane == 0) {
-            __threadfence();
-            const volatile double* l64 = a.refine_logits + (size_t)i * a.E;
-            int sel[kMaxTopK];
-            for (int j = 0; j < a.K; ++j) {
-                int best = 0;
-                double bv = -INFINITY;
-                for (int ee = 0; ee < a.E; ++ee) {
-                    bool taken = false;
-                    for (int q = 0; q < j; ++q) taken |= (sel[q] == ee);
-                    const double v = l64[ee];
-                    if (!taken && v > bv) {
-                        bv = v;
-                        best = ee;
-                    }
+        // last logit of token i: the whole warp redoes the selection on the fp64 logits
+        // (k rounds of warp arg-max, ties to the lowest expert id) and the fp32 softmax
+        __threadfence();
+        constexpr int PER_LANE = 8;  // E <= 256
+        const double* l64 = a.refine_logits + (size_t)i * a.E;
+        double cand[PER_LANE];
+        float lf[PER_LANE];
+#pragma unroll
+        for (int q = 0; q < PER_LANE; ++q) {
+            const int ee = lane + 32 * q;
+            cand[q] = ee < a.E ? __ldcg(l64 + ee) : -INFINITY;
+            lf[q] = (float)cand[q];
+        }
+        float m = -INFINITY;
+#pragma unroll
+        for (int q = 0; q < PER_LANE; ++q) m = fmaxf(m, lf[q]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        float d = 0.f;
+#pragma unroll
+        for (int q = 0; q < PER_LANE; ++q)
+            if (lane + 32 * q < a.E) d += __expf(lf[q] - m);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+        const float inv = 1.f / d;
+        float wsum = 0.f;
+        for (int j = 0; j < a.K; ++j) {
+            double bv = -INFINITY;
+            int be = 0x7fffffff;
+#pragma unroll
+            for (int q = 0; q < PER_LANE; ++q) {
+                const int ee = lane + 32 * q;  // ascending per lane, so '>' keeps the lower id
+                if (cand[q] > bv) {
+                    bv = cand[q];
+                    be = ee;
                 }
-                sel[j] = best;
             }
-            float m = -INFINITY;
-            for (int ee = 0; ee < a.E; ++ee) m = fmaxf(m, (float)l64[ee]);
-            float d = 0.f;
-            for (int ee = 0; ee < a.E; ++ee) d += __expf((float)l64[ee] - m);
-            float wsum = 0.f;
-            for (int j = 0; j < a.K; ++j) {
-                a.topk[(size_t)t * a.K + j] = sel[j];
-                wsum += __expf((float)l64[sel[j]] - m) / d;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const double ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+                if (ov > bv || (ov == bv && oe < be)) {
+                    bv = ov;
+                    be = oe;
+                }
             }
+            // every lane now agrees on (bv, be); its owner retires the candidate
+#pragma unroll
+            for (int q = 0; q < PER_LANE; ++q)
+                if (lane + 32 * q == be) cand[q] = -INFINITY;
+            if (lane == 0) a.topk[(size_t)t * a.K + j] = be;
+            wsum += __expf((float)bv - m) * inv;
+        }
+        if (lane == 0) {
             a.mcw[t] = wsum;
-            T* probs = static_cast<T*>(a.probs);
-            for (int ee = 0; ee < a.E; ++ee)
-                probs[(size_t)t * a.PX + ee] = Elem<T>::from_f(__expf((float)l64[ee] - m) / d);
             a.refine_done[i] = 0;  // ready for the next forward
+        }
+        T* probs = static_cast<T*>(a.probs);
+#pragma unroll
+        for (int q = 0; q < PER_LANE; ++q) {
+            const int ee = lane + 32 * q;
+            if (ee < a.E) probs[(size_t)t * a.PX + ee] = Elem<T>::from_f(__expf(lf[q] - m) * inv);
         }
     }
 }

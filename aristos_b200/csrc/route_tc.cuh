@@ -143,23 +143,12 @@ route_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             }
             tc_fence_before();
             if (row0 + r < a.S) {
-                const float* l = Ls + r * Sh::LDL;
-                float m = -INFINITY;
-                for (int e = 0; e < a.E; ++e) m = fmaxf(m, l[e]);
-                float d = 0.f;
-                for (int e = 0; e < a.E; ++e) d += __expf(l[e] - m);
-                rowmax[r] = m;
-                rowden[r] = d;
-                int sel[kMaxTopK];
-                float kth;
-                const float margin = select_topk_row(l, a.E, a.K, sel, &kth);
-                float w = 0.f;
-                for (int j = 0; j < a.K; ++j) {
-                    a.topk[(size_t)(row0 + r) * a.K + j] = sel[j];
-                    w += __expf(l[sel[j]] - m) / d;
-                }
-                a.mcw[row0 + r] = w;
-                if (a.K < a.E && margin < a.tie_eps * fmaxf(1.f, fabsf(kth))) {
+                const RowDecision d = decide_row(Ls + r * Sh::LDL, a.E, a.K,
+                                                 a.topk + (size_t)(row0 + r) * a.K,
+                                                 a.mcw + row0 + r);
+                rowmax[r] = d.max;
+                rowden[r] = d.inv_den;
+                if (d.margin < a.tie_eps * fmaxf(1.f, fabsf(d.kth))) {
                     const int pos = atomicAdd(a.refine_count, 1);
                     a.refine_list[pos] = row0 + r;
                 }
@@ -170,12 +159,15 @@ route_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         if (ok && !*abort_flag) {
             __nv_bfloat16* probs = static_cast<__nv_bfloat16*>(a.probs);
             const int et = tid - 128;
-            for (int idx = et; idx < BM * a.PX; idx += 128) {
-                const int rr = idx / a.PX, e = idx - rr * a.PX;
+            // two adjacent probabilities per thread, 4-byte stores (PX == PXT)
+            for (int idx = 2 * et; idx < BM * PXT; idx += 256) {
+                const int rr = idx / PXT, e = idx % PXT;
                 if (row0 + rr >= a.S) break;
-                float p = 0.f;
-                if (e < a.E) p = __expf(Ls[rr * Sh::LDL + e] - rowmax[rr]) / rowden[rr];
-                probs[(size_t)(row0 + rr) * a.PX + e] = __float2bfloat16_rn(p);
+                const float m = rowmax[rr], inv = rowden[rr];
+                const float p0 = e < a.E ? __expf(Ls[rr * Sh::LDL + e] - m) * inv : 0.f;
+                const float p1 = e + 1 < a.E ? __expf(Ls[rr * Sh::LDL + e + 1] - m) * inv : 0.f;
+                *reinterpret_cast<__nv_bfloat162*>(probs + (size_t)(row0 + rr) * PXT + e) =
+                    __floats2bfloat162_rn(p0, p1);
             }
         }
     }

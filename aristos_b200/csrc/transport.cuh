@@ -207,6 +207,7 @@ __global__ void __launch_bounds__(256) combine_kernel(CombineArgs a) {
             }
         }
         const float w = a.mcw[t];
+        const float inv_w = 1.f / w;
         T* orow = static_cast<T*>(a.out) + (size_t)t * a.H;
         for (int c0 = lane; c0 < chunks; c0 += 32 * UNR) {
             uint4 raw[UNR][KMAX];
@@ -220,28 +221,55 @@ __global__ void __launch_bounds__(256) combine_kernel(CombineArgs a) {
             for (int u = 0; u < UNR; ++u) {
                 const int c = c0 + 32 * u;
                 if (c >= chunks) break;
-                float acc[VEC];
+                uint4 o;
+                if constexpr (sizeof(T) == 2) {
+                    // bf16: Element(y / mCw) is one fp32 multiply and a packed round; the product
+                    // with the bf16 probability and the running sum are single-rounding bf16x2
+                    // instructions, which is exactly the element-type arithmetic of the
+                    // reference's combine
+                    __nv_bfloat162 acc2[4];
 #pragma unroll
-                for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
+                    for (int i = 0; i < 4; ++i) acc2[i] = __floats2bfloat162_rn(0.f, 0.f);
 #pragma unroll
-                for (int j = 0; j < KMAX; ++j)
-                    if (j < K && yrow[j] != nullptr) {
-                        const T* yv = reinterpret_cast<const T*>(&raw[u][j]);
+                    for (int j = 0; j < KMAX; ++j)
+                        if (j < K && yrow[j] != nullptr) {
+                            const __nv_bfloat162* y2 = reinterpret_cast<const __nv_bfloat162*>(&raw[u][j]);
+                            const __nv_bfloat162 pj = __floats2bfloat162_rn(p[j], p[j]);
 #pragma unroll
-                        for (int i = 0; i < VEC; ++i) {
-                            if (K > 1) {
-                                const float v = Elem<T>::round(Elem<T>::to_f(yv[i]) / w);
-                                const float sc = Elem<T>::round(p[j] * v);
-                                acc[i] = Elem<T>::round(acc[i] + sc);
-                            } else {
-                                acc[i] = Elem<T>::to_f(yv[i]);
+                            for (int i = 0; i < 4; ++i) {
+                                if (K > 1) {
+                                    const float2 yf = __bfloat1622float2(y2[i]);
+                                    const __nv_bfloat162 v = __floats2bfloat162_rn(yf.x * inv_w, yf.y * inv_w);
+                                    acc2[i] = __hadd2(acc2[i], __hmul2(pj, v));
+                                } else {
+                                    acc2[i] = y2[i];
+                                }
                             }
                         }
-                    }
-                uint4 o;
-                T* ov = reinterpret_cast<T*>(&o);
+                    o = *reinterpret_cast<const uint4*>(acc2);
+                } else {
+                    float acc[VEC];
 #pragma unroll
-                for (int i = 0; i < VEC; ++i) ov[i] = Elem<T>::from_f(acc[i]);
+                    for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
+#pragma unroll
+                    for (int j = 0; j < KMAX; ++j)
+                        if (j < K && yrow[j] != nullptr) {
+                            const T* yv = reinterpret_cast<const T*>(&raw[u][j]);
+#pragma unroll
+                            for (int i = 0; i < VEC; ++i) {
+                                if (K > 1) {
+                                    const float v = Elem<T>::round(Elem<T>::to_f(yv[i]) / w);
+                                    const float sc = Elem<T>::round(p[j] * v);
+                                    acc[i] = Elem<T>::round(acc[i] + sc);
+                                } else {
+                                    acc[i] = Elem<T>::to_f(yv[i]);
+                                }
+                            }
+                        }
+                    T* ov = reinterpret_cast<T*>(&o);
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) ov[i] = Elem<T>::from_f(acc[i]);
+                }
                 *reinterpret_cast<uint4*>(orow + (size_t)c * VEC) = o;
             }
         }

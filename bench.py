@@ -40,6 +40,11 @@ def workload(name: str):
         return (KleosConfig(sequence_len=2048, hidden_size=2048, intermediate_size=2048,
                             num_experts=16, torch_dtype=2),
                 "C3q: S=2048 tokens/rank, H=I=2048, E=16, top-2, CF=1, bf16 (profiling size)")
+    if name == "C3r8":
+        # what ONE rank of the 8-rank C3 layer computes locally: 8 experts x 2048 routed rows
+        return (KleosConfig(sequence_len=8192, hidden_size=2048, intermediate_size=2048,
+                            num_experts=8, torch_dtype=2),
+                "C3r8: S=8192 tokens, H=I=2048, E=8, top-2, CF=1, bf16 (per-rank shape of C3 at 8 ranks)")
     cfg, _ = baseline_config(name)
     return cfg, (f"{name}: S={cfg.S} tokens/rank, H={cfg.H}, I={cfg.I}, E={cfg.E}, "
                  f"top-{cfg.K}, CF={cfg.capacity_factor}, {cfg.dtype_name}")
