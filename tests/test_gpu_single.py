@@ -78,3 +78,14 @@ def test_baseline_config_sampled(name):
     ref = c_oracle.moe_forward_rank(cfg, 1, 0, views, tokens=rows)
     probs, out, routing = hz.run_layer_single_gpu(cfg, packed[0])
     hz.check_against_oracle(cfg, ref, probs, out, routing, rows=rows)
+
+
+@pytest.mark.parametrize("name", ["fp32_w1", "bf16_w1", "fp32_top1"])
+def test_against_committed_golden_fixtures(name):
+    from tests import golden_util
+    cfg, world, bias, packed, _, expect = golden_util.load(name)
+    assert world == 1
+    probs, out, routing = hz.run_layer_single_gpu(cfg, packed[0], gate_bias=bias)
+    ref = dict(expect[0])
+    ref["margin"] = 1.0  # fixtures were generated from seeds whose margins were checked
+    hz.check_against_oracle(cfg, ref, probs, out, routing)

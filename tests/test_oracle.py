@@ -1,0 +1,90 @@
+"""The two CPU oracles against each other and against the committed golden fixtures."""
+import numpy as np
+import pytest
+
+from aristos_b200 import synth
+from aristos_b200.config import KleosConfig
+from oracle import c_oracle, moe_oracle
+from tests import golden_util
+
+
+def _agree(cfg, a, b, out_tol):
+    assert np.array_equal(a["topk"], b["topk"])
+    assert np.array_equal(a["slots"], b["slots"])
+    assert np.array_equal(a["counts"], b["counts"])
+    assert np.abs(a["mcw"] - b["mcw"]).max() <= 2e-6
+    assert np.abs(a["probs"] - b["probs"]).max() <= (2e-6 if cfg.torch_dtype == 0 else 4e-3)
+    denom = max(np.abs(b["out"]).max(), 1e-30)
+    assert np.abs(a["out"] - b["out"]).max() / denom <= out_tol
+
+
+@pytest.mark.parametrize("name", golden_util.names())
+def test_numpy_oracle_reproduces_golden(name):
+    cfg, world, bias, _, views, expect = golden_util.load(name)
+    got = moe_oracle.moe_forward(cfg, world, views, gate_bias=bias)
+    for r in range(world):
+        _agree(cfg, got[r], expect[r], 0.0 if cfg.torch_dtype == 2 else 1e-6)
+
+
+@pytest.mark.parametrize("name", golden_util.names())
+def test_c_oracle_matches_golden(name):
+    cfg, world, bias, _, views, expect = golden_util.load(name)
+    for r in range(world):
+        got = c_oracle.moe_forward_rank(cfg, world, r, views, gate_bias=bias)
+        # bf16: identical roundings; fp32: softmax summation order differs in the last ulp
+        _agree(cfg, got, expect[r], 4e-3 if cfg.torch_dtype == 2 else 1e-6)
+
+
+@pytest.mark.parametrize("dtype,world", [(0, 1), (2, 1), (2, 2), (0, 4)])
+def test_c_and_numpy_agree_on_fresh_inputs(dtype, world):
+    cfg = KleosConfig(sequence_len=128, hidden_size=128, intermediate_size=192, num_experts=8,
+                      torch_dtype=dtype)
+    views = [synth.split_packed(cfg, synth.packed_input(cfg, r, world, seed=3), world)
+             for r in range(world)]
+    ref = moe_oracle.moe_forward(cfg, world, views)
+    for r in range(world):
+        got = c_oracle.moe_forward_rank(cfg, world, r, views)
+        _agree(cfg, got, ref[r], 4e-3 if dtype == 2 else 1e-6)
+
+
+def test_token_subset_equals_full_rows():
+    cfg = KleosConfig(sequence_len=128, hidden_size=64, intermediate_size=64, num_experts=8,
+                      torch_dtype=2)
+    views = [synth.split_packed(cfg, synth.packed_input(cfg, 0, 1), 1)]
+    full = c_oracle.moe_forward_rank(cfg, 1, 0, views)
+    rows = np.array([0, 5, 17, 127], dtype=np.int32)
+    part = c_oracle.moe_forward_rank(cfg, 1, 0, views, tokens=rows)
+    assert np.array_equal(part["out"], full["out"][rows])
+    part_np = moe_oracle.moe_forward(cfg, 1, views, token_subset=rows)[0]
+    assert np.abs(part_np["out"] - full["out"][rows]).max() <= 4e-3 * np.abs(full["out"]).max()
+
+
+def test_ties_go_to_lowest_expert_id():
+    """All experts share one gate row, so every logit ties: top-k must be {0, 1}."""
+    cfg = KleosConfig(sequence_len=128, hidden_size=64, intermediate_size=64, num_experts=8,
+                      torch_dtype=0)
+    packed = synth.packed_input(cfg, 0, 1)
+    v = synth.split_packed(cfg, packed, 1)
+    v["Wg"][: cfg.E] = v["Wg"][0]
+    for res in (moe_oracle.moe_forward(cfg, 1, [v])[0], c_oracle.moe_forward_rank(cfg, 1, 0, [v])):
+        assert np.array_equal(np.sort(res["topk"], axis=1),
+                              np.tile(np.array([0, 1]), (cfg.S, 1)))
+        # capacity EC = ceil(S/E)*k = 32: the first 32 tokens keep their slot, the rest drop
+        assert res["counts"][0] == cfg.S and res["counts"][1] == cfg.S
+        assert (res["slots"][: cfg.EC] >= 0).all() and (res["slots"][cfg.EC:] < 0).all()
+        assert np.all(res["out"][cfg.EC:] == 0)
+
+
+def test_capacity_formula_and_drops():
+    cfg = KleosConfig(sequence_len=256, hidden_size=64, intermediate_size=64, num_experts=16,
+                      torch_dtype=2, capacity_factor=1.25)
+    assert cfg.EC == 40 and cfg.pEC == 128
+    views = [synth.split_packed(cfg, synth.packed_input(cfg, 0, 1), 1)]
+    bias = synth.zipf_gate_bias(cfg, 1.2) * 3
+    res = moe_oracle.moe_forward(cfg, 1, views, gate_bias=bias)[0]
+    assert (res["routed"] <= cfg.EC).all() and (res["counts"] >= res["routed"]).all()
+    over = res["counts"] > cfg.EC
+    assert over.any(), "the skewed gate should overflow at least one expert"
+    kept = (res["slots"] >= 0).sum()
+    assert kept == res["routed"].sum()
+    assert res["slots"].max() < cfg.EC
