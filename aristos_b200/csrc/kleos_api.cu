@@ -702,3 +702,6 @@ int kleos_finalize(void) {
 }
 
 }  // extern "C"
+
+// Allocation-free router entry point (kleos_route_static) with its fixed device scratch array.
+#include "route_static.cuh"

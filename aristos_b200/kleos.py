@@ -26,7 +26,7 @@ EXPORTS = (
     "kleos_get_unique_id", "kleos_config_probe", "kleos_set_device", "kleos_initialize", "kleos_set_gate_bias",
     "kleos_forward", "kleos_forward_bench", "kleos_forward_host", "kleos_get_rank",
     "kleos_local_experts", "kleos_get_info", "kleos_last_status", "kleos_debug_routing",
-    "kleos_phase_times", "kleos_debug_gemm_stats", "kleos_finalize", "kleos_error_string",
+    "kleos_phase_times", "kleos_debug_gemm_stats", "kleos_route_static", "kleos_finalize", "kleos_error_string",
 )
 
 PHASE_NAMES = ("route", "slots", "dispatch", "plan", "gemm1", "gemm2", "combine", "total")
@@ -179,6 +179,17 @@ def gemm_stats():
     if n < 0:
         _check(n, "kleos_debug_gemm_stats")
     return buf[:n].reshape(2, -1, 8)
+
+
+def route_static(A, Wg, gate_bias, S, H, E, K, torch_dtype, probs, topk, mcw, stream=None) -> None:
+    """Router without any device allocation (fixed scratch inside the library): see
+    kleos_route_static in include/kleos_b200.h for limits and the no-overlap rule."""
+    lib = load_library()
+    lib.kleos_route_static.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p] + \
+        [ctypes.c_int] * 5 + [ctypes.c_void_p] * 4
+    _check(lib.kleos_route_static(_ptr(A), _ptr(Wg), _ptr(gate_bias), S, H, E, K, torch_dtype,
+                                  _ptr(probs), _ptr(topk), _ptr(mcw), stream),
+           "kleos_route_static")
 
 
 def last_status() -> Status:

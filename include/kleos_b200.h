@@ -127,6 +127,24 @@ int kleos_phase_times(float* ms, int n);
  * A tuning aid with no counterpart in the reference. */
 int kleos_debug_gemm_stats(long long* out, int max_values);
 
+/* Router only, for callers that cannot allocate device memory when they call (inside another
+ * runtime's allocator callback, in a serving loop with a frozen memory budget, ...).  It has no
+ * counterpart in the reference, which always routes inside its fused kernel.  It needs no
+ * kleos_initialize: the scratch it uses (near-tie list, fp64 logits, counters; 2,130,176 bytes)
+ * is a fixed array inside the library that every GPU loading it keeps until the process ends,
+ * and the call performs no cudaMalloc / cudaFree.
+ *   A [S,H], Wg [64,H] (row e = expert e, rows >= E zero), gate_bias [E] floats or NULL,
+ *   probs [S,64] (element type), topk [S,K], mcw [S]: all DEVICE pointers owned by the caller.
+ *   Limits: S <= 4096, E <= 64, K <= min(E, 8), H a multiple of 64, torch_dtype 0 or 2; anything
+ *   larger is refused with KLEOS_E_ARG and a message on stderr.
+ * The first call on each device looks up the array's device address; make that call before any
+ * stream capture.  All calls share the one array and each call first clears the part that must
+ * start at zero, so two calls that overlap on the GPU (different streams, different threads)
+ * race: serialise them.  Asynchronous on `stream` (NULL = per-thread default stream). */
+int kleos_route_static(const void* A, const void* Wg, const float* gate_bias, int S, int H, int E,
+                       int K, int torch_dtype, void* probs, int32_t* topk, float* mcw,
+                       void* stream);
+
 /* Free everything.  Replaces kleos::finalize() (bootstrap.cuh:561-588). */
 int kleos_finalize(void);
 
