@@ -30,7 +30,7 @@ constexpr int A_STAGE_BYTES = BM * BK * 2;        // 16 KiB: this block's panel
 constexpr int B_STAGE_BYTES = (BN / 2) * BK * 2;  // 16 KiB: this block's half of the weight tile
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int TMEM_COLS = 512;  // two accumulators of 256 fp32 columns
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 12288;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 28672;
 constexpr uint32_t kInstrDesc = tc::make_instr_desc_bf16(2 * BM, BN);
 
 struct Control {
@@ -42,6 +42,7 @@ struct Control {
     int abort;
     int le_start[257];
     __align__(16) float bias_s[2][4][256];  // bias of the tile being read back: [accumulator][epilogue warp]
+    __align__(16) uint4 stage_s[4][32 * 8];  // per epilogue warp: 32 rows x 128 bytes, swizzled
 };
 
 struct PairTile {
@@ -255,9 +256,20 @@ ffn_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
             tc_fence_after();
             const int n0 = pt.nt * BN;
             const uint32_t taddr = tmem_base + buf * BN + (static_cast<uint32_t>(q * 32) << 16);
-            __nv_bfloat16* orow = (row < rows) ? out_ptr<__nv_bfloat16>(g, p, row, n0) : nullptr;
-            // accumulator read-back, two 32-column chunks in flight; bias fetched as 16-byte
-            // broadcast loads
+            // this warp's 32 accumulator rows; rows_w of them carry tokens
+            const int rows_w = min(32, rows - q * 32);
+            if (rows_w <= 0) {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&ctl->acc_empty[buf]), 0));
+                continue;
+            }
+            __nv_bfloat16* obase = out_ptr<__nv_bfloat16>(g, p, q * 32, n0);
+            uint4* stg = ctl->stage_s[q];
+            // Accumulator read-back, two 32-column chunks in flight.  Every 64 columns the warp
+            // transposes through a swizzled shared-memory tile so that each store instruction
+            // writes four complete 128-byte lines (one row segment per 8 lanes) instead of 32
+            // scattered 16-byte pieces: this is what the NVLink path to a peer's cell needs.
             uint32_t r[2][32];
             tmem_ld_32x32(taddr, r[0]);
 #pragma unroll
@@ -265,36 +277,53 @@ ffn_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
                 const long long tq = clock64();
                 tmem_ld_wait();
                 w_tmem += clock64() - tq;
-                if (c + 1 < BN / 32) tmem_ld_32x32(taddr + (c + 1) * 32, r[(c + 1) & 1]);
-                if (orow != nullptr && n0 + c * 32 < g.N) {
-                    const uint32_t* rc = r[c & 1];
-                    const float4* bq = reinterpret_cast<const float4*>(&ctl->bias_s[buf][q][c * 32]);
-                    uint32_t packed[16];
+                if (c + 1 < BN / 32) {
+                    tmem_ld_32x32(taddr + (c + 1) * 32, r[(c + 1) & 1]);
+                } else {
+                    // the whole accumulator is in registers: hand it back to the MMA issuer
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&ctl->acc_empty[buf]), 0));
+                }
+                const uint32_t* rc = r[c & 1];
+                const float4* bq = reinterpret_cast<const float4*>(&ctl->bias_s[buf][q][c * 32]);
+                uint32_t packed[16];
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const float4 bf = bq[j >> 1];
-                        float v0 = __uint_as_float(rc[2 * j]) + ((j & 1) ? bf.z : bf.x);
-                        float v1 = __uint_as_float(rc[2 * j + 1]) + ((j & 1) ? bf.w : bf.y);
-                        if constexpr (kEpi == 0) {
-                            v0 = fmaxf(v0, 0.f);
-                            v1 = fmaxf(v1, 0.f);
-                        } else if constexpr (kEpi == 1) {
-                            v0 = apply_act(v0, 1);
-                            v1 = apply_act(v1, 1);
-                        }
-                        const __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
-                        packed[j] = *reinterpret_cast<const uint32_t*>(&h);
+                for (int j = 0; j < 16; ++j) {
+                    const float4 bf = bq[j >> 1];
+                    float v0 = __uint_as_float(rc[2 * j]) + ((j & 1) ? bf.z : bf.x);
+                    float v1 = __uint_as_float(rc[2 * j + 1]) + ((j & 1) ? bf.w : bf.y);
+                    if constexpr (kEpi == 0) {
+                        v0 = fmaxf(v0, 0.f);
+                        v1 = fmaxf(v1, 0.f);
+                    } else if constexpr (kEpi == 1) {
+                        v0 = apply_act(v0, 1);
+                        v1 = apply_act(v1, 1);
                     }
-                    uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
+                    const __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
+                    packed[j] = *reinterpret_cast<const uint32_t*>(&h);
+                }
 #pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        dst[j] = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2],
-                                            packed[4 * j + 3]);
+                for (int j = 0; j < 4; ++j) {
+                    const int ch = (c & 1) * 4 + j;  // 16-byte chunk inside the 128-byte row segment
+                    stg[lane * 8 + (ch ^ (lane & 7))] = make_uint4(
+                        packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+                }
+                if (c & 1) {
+                    __syncwarp();
+                    const int col0 = (c - 1) * 32;
+                    if (n0 + col0 < g.N) {
+#pragma unroll
+                        for (int it = 0; it < 8; ++it) {
+                            const int rr = it * 4 + (lane >> 3), ch = lane & 7;
+                            const uint4 v = stg[rr * 8 + (ch ^ (rr & 7))];
+                            if (rr < rows_w)
+                                *reinterpret_cast<uint4*>(obase + (size_t)rr * g.N + col0 + ch * 8) = v;
+                        }
+                    }
+                    __syncwarp();
                 }
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&ctl->acc_empty[buf]), 0));
         }
         if (g.stats && warp == 4 && lane == 0) {
             g.stats[blockIdx.x * 8 + 5] = w_accfull;
