@@ -13,6 +13,8 @@
 
 namespace kleos {
 
+constexpr int kStatSlots = 12;  // per-block stall counters (see kleos_debug_gemm_stats)
+
 struct GemmArgs {
     const PanelEntry* panels;
     const int* le_start;  // [nLx+1]
@@ -24,7 +26,7 @@ struct GemmArgs {
     ArenaLayout lay;
     ReturnFlagArgs ret;   // mode 1: flags raised by the last block
     DeviceStatus* status;
-    long long* stats;     // optional [grid][8] per-role stall counters (cycles), or null
+    long long* stats;     // optional [grid][kStatSlots] per-role stall counters (cycles), or null
     long long wait_cycles;
     int N, Kd, mode, hidden_act;
     int nLx, pEC, rank, elem_bytes;

@@ -121,8 +121,8 @@ ffn_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 }
             }
             if (g.stats) {
-                g.stats[blockIdx.x * 8 + 0] = w_empty;
-                g.stats[blockIdx.x * 8 + 1] = clock64() - t_begin;
+                g.stats[blockIdx.x * kStatSlots + 0] = w_empty;
+                g.stats[blockIdx.x * kStatSlots + 1] = clock64() - t_begin;
             }
         }
         __syncwarp();
@@ -167,9 +167,9 @@ ffn_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 umma_commit(&ctl->acc_full[buf]);
             }
             if (g.stats) {
-                g.stats[blockIdx.x * 8 + 2] = w_acc;
-                g.stats[blockIdx.x * 8 + 3] = w_full;
-                g.stats[blockIdx.x * 8 + 4] = clock64() - t_begin;
+                g.stats[blockIdx.x * kStatSlots + 2] = w_acc;
+                g.stats[blockIdx.x * kStatSlots + 3] = w_full;
+                g.stats[blockIdx.x * kStatSlots + 4] = clock64() - t_begin;
             }
         }
         __syncwarp();
@@ -257,9 +257,9 @@ ffn_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             if (lane == 0) mbar_arrive(&ctl->acc_empty[buf]);
         }
         if (g.stats && warp == 4 && lane == 0) {
-            g.stats[blockIdx.x * 8 + 5] = w_accfull;
-            g.stats[blockIdx.x * 8 + 6] = clock64() - t_begin;
-            g.stats[blockIdx.x * 8 + 7] = w_tmem;
+            g.stats[blockIdx.x * kStatSlots + 5] = w_accfull;
+            g.stats[blockIdx.x * kStatSlots + 6] = clock64() - t_begin;
+            g.stats[blockIdx.x * kStatSlots + 7] = w_tmem;
         }
     }
 

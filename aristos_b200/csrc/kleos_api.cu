@@ -49,7 +49,9 @@ struct State {
     uint32_t epoch = 0;
     long long wait_cycles = 4000000000LL;  // about two seconds of SM clock
     bool use_tc = false;
-    bool use_pair = true;  // cta_group::2 GEMM (two blocks per 256x256 tile)
+    bool use_pair = true;
+    bool use_fused = false; // experimental: dispatch + plan inside the GEMM1 kernel (KLEOS_FUSED=1)
+    int dispatch_ctas = 12; // blocks of the fused kernel that only move tokens (KLEOS_DISPATCH_CTAS)  // cta_group::2 GEMM (two blocks per 256x256 tile)
 
     // symmetric arena
     ArenaLayout lay{};
@@ -64,7 +66,7 @@ struct State {
     double* refine_logits = nullptr;
     float *mcw = nullptr, *bias = nullptr;
     unsigned *counts = nullptr, *done_dispatch = nullptr, *done_gemm2 = nullptr,
-             *cell_counts = nullptr;
+             *cell_counts = nullptr, *cell_done = nullptr;
     PanelEntry* panels = nullptr;
     DeviceStatus* status = nullptr;
     long long* gemm_stats = nullptr;  // [2][grid][8] when KLEOS_GEMM_STATS=1
@@ -278,26 +280,36 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed) {
     KLEOS_CUDA(mark());
 
     // 2. slots
-    SlotArgs sa{g.topk, g.slots, g.cell_tokens, g.counts, c.S, c.K, c.E, c.EC, c.pEC};
+    SlotArgs sa{};
+    sa.topk = g.topk; sa.slots = g.slots; sa.cell_tokens = g.cell_tokens; sa.counts = g.counts;
+    sa.S = c.S; sa.K = c.K; sa.E = c.E; sa.EC = c.EC; sa.pEC = c.pEC;
+    for (int r = 0; r < kMaxWorld; ++r) sa.peer_arena[r] = g.peers.arena[r];
+    sa.cflag_offset = g.lay.cflag; sa.rank = g.rank; sa.nLx = g.nLx; sa.epoch = g.epoch;
     slot_kernel<<<c.E, 256, 0, st>>>(sa);
     KLEOS_CUDA(mark());
 
+    const bool fused = g.use_tc && g.use_pair && g.use_fused;
+    if (!fused) {
     // 3. dispatch
-    DispatchArgs da{};
-    da.A = s.A; da.cell_tokens = g.cell_tokens; da.counts = g.counts; da.peers = g.peers;
-    da.lay = g.lay; da.done_counter = g.done_dispatch; da.H = c.H; da.E = c.E; da.EC = c.EC;
-    da.pEC = c.pEC; da.nLx = g.nLx; da.rank = g.rank; da.world = g.world; da.epoch = g.epoch;
-    da.elem_bytes = c.elem_bytes;
-    dispatch_kernel<<<g.sm_count * 4, 256, 0, st>>>(da);
-    KLEOS_CUDA(mark());
+        DispatchArgs da{};
+        da.A = s.A; da.cell_tokens = g.cell_tokens; da.counts = g.counts; da.peers = g.peers;
+        da.lay = g.lay; da.done_counter = g.done_dispatch; da.H = c.H; da.E = c.E; da.EC = c.EC;
+        da.pEC = c.pEC; da.nLx = g.nLx; da.rank = g.rank; da.world = g.world; da.epoch = g.epoch;
+        da.elem_bytes = c.elem_bytes;
+        dispatch_kernel<<<g.sm_count * 4, 256, 0, st>>>(da);
+        KLEOS_CUDA(mark());
 
-    // 4. plan: wait for every source's counts, list the panels
-    PlanArgs pa{};
-    pa.arena = g.arena; pa.lay = g.lay; pa.panels = g.panels; pa.le_start = g.le_start;
-    pa.cell_counts = g.cell_counts; pa.status = g.status; pa.world = g.world; pa.nLx = g.nLx;
-    pa.pEC = c.pEC; pa.epoch = g.epoch; pa.wait_cycles = g.wait_cycles;
-    plan_kernel<<<1, 1024, 0, st>>>(pa);
-    KLEOS_CUDA(mark());
+        // 4. plan: wait for every source's counts, list the panels
+        PlanArgs pa{};
+        pa.arena = g.arena; pa.lay = g.lay; pa.panels = g.panels; pa.le_start = g.le_start;
+        pa.cell_counts = g.cell_counts; pa.status = g.status; pa.world = g.world; pa.nLx = g.nLx;
+        pa.pEC = c.pEC; pa.epoch = g.epoch; pa.wait_cycles = g.wait_cycles;
+        plan_kernel<<<1, 1024, 0, st>>>(pa);
+        KLEOS_CUDA(mark());
+    } else {
+        KLEOS_CUDA(mark());
+        KLEOS_CUDA(mark());
+    }
 
     // 5./6. expert FFN
     GemmArgs ga{};
@@ -314,18 +326,30 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed) {
     g2.A = g.y1; g2.B = s.W2; g2.bias = s.b2; g2.N = c.H; g2.Kd = c.I; g2.mode = 1;
     if (g.gemm_stats) {
         g1.stats = g.gemm_stats;
-        g2.stats = g.gemm_stats + (size_t)g.sm_count * 8;
+        g2.stats = g.gemm_stats + (size_t)g.sm_count * kStatSlots;
     }
     if (g.use_tc) {
         if constexpr (sizeof(T) == 2) {
             if (g.use_pair) {
                 const int grid = g.sm_count & ~1;
-                if (c.hidden_act == 0)
-                    ffn_gemm_tc2<0><<<grid, 256, gemm_tc2::SMEM_BYTES, st>>>(g.map_x, g.map_w1h, g1);
-                else
-                    ffn_gemm_tc2<1><<<grid, 256, gemm_tc2::SMEM_BYTES, st>>>(g.map_x, g.map_w1h, g1);
+                gemm_tc2::FusedArgs fa{};
+                fa.tokens = s.A; fa.cell_tokens = g.cell_tokens; fa.counts = g.counts;
+                fa.cell_done = g.cell_done; fa.panels_out = g.panels; fa.le_start_out = g.le_start;
+                fa.arena = g.arena; fa.E = c.E; fa.EC = c.EC; fa.world = g.world; fa.H = c.H;
+                fa.dispatch_ctas = fused ? g.dispatch_ctas : 0;
+                if (fused) {
+                    const int thr = gemm_tc2::kFusedThreads;
+                    if (c.hidden_act == 0)
+                        ffn_gemm_tc2<0, true><<<grid, thr, gemm_tc2::SMEM_BYTES, st>>>(g.map_x, g.map_w1h, g1, fa);
+                    else
+                        ffn_gemm_tc2<1, true><<<grid, thr, gemm_tc2::SMEM_BYTES, st>>>(g.map_x, g.map_w1h, g1, fa);
+                } else if (c.hidden_act == 0) {
+                    ffn_gemm_tc2<0, false><<<grid, 256, gemm_tc2::SMEM_BYTES, st>>>(g.map_x, g.map_w1h, g1, fa);
+                } else {
+                    ffn_gemm_tc2<1, false><<<grid, 256, gemm_tc2::SMEM_BYTES, st>>>(g.map_x, g.map_w1h, g1, fa);
+                }
                 KLEOS_CUDA(mark());
-                ffn_gemm_tc2<2><<<grid, 256, gemm_tc2::SMEM_BYTES, st>>>(g.map_y1, g.map_w2h, g2);
+                ffn_gemm_tc2<2, false><<<grid, 256, gemm_tc2::SMEM_BYTES, st>>>(g.map_y1, g.map_w2h, g2, fa);
                 KLEOS_CUDA(mark());
             } else {
                 if (c.hidden_act == 0)
@@ -375,7 +399,7 @@ void release_all() {
     cudaFree(g.y1); cudaFree(g.topk); cudaFree(g.slots); cudaFree(g.cell_tokens);
     cudaFree(g.refine_list); cudaFree(g.refine_count); cudaFree(g.refine_done); cudaFree(g.refine_logits); cudaFree(g.le_start); cudaFree(g.mcw);
     cudaFree(g.bias); cudaFree(g.counts); cudaFree(g.done_dispatch); cudaFree(g.done_gemm2);
-    cudaFree(g.cell_counts); cudaFree(g.panels); cudaFree(g.status); cudaFree(g.gemm_stats);
+    cudaFree(g.cell_counts); cudaFree(g.cell_done); cudaFree(g.panels); cudaFree(g.status); cudaFree(g.gemm_stats);
     for (auto& e : g.ev)
         if (e) cudaEventDestroy(e);
     if (g.comm && nccl.CommDestroy) nccl.CommDestroy(g.comm);
@@ -482,7 +506,8 @@ int kleos_initialize(const char* config_json_path, int rank, int world, const vo
     g.lay.xcell = 0;
     g.lay.ycell = align_up(g.lay.xcell + cell_bytes, 1024);
     g.lay.xflag = align_up(g.lay.ycell + cell_bytes, 1024);
-    g.lay.yflag = align_up(g.lay.xflag + (size_t)cfg.E * 8, 1024);
+    g.lay.cflag = align_up(g.lay.xflag + (size_t)cfg.E * 8, 1024);
+    g.lay.yflag = align_up(g.lay.cflag + (size_t)cfg.E * 8, 1024);
     g.lay.bytes = align_up(g.lay.yflag + (size_t)kMaxWorld * 8, 1024);
 
     int rc;
@@ -504,11 +529,12 @@ int kleos_initialize(const char* config_json_path, int rank, int world, const vo
     if ((rc = dev_alloc(&g.done_dispatch, 1))) return rc;
     if ((rc = dev_alloc(&g.done_gemm2, 1))) return rc;
     if ((rc = dev_alloc(&g.cell_counts, (size_t)cfg.E))) return rc;
+    if ((rc = dev_alloc(&g.cell_done, (size_t)cfg.E))) return rc;
     if ((rc = dev_alloc(&g.panels, (size_t)cfg.E * cfg.pEC / kTileM))) return rc;
     if ((rc = dev_alloc(&g.status, 1))) return rc;
     for (auto& e : g.ev) KLEOS_CUDA(cudaEventCreate(&e));
     if (const char* gs = std::getenv("KLEOS_GEMM_STATS"))
-        if (gs[0] == '1' && (rc = dev_alloc(&g.gemm_stats, (size_t)2 * g.sm_count * 8))) return rc;
+        if (gs[0] == '1' && (rc = dev_alloc(&g.gemm_stats, (size_t)2 * g.sm_count * kStatSlots))) return rc;
 
     if (g.use_tc) {
         KLEOS_CUDA(cudaFuncSetAttribute(route_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -517,11 +543,19 @@ int kleos_initialize(const char* config_json_path, int rank, int world, const vo
                                         route_tc::Shape<128>::SMEM_BYTES));
     }
     if (const char* pr = std::getenv("KLEOS_GEMM_PAIR")) g.use_pair = pr[0] != '0';
+    if (const char* fu = std::getenv("KLEOS_FUSED")) g.use_fused = fu[0] != '0';
+    if (const char* dc = std::getenv("KLEOS_DISPATCH_CTAS")) g.dispatch_ctas = std::max(2, std::atoi(dc) & ~1);
+    // the fused kernel keeps its panel list and per-cell tables in shared memory
+    if ((size_t)cfg.E * cfg.pEC / kTileM > (size_t)gemm_tc2::kMaxFusedPanels || cfg.E > 256 || g.nLx > 255 ||
+        cfg.H * 2 > gemm_tc2::kRowBufBytes)
+        g.use_fused = false;
     if (g.use_tc)
     {
-        KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm_tc2::SMEM_BYTES));
-        KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm_tc2::SMEM_BYTES));
-        KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm_tc2::SMEM_BYTES));
+        KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm_tc2::SMEM_BYTES));
+        KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm_tc2::SMEM_BYTES));
+        KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm_tc2::SMEM_BYTES));
+        KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm_tc2::SMEM_BYTES));
+        KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm_tc2::SMEM_BYTES));
         KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm_tc::SMEM_BYTES));
         KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm_tc::SMEM_BYTES));
         KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm_tc::SMEM_BYTES));
@@ -676,7 +710,7 @@ int kleos_debug_routing(int32_t* topk, int32_t* slots, uint32_t* counts, float* 
 int kleos_debug_gemm_stats(long long* out, int max_values) {
     if (!g.initialised) return fail(KLEOS_E_STATE, "not initialised");
     if (!g.gemm_stats) return fail(KLEOS_E_STATE, "set KLEOS_GEMM_STATS=1 before kleos_initialize");
-    const int n = 2 * g.sm_count * 8;
+    const int n = 2 * g.sm_count * kStatSlots;
     if (!out || max_values < n) return fail(KLEOS_E_ARG, "need room for %d values", n);
     KLEOS_CUDA(cudaStreamSynchronize(cudaStreamPerThread));
     KLEOS_CUDA(cudaMemcpy(out, g.gemm_stats, sizeof(long long) * n, cudaMemcpyDeviceToHost));

@@ -297,6 +297,12 @@ struct SlotArgs {
     int* cell_tokens;       // [E,pEC] token id held by each slot
     unsigned* counts;       // [E] unclamped
     int S, K, E, EC, pEC;
+    // count flags: cflag[owner][rank*nLx + le] = (epoch<<32)|routed, one 8-byte peer store per
+    // expert (the reference's first-stage signal carries the same count, types.cuh:300-317)
+    char* peer_arena[kMaxWorld];
+    size_t cflag_offset;
+    int rank, nLx;
+    uint32_t epoch;
 };
 
 // One block per expert; slots in ascending token order.
@@ -326,6 +332,10 @@ __global__ void __launch_bounds__(256) slot_kernel(SlotArgs a) {
         }
         base_s = run;
         a.counts[e] = (unsigned)run;
+        const int owner = e / a.nLx, le = e - owner * a.nLx;
+        st_release_sys(reinterpret_cast<unsigned long long*>(a.peer_arena[owner] + a.cflag_offset) +
+                           ((size_t)a.rank * a.nLx + le),
+                       make_flag(a.epoch, (unsigned)min(run, a.EC)));
     }
     __syncthreads();
     int pos = warp_sums[warp] + incl - mine;

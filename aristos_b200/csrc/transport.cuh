@@ -18,7 +18,8 @@ namespace kleos {
 struct ArenaLayout {
     size_t xcell;  // [world*nLx][pEC][H] dispatched token rows, by (source rank, local expert)
     size_t ycell;  // [E][pEC][H] returned FFN rows, by global expert
-    size_t xflag;  // [world*nLx] u64: (epoch<<32)|routed count
+    size_t xflag;  // [world*nLx] u64: (epoch<<32)|routed count, raised when the cell's rows are stored
+    size_t cflag;  // [world*nLx] u64: (epoch<<32)|routed count, raised as soon as the count is known
     size_t yflag;  // [world] u64: (epoch<<32)|1 when that expert rank has returned everything
     size_t bytes;
 };

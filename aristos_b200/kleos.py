@@ -174,11 +174,11 @@ def phase_times() -> dict:
 def gemm_stats():
     """Per-block stall counters of the last two GEMM launches (needs KLEOS_GEMM_STATS=1)."""
     import numpy as np
-    buf = np.zeros(2 * 256 * 8, dtype=np.int64)
+    buf = np.zeros(2 * 256 * 12, dtype=np.int64)
     n = load_library().kleos_debug_gemm_stats(buf.ctypes.data_as(ctypes.c_void_p), buf.size)
     if n < 0:
         _check(n, "kleos_debug_gemm_stats")
-    return buf[:n].reshape(2, -1, 8)
+    return buf[:n].reshape(2, -1, 12)
 
 
 def route_static(A, Wg, gate_bias, S, H, E, K, torch_dtype, probs, topk, mcw, stream=None) -> None:

@@ -121,9 +121,10 @@ int kleos_debug_routing(int32_t* topk, int32_t* slots, uint32_t* counts, float* 
 int kleos_phase_times(float* ms, int n);
 
 /* Stall counters of the last GEMM1 and GEMM2 launches, only when the environment variable
- * KLEOS_GEMM_STATS=1 was set at initialise time: [2][blocks][8] clock cycles per block
+ * KLEOS_GEMM_STATS=1 was set at initialise time: [2][blocks][12] clock cycles per block
  * {producer wait-empty, producer total, MMA wait-accumulator, MMA wait-operands, MMA total,
- *  epilogue wait-accumulator, epilogue total, unused}.  Returns the number of values written.
+ *  epilogue wait-accumulator, epilogue total, epilogue TMEM wait, plan prologue, producer wait
+ *  for cell data, dispatch finished at, unused}.  Returns the number of values written.
  * A tuning aid with no counterpart in the reference. */
 int kleos_debug_gemm_stats(long long* out, int max_values);
 
