@@ -30,6 +30,7 @@ struct GemmArgs {
     long long wait_cycles;
     int N, Kd, mode, hidden_act;
     int nLx, pEC, rank, elem_bytes;
+    int le_begin, le_end;  // local experts this launch works on
     uint32_t epoch;
 };
 
@@ -39,9 +40,9 @@ struct TileCoord {
 
 // Tiles are ordered: local expert, then N tile, then panel, so that consecutive tiles (which
 // persistent blocks pick up at about the same time) read the same weight tile from L2.
-__device__ __forceinline__ bool decode_tile(int t, const int* le_start, int nLx, int NT,
-                                            TileCoord* c) {
-    for (int le = 0; le < nLx; ++le) {
+__device__ __forceinline__ bool decode_tile(int t, const int* le_start, int le_begin, int le_end,
+                                            int NT, TileCoord* c) {
+    for (int le = le_begin; le < le_end; ++le) {
         const int p0 = le_start[le], np = le_start[le + 1] - p0;
         const int tiles = np * NT;
         if (t < tiles) {

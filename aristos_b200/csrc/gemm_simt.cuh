@@ -22,7 +22,7 @@ __global__ void __launch_bounds__(256) ffn_gemm_simt(GemmArgs g) {
     for (int i = tid; i <= g.nLx; i += 256) le_start_s[i] = g.le_start[i];
     __syncthreads();
     const int NT = (g.N + BN - 1) / BN;
-    const int total = le_start_s[g.nLx] * NT;
+    const int total = (le_start_s[g.le_end] - le_start_s[g.le_begin]) * NT;
     const T* A = static_cast<const T*>(g.A);
     const T* B = static_cast<const T*>(g.B);
     const T* bias = static_cast<const T*>(g.bias);
@@ -30,7 +30,7 @@ __global__ void __launch_bounds__(256) ffn_gemm_simt(GemmArgs g) {
 
     for (int t = blockIdx.x; t < total; t += gridDim.x) {
         TileCoord tc;
-        if (!decode_tile(t, le_start_s, g.nLx, NT, &tc)) break;
+        if (!decode_tile(t, le_start_s, g.le_begin, g.le_end, NT, &tc)) break;
         const PanelEntry p = g.panels[tc.panel];
         const int n0 = tc.nt * BN;
         const T* arow = A + (size_t)(p.row_base + lrow) * g.Kd;

@@ -89,7 +89,7 @@ ffn_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     const uint32_t tmem_base = ctl->tmem_base;
 
     const int NT = (g.N + BN - 1) / BN;
-    const int total = ctl->le_start[g.nLx] * NT;
+    const int total = (ctl->le_start[g.le_end] - ctl->le_start[g.le_begin]) * NT;
     const int KB = g.Kd / BK;
 
     if (warp == 0) {
@@ -103,7 +103,7 @@ ffn_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             const long long t_begin = clock64();
             for (int t = blockIdx.x; t < total && !*abort_flag; t += gridDim.x) {
                 TileCoord tcd;
-                if (!decode_tile(t, ctl->le_start, g.nLx, NT, &tcd)) break;
+                if (!decode_tile(t, ctl->le_start, g.le_begin, g.le_end, NT, &tcd)) break;
                 const PanelEntry p = g.panels[tcd.panel];
                 const int brow = tcd.le * g.N + tcd.nt * BN;
                 for (int kb = 0; kb < KB; ++kb, ++it) {
@@ -183,7 +183,7 @@ ffn_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         const long long t_begin = clock64();
         for (int t = blockIdx.x; t < total; t += gridDim.x, ++tile_n) {
             TileCoord tcd;
-            if (!decode_tile(t, ctl->le_start, g.nLx, NT, &tcd)) break;
+            if (!decode_tile(t, ctl->le_start, g.le_begin, g.le_end, NT, &tcd)) break;
             const PanelEntry p = g.panels[tcd.panel];
             const uint32_t buf = tile_n & 1, use = tile_n >> 1;
             if (*abort_flag) break;

@@ -93,9 +93,9 @@ struct PairTile {
 };
 
 // Tiles ordered by local expert, then N tile, then panel pair.
-__device__ __forceinline__ bool decode_pair_tile(int t, const int* le_start, int nLx, int NT,
-                                                 PairTile* c) {
-    for (int le = 0; le < nLx; ++le) {
+__device__ __forceinline__ bool decode_pair_tile(int t, const int* le_start, int le_begin,
+                                                 int le_end, int NT, PairTile* c) {
+    for (int le = le_begin; le < le_end; ++le) {
         const int p0 = le_start[le], np = le_start[le + 1] - p0;
         const int npair = (np + 1) >> 1;
         const int tiles = npair * NT;
@@ -112,9 +112,10 @@ __device__ __forceinline__ bool decode_pair_tile(int t, const int* le_start, int
     return false;
 }
 
-__device__ __forceinline__ int total_pair_tiles(const int* le_start, int nLx, int NT) {
+__device__ __forceinline__ int total_pair_tiles(const int* le_start, int le_begin, int le_end,
+                                                int NT) {
     int total = 0;
-    for (int le = 0; le < nLx; ++le) total += ((le_start[le + 1] - le_start[le] + 1) >> 1) * NT;
+    for (int le = le_begin; le < le_end; ++le) total += ((le_start[le + 1] - le_start[le] + 1) >> 1) * NT;
     return total;
 }
 
@@ -250,7 +251,7 @@ ffn_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     };
 
     const int NT = (g.N + BN - 1) / BN;
-    const int total = total_pair_tiles(ctl->le_start, g.nLx, NT);
+    const int total = total_pair_tiles(ctl->le_start, g.le_begin, g.le_end, NT);
     const int KB = g.Kd / BK;
     const int n_clusters = ((int)gridDim.x - n_disp) >> 1, cluster_id = blockIdx.x >> 1;
 
@@ -265,7 +266,7 @@ ffn_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
             const long long t_begin = clock64();
             for (int t = cluster_id; t < total && !*abort_flag; t += n_clusters) {
                 PairTile pt;
-                if (!decode_pair_tile(t, ctl->le_start, g.nLx, NT, &pt)) break;
+                if (!decode_pair_tile(t, ctl->le_start, g.le_begin, g.le_end, NT, &pt)) break;
                 // the block without a panel of its own re-reads the first one and discards
                 const int my_panel = pt.panel0 + ((int)cta_rank < pt.n_panels_left ? (int)cta_rank : 0);
                 const PanelEntry p = panel_at(my_panel);
@@ -371,7 +372,7 @@ ffn_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
         const long long t_begin = clock64();
         for (int t = cluster_id; t < total; t += n_clusters, ++tile_n) {
             PairTile pt;
-            if (!decode_pair_tile(t, ctl->le_start, g.nLx, NT, &pt)) break;
+            if (!decode_pair_tile(t, ctl->le_start, g.le_begin, g.le_end, NT, &pt)) break;
             const bool have_panel = (int)cta_rank < pt.n_panels_left;
             const PanelEntry p = panel_at(pt.panel0 + (have_panel ? (int)cta_rank : 0));
             const int rows = have_panel ? p.rows : 0;

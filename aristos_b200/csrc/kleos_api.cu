@@ -51,7 +51,10 @@ struct State {
     bool use_tc = false;
     bool use_pair = true;
     bool use_fused = false; // experimental: dispatch + plan inside the GEMM1 kernel (KLEOS_FUSED=1)
-    int dispatch_ctas = 12; // blocks of the fused kernel that only move tokens (KLEOS_DISPATCH_CTAS)  // cta_group::2 GEMM (two blocks per 256x256 tile)
+    int dispatch_ctas = 12; // blocks of the fused kernel that only move tokens (KLEOS_DISPATCH_CTAS)
+    int pipe_parts = 1;     // dispatch / GEMM1 software pipeline over groups of local experts (KLEOS_PIPE)
+    cudaStream_t copy_stream = nullptr;
+    cudaEvent_t ev_slots = nullptr, ev_part[8] = {};  // cta_group::2 GEMM (two blocks per 256x256 tile)
 
     // symmetric arena
     ArenaLayout lay{};
@@ -62,7 +65,7 @@ struct State {
     // local bookkeeping
     void* y1 = nullptr;
     int *topk = nullptr, *slots = nullptr, *cell_tokens = nullptr, *refine_list = nullptr,
-        *refine_count = nullptr, *le_start = nullptr, *refine_done = nullptr;
+        *refine_count = nullptr, *le_start = nullptr, *refine_done = nullptr, *tile_hist = nullptr;
     double* refine_logits = nullptr;
     float *mcw = nullptr, *bias = nullptr;
     unsigned *counts = nullptr, *done_dispatch = nullptr, *done_gemm2 = nullptr,
@@ -285,25 +288,44 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed) {
     sa.S = c.S; sa.K = c.K; sa.E = c.E; sa.EC = c.EC; sa.pEC = c.pEC;
     for (int r = 0; r < kMaxWorld; ++r) sa.peer_arena[r] = g.peers.arena[r];
     sa.cflag_offset = g.lay.cflag; sa.rank = g.rank; sa.nLx = g.nLx; sa.epoch = g.epoch;
-    slot_kernel<<<c.E, 256, 0, st>>>(sa);
+    sa.tile_hist = g.tile_hist;
+    tile_hist_kernel<<<(c.S + kSlotTile - 1) / kSlotTile, 256, 0, st>>>(sa);
+    slot_kernel<<<(c.S + kSlotTile - 1) / kSlotTile, 256, 0, st>>>(sa);
     KLEOS_CUDA(mark());
 
     const bool fused = g.use_tc && g.use_pair && g.use_fused;
+    // Dispatch and GEMM1 are software-pipelined over `parts` groups of local experts: the copy
+    // stream moves the rows of group p+1 to their owners while this stream plans and multiplies
+    // group p.  Every plan launch waits (on the device, bounded) for the count flags of its
+    // group from all source ranks, so there is still no host-side collective.
+    const int parts = fused ? 1 : std::max(1, std::min(std::min(g.pipe_parts, 8), g.nLx));
+    DispatchArgs da{};
+    da.A = s.A; da.cell_tokens = g.cell_tokens; da.counts = g.counts; da.peers = g.peers;
+    da.lay = g.lay; da.done_counter = g.done_dispatch; da.H = c.H; da.E = c.E; da.EC = c.EC;
+    da.pEC = c.pEC; da.nLx = g.nLx; da.rank = g.rank; da.world = g.world; da.epoch = g.epoch;
+    da.elem_bytes = c.elem_bytes;
+    PlanArgs pa{};
+    pa.arena = g.arena; pa.lay = g.lay; pa.panels = g.panels; pa.le_start = g.le_start;
+    pa.cell_counts = g.cell_counts; pa.status = g.status; pa.world = g.world; pa.nLx = g.nLx;
+    pa.pEC = c.pEC; pa.epoch = g.epoch; pa.wait_cycles = g.wait_cycles;
     if (!fused) {
-    // 3. dispatch
-        DispatchArgs da{};
-        da.A = s.A; da.cell_tokens = g.cell_tokens; da.counts = g.counts; da.peers = g.peers;
-        da.lay = g.lay; da.done_counter = g.done_dispatch; da.H = c.H; da.E = c.E; da.EC = c.EC;
-        da.pEC = c.pEC; da.nLx = g.nLx; da.rank = g.rank; da.world = g.world; da.epoch = g.epoch;
-        da.elem_bytes = c.elem_bytes;
-        dispatch_kernel<<<g.sm_count * 4, 256, 0, st>>>(da);
+        // 3. dispatch, all parts queued on the copy stream behind the slot kernel
+        cudaStream_t cs = parts > 1 ? g.copy_stream : st;
+        if (parts > 1) {
+            KLEOS_CUDA(cudaEventRecord(g.ev_slots, st));
+            KLEOS_CUDA(cudaStreamWaitEvent(cs, g.ev_slots, 0));
+        }
+        for (int p = 0; p < parts; ++p) {
+            da.le_begin = p * g.nLx / parts;
+            da.le_end = (p + 1) * g.nLx / parts;
+            dispatch_kernel<<<g.sm_count * 4, 256, 0, cs>>>(da);
+            if (parts > 1) KLEOS_CUDA(cudaEventRecord(g.ev_part[p], cs));
+        }
+        if (parts > 1) KLEOS_CUDA(cudaStreamWaitEvent(st, g.ev_part[0], 0));
         KLEOS_CUDA(mark());
-
-        // 4. plan: wait for every source's counts, list the panels
-        PlanArgs pa{};
-        pa.arena = g.arena; pa.lay = g.lay; pa.panels = g.panels; pa.le_start = g.le_start;
-        pa.cell_counts = g.cell_counts; pa.status = g.status; pa.world = g.world; pa.nLx = g.nLx;
-        pa.pEC = c.pEC; pa.epoch = g.epoch; pa.wait_cycles = g.wait_cycles;
+        // 4. plan of the first part: wait for every source's counts, list the panels
+        pa.le_begin = 0;
+        pa.le_end = g.nLx / parts;
         plan_kernel<<<1, 1024, 0, st>>>(pa);
         KLEOS_CUDA(mark());
     } else {
@@ -316,7 +338,7 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed) {
     ga.panels = g.panels; ga.le_start = g.le_start; ga.y1 = g.y1; ga.peers = g.peers;
     ga.lay = g.lay; ga.status = g.status; ga.wait_cycles = g.wait_cycles; ga.stats = nullptr;
     ga.hidden_act = c.hidden_act; ga.nLx = g.nLx; ga.pEC = c.pEC; ga.rank = g.rank;
-    ga.elem_bytes = c.elem_bytes; ga.epoch = g.epoch;
+    ga.elem_bytes = c.elem_bytes; ga.epoch = g.epoch; ga.le_begin = 0; ga.le_end = g.nLx;
     ga.ret.peers = g.peers; ga.ret.lay = g.lay; ga.ret.done_counter = g.done_gemm2;
     ga.ret.rank = g.rank; ga.ret.world = g.world; ga.ret.epoch = g.epoch;
 
@@ -324,6 +346,15 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed) {
     g1.A = g.arena + g.lay.xcell; g1.B = s.W1; g1.bias = s.b1; g1.N = c.I; g1.Kd = c.H; g1.mode = 0;
     GemmArgs g2 = ga;
     g2.A = g.y1; g2.B = s.W2; g2.bias = s.b2; g2.N = c.H; g2.Kd = c.I; g2.mode = 1;
+    // before GEMM1 of part p > 0: wait for that part's rows and extend the plan
+    auto next_part = [&](int p) -> int {
+        if (p == 0 || fused) return KLEOS_OK;
+        KLEOS_CUDA(cudaStreamWaitEvent(st, g.ev_part[p], 0));
+        pa.le_begin = p * g.nLx / parts;
+        pa.le_end = (p + 1) * g.nLx / parts;
+        plan_kernel<<<1, 1024, 0, st>>>(pa);
+        return KLEOS_OK;
+    };
     if (g.gemm_stats) {
         g1.stats = g.gemm_stats;
         g2.stats = g.gemm_stats + (size_t)g.sm_count * kStatSlots;
@@ -343,26 +374,41 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed) {
                         ffn_gemm_tc2<0, true><<<grid, thr, gemm_tc2::SMEM_BYTES, st>>>(g.map_x, g.map_w1h, g1, fa);
                     else
                         ffn_gemm_tc2<1, true><<<grid, thr, gemm_tc2::SMEM_BYTES, st>>>(g.map_x, g.map_w1h, g1, fa);
-                } else if (c.hidden_act == 0) {
-                    ffn_gemm_tc2<0, false><<<grid, 256, gemm_tc2::SMEM_BYTES, st>>>(g.map_x, g.map_w1h, g1, fa);
-                } else {
-                    ffn_gemm_tc2<1, false><<<grid, 256, gemm_tc2::SMEM_BYTES, st>>>(g.map_x, g.map_w1h, g1, fa);
+                }
+                for (int p = 0; p < parts && !fused; ++p) {
+                    if ((rc = next_part(p))) return rc;
+                    g1.le_begin = p * g.nLx / parts;
+                    g1.le_end = (p + 1) * g.nLx / parts;
+                    if (c.hidden_act == 0)
+                        ffn_gemm_tc2<0, false><<<grid, 256, gemm_tc2::SMEM_BYTES, st>>>(g.map_x, g.map_w1h, g1, fa);
+                    else
+                        ffn_gemm_tc2<1, false><<<grid, 256, gemm_tc2::SMEM_BYTES, st>>>(g.map_x, g.map_w1h, g1, fa);
                 }
                 KLEOS_CUDA(mark());
                 ffn_gemm_tc2<2, false><<<grid, 256, gemm_tc2::SMEM_BYTES, st>>>(g.map_y1, g.map_w2h, g2, fa);
                 KLEOS_CUDA(mark());
             } else {
-                if (c.hidden_act == 0)
-                    ffn_gemm_tc<0><<<g.sm_count, 256, gemm_tc::SMEM_BYTES, st>>>(g.map_x, g.map_w1, g1);
-                else
-                    ffn_gemm_tc<1><<<g.sm_count, 256, gemm_tc::SMEM_BYTES, st>>>(g.map_x, g.map_w1, g1);
+                for (int p = 0; p < parts; ++p) {
+                    if ((rc = next_part(p))) return rc;
+                    g1.le_begin = p * g.nLx / parts;
+                    g1.le_end = (p + 1) * g.nLx / parts;
+                    if (c.hidden_act == 0)
+                        ffn_gemm_tc<0><<<g.sm_count, 256, gemm_tc::SMEM_BYTES, st>>>(g.map_x, g.map_w1, g1);
+                    else
+                        ffn_gemm_tc<1><<<g.sm_count, 256, gemm_tc::SMEM_BYTES, st>>>(g.map_x, g.map_w1, g1);
+                }
                 KLEOS_CUDA(mark());
                 ffn_gemm_tc<2><<<g.sm_count, 256, gemm_tc::SMEM_BYTES, st>>>(g.map_y1, g.map_w2, g2);
                 KLEOS_CUDA(mark());
             }
         }
     } else {
-        ffn_gemm_simt<T><<<g.sm_count * 2, 256, 0, st>>>(g1);
+        for (int p = 0; p < parts; ++p) {
+            if ((rc = next_part(p))) return rc;
+            g1.le_begin = p * g.nLx / parts;
+            g1.le_end = (p + 1) * g.nLx / parts;
+            ffn_gemm_simt<T><<<g.sm_count * 2, 256, 0, st>>>(g1);
+        }
         KLEOS_CUDA(mark());
         ffn_gemm_simt<T><<<g.sm_count * 2, 256, 0, st>>>(g2);
         KLEOS_CUDA(mark());
@@ -397,11 +443,15 @@ void release_all() {
         if (g.peer_opened[r]) cudaIpcCloseMemHandle(g.peers.arena[r]);
     cudaFree(g.arena);
     cudaFree(g.y1); cudaFree(g.topk); cudaFree(g.slots); cudaFree(g.cell_tokens);
-    cudaFree(g.refine_list); cudaFree(g.refine_count); cudaFree(g.refine_done); cudaFree(g.refine_logits); cudaFree(g.le_start); cudaFree(g.mcw);
+    cudaFree(g.refine_list); cudaFree(g.refine_count); cudaFree(g.tile_hist); cudaFree(g.refine_done); cudaFree(g.refine_logits); cudaFree(g.le_start); cudaFree(g.mcw);
     cudaFree(g.bias); cudaFree(g.counts); cudaFree(g.done_dispatch); cudaFree(g.done_gemm2);
     cudaFree(g.cell_counts); cudaFree(g.cell_done); cudaFree(g.panels); cudaFree(g.status); cudaFree(g.gemm_stats);
     for (auto& e : g.ev)
         if (e) cudaEventDestroy(e);
+    for (auto& e : g.ev_part)
+        if (e) cudaEventDestroy(e);
+    if (g.ev_slots) cudaEventDestroy(g.ev_slots);
+    if (g.copy_stream) cudaStreamDestroy(g.copy_stream);
     if (g.comm && nccl.CommDestroy) nccl.CommDestroy(g.comm);
     g = State();
 }
@@ -520,6 +570,7 @@ int kleos_initialize(const char* config_json_path, int rank, int world, const vo
     if ((rc = dev_alloc(&g.cell_tokens, (size_t)cfg.E * cfg.pEC))) return rc;
     if ((rc = dev_alloc(&g.refine_list, (size_t)cfg.S))) return rc;
     if ((rc = dev_alloc(&g.refine_count, 1))) return rc;
+    if ((rc = dev_alloc(&g.tile_hist, (size_t)((cfg.S + kSlotTile - 1) / kSlotTile) * cfg.E))) return rc;
     if ((rc = dev_alloc(&g.refine_done, (size_t)cfg.S))) return rc;
     if ((rc = dev_alloc(&g.refine_logits, (size_t)cfg.S * cfg.E))) return rc;
     if ((rc = dev_alloc(&g.le_start, (size_t)g.nLx + 1))) return rc;
@@ -533,6 +584,10 @@ int kleos_initialize(const char* config_json_path, int rank, int world, const vo
     if ((rc = dev_alloc(&g.panels, (size_t)cfg.E * cfg.pEC / kTileM))) return rc;
     if ((rc = dev_alloc(&g.status, 1))) return rc;
     for (auto& e : g.ev) KLEOS_CUDA(cudaEventCreate(&e));
+    KLEOS_CUDA(cudaStreamCreateWithFlags(&g.copy_stream, cudaStreamNonBlocking));
+    KLEOS_CUDA(cudaEventCreateWithFlags(&g.ev_slots, cudaEventDisableTiming));
+    for (auto& e : g.ev_part) KLEOS_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    if (const char* pp = std::getenv("KLEOS_PIPE")) g.pipe_parts = std::max(1, std::atoi(pp));
     if (const char* gs = std::getenv("KLEOS_GEMM_STATS"))
         if (gs[0] == '1' && (rc = dev_alloc(&g.gemm_stats, (size_t)2 * g.sm_count * kStatSlots))) return rc;
 

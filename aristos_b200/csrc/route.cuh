@@ -296,6 +296,7 @@ struct SlotArgs {
     int* slots;             // [S,K] slot or kDropped
     int* cell_tokens;       // [E,pEC] token id held by each slot
     unsigned* counts;       // [E] unclamped
+    int* tile_hist;         // [tiles, E] per-tile histogram of the chosen experts
     int S, K, E, EC, pEC;
     // count flags: cflag[owner][rank*nLx + le] = (epoch<<32)|routed, one 8-byte peer store per
     // expert (the reference's first-stage signal carries the same count, types.cuh:300-317)
@@ -305,51 +306,64 @@ struct SlotArgs {
     uint32_t epoch;
 };
 
-// One block per expert; slots in ascending token order.
+// Slots in ascending token order (the reference hands them out in atomicAdd arrival order,
+// moe/gate.cuh:689-718; ascending order is one of its possible outcomes and is reproducible).
+// Two small launches over tiles of 128 tokens:
+//   tile_hist_kernel  per-tile histogram of the chosen experts;
+//   slot_kernel       base slot of every expert for the tile = sum of the earlier tiles'
+//                     histograms, then each token's rank inside the tile; the last block also
+//                     has the totals and publishes them: counts[e] and one count flag per
+//                     expert to the expert's owner rank.
+constexpr int kSlotTile = 128;
+
+__global__ void __launch_bounds__(256) tile_hist_kernel(SlotArgs a) {
+    __shared__ int hist[256];  // E <= 256
+    const int tid = threadIdx.x, tok0 = blockIdx.x * kSlotTile;
+    for (int e = tid; e < a.E; e += blockDim.x) hist[e] = 0;
+    __syncthreads();
+    const int n_own = min(kSlotTile, a.S - tok0) * a.K;
+    for (int i = tid; i < n_own; i += blockDim.x) atomicAdd(&hist[a.topk[(size_t)tok0 * a.K + i]], 1);
+    __syncthreads();
+    for (int e = tid; e < a.E; e += blockDim.x) a.tile_hist[(size_t)blockIdx.x * a.E + e] = hist[e];
+}
+
 __global__ void __launch_bounds__(256) slot_kernel(SlotArgs a) {
-    __shared__ int warp_sums[8];
-    __shared__ int base_s;
-    const int e = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int chunk = (a.S + 255) / 256;
-    const int t0 = tid * chunk, t1 = min(a.S, t0 + chunk);
-    int mine = 0;
-    for (int t = t0; t < t1; ++t)
-        for (int j = 0; j < a.K; ++j) mine += (a.topk[(size_t)t * a.K + j] == e);
-    int incl = mine;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const int v = __shfl_up_sync(0xffffffffu, incl, o);
-        if (lane >= o) incl += v;
-    }
-    if (lane == 31) warp_sums[warp] = incl;
-    __syncthreads();
-    if (tid == 0) {
+    __shared__ int base[256];
+    __shared__ int sel_s[kSlotTile * kMaxTopK];
+    const int tid = threadIdx.x, b = blockIdx.x;
+    const int tok0 = b * kSlotTile;
+    const bool last = b == (int)gridDim.x - 1;
+    for (int e = tid; e < a.E; e += blockDim.x) {
         int run = 0;
-        for (int w = 0; w < 8; ++w) {
-            const int v = warp_sums[w];
-            warp_sums[w] = run;
-            run += v;
+        for (int t = 0; t < b; ++t) run += a.tile_hist[(size_t)t * a.E + e];
+        base[e] = run;
+        if (last) {
+            const int total = run + a.tile_hist[(size_t)b * a.E + e];
+            a.counts[e] = (unsigned)total;
+            const int owner = e / a.nLx, le = e - owner * a.nLx;
+            st_release_sys(reinterpret_cast<unsigned long long*>(a.peer_arena[owner] + a.cflag_offset) +
+                               ((size_t)a.rank * a.nLx + le),
+                           make_flag(a.epoch, (unsigned)min(total, a.EC)));
         }
-        base_s = run;
-        a.counts[e] = (unsigned)run;
-        const int owner = e / a.nLx, le = e - owner * a.nLx;
-        st_release_sys(reinterpret_cast<unsigned long long*>(a.peer_arena[owner] + a.cflag_offset) +
-                           ((size_t)a.rank * a.nLx + le),
-                       make_flag(a.epoch, (unsigned)min(run, a.EC)));
     }
+    const int n_own = min(kSlotTile, a.S - tok0) * a.K;
+    for (int i = tid; i < kSlotTile * a.K; i += blockDim.x)
+        sel_s[i] = i < n_own ? a.topk[(size_t)tok0 * a.K + i] : -1;
     __syncthreads();
-    int pos = warp_sums[warp] + incl - mine;
-    for (int t = t0; t < t1; ++t)
-        for (int j = 0; j < a.K; ++j)
-            if (a.topk[(size_t)t * a.K + j] == e) {
-                if (pos < a.EC) {
-                    a.slots[(size_t)t * a.K + j] = pos;
-                    a.cell_tokens[(size_t)e * a.pEC + pos] = t;
-                } else {
-                    a.slots[(size_t)t * a.K + j] = kDropped;
-                }
-                ++pos;
+    if (tid < kSlotTile && tok0 + tid < a.S) {
+        for (int j = 0; j < a.K; ++j) {
+            const int e = sel_s[tid * a.K + j];
+            int rank = 0;
+            for (int i = 0; i < tid * a.K; ++i) rank += (sel_s[i] == e);
+            const int pos = base[e] + rank;
+            if (pos < a.EC) {
+                a.slots[(size_t)(tok0 + tid) * a.K + j] = pos;
+                a.cell_tokens[(size_t)e * a.pEC + pos] = tok0 + tid;
+            } else {
+                a.slots[(size_t)(tok0 + tid) * a.K + j] = kDropped;
             }
+        }
+    }
 }
 
 }  // namespace kleos

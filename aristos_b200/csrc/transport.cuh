@@ -34,6 +34,7 @@ struct DispatchArgs {
     int H, E, EC, pEC, nLx, rank, world;
     uint32_t epoch;
     int elem_bytes;
+    int le_begin, le_end;      // only experts whose local index is in [le_begin, le_end) are moved
 };
 
 // Warp per routed row; rows are spread over the whole grid.
@@ -41,11 +42,18 @@ __global__ void __launch_bounds__(256) dispatch_kernel(DispatchArgs a) {
     __shared__ unsigned prefix[257];  // E <= 256
     __shared__ bool last_block;
     const int tid = threadIdx.x;
+    // routed rows per expert (zero outside this launch's local-expert range), then their prefix
+    for (int e = tid; e < a.E; e += blockDim.x) {
+        const int le = e % a.nLx;
+        prefix[e + 1] = (le >= a.le_begin && le < a.le_end) ? min(a.counts[e], (unsigned)a.EC) : 0u;
+    }
+    __syncthreads();
     if (tid == 0) {
         unsigned run = 0;
         for (int e = 0; e < a.E; ++e) {
+            const unsigned n = prefix[e + 1];
             prefix[e] = run;
-            run += min(a.counts[e], (unsigned)a.EC);
+            run += n;
         }
         prefix[a.E] = run;
     }
@@ -83,6 +91,7 @@ __global__ void __launch_bounds__(256) dispatch_kernel(DispatchArgs a) {
         __threadfence_system();
         for (int e = tid; e < a.E; e += blockDim.x) {
             const int owner = e / a.nLx, le = e - owner * a.nLx;
+            if (le < a.le_begin || le >= a.le_end) continue;
             unsigned long long* f = reinterpret_cast<unsigned long long*>(
                 a.peers.arena[owner] + a.lay.xflag) + ((size_t)a.rank * a.nLx + le);
             st_release_sys(f, make_flag(a.epoch, min(a.counts[e], (unsigned)a.EC)));
@@ -109,42 +118,58 @@ struct PlanArgs {
     int world, nLx, pEC;
     uint32_t epoch;
     long long wait_cycles;
+    int le_begin, le_end;    // local experts planned by this launch; panels are appended
 };
 
 // Single block.  Waits (bounded) for the count flag of every (source, local expert) cell, then
 // lists the panels grouped by local expert so that tiles sharing a weight tile run together.
 __global__ void __launch_bounds__(1024) plan_kernel(PlanArgs a) {
     __shared__ int failed;
+    __shared__ unsigned short cnt_s[2048];  // world * nLx <= 8 * 256
     const int cells = a.world * a.nLx;
     if (threadIdx.x == 0) failed = 0;
     __syncthreads();
     const unsigned long long* flags =
         reinterpret_cast<const unsigned long long*>(a.arena + a.lay.xflag);
     for (int c = threadIdx.x; c < cells; c += blockDim.x) {
+        const int cle = c % a.nLx;
+        if (cle < a.le_begin || cle >= a.le_end) continue;
         unsigned long long v = 0;
         if (!wait_flag(flags + c, a.epoch, a.wait_cycles, &v)) {
             report_error(a.status, KLEOS_AT_PLAN_WAIT, c, (int)a.epoch);
             atomicExch(&failed, 1);
             a.cell_counts[c] = 0;
+            cnt_s[c] = 0;
         } else {
-            a.cell_counts[c] = min((unsigned)(v & 0xffffffffu), (unsigned)a.pEC);
+            const unsigned n = min((unsigned)(v & 0xffffffffu), (unsigned)a.pEC);
+            a.cell_counts[c] = n;
+            cnt_s[c] = (unsigned short)n;
         }
     }
-    __threadfence();
     __syncthreads();
+    // plan order: local expert by local expert, sources ascending.  One thread scans the panel
+    // counts of the cells in that order, then every cell writes its own panels.
+    __shared__ int off_s[2049];
+    const int ncell = (a.le_end - a.le_begin) * a.world;
     if (threadIdx.x == 0) {
-        int n = 0;
-        for (int le = 0; le < a.nLx; ++le) {
-            a.le_start[le] = n;
-            if (failed) continue;
-            for (int src = 0; src < a.world; ++src) {
-                const int c = src * a.nLx + le;
-                const int cnt = (int)a.cell_counts[c];
-                for (int r = 0; r < cnt; r += kTileM)
-                    a.panels[n++] = PanelEntry{c * a.pEC + r, min(kTileM, cnt - r), le, src};
-            }
+        int n = a.le_begin == 0 ? 0 : a.le_start[a.le_begin];  // continue the previous launch's list
+        for (int o = 0; o < ncell; ++o) {
+            const int le = a.le_begin + o / a.world, src = o % a.world;
+            if (src == 0) a.le_start[le] = n;
+            off_s[o] = n;
+            if (!failed) n += (cnt_s[src * a.nLx + le] + kTileM - 1) / kTileM;
         }
-        a.le_start[a.nLx] = n;
+        a.le_start[a.le_end] = n;
+    }
+    __syncthreads();
+    if (failed) return;
+    for (int o = threadIdx.x; o < ncell; o += blockDim.x) {
+        const int le = a.le_begin + o / a.world, src = o % a.world;
+        const int c = src * a.nLx + le;
+        const int cnt = cnt_s[c];
+        int n = off_s[o];
+        for (int r = 0; r < cnt; r += kTileM)
+            a.panels[n++] = PanelEntry{c * a.pEC + r, min(kTileM, cnt - r), le, src};
     }
 }
 
