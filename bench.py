@@ -289,10 +289,28 @@ def run_cuda(args):
         dist.all_reduce(pairs)
     pairs_per_rank = float(pairs.item()) / world
     peaks = load_peaks()
-    gemm_flops = 2.0 * pairs_per_rank * cfg.H * cfg.I  # one of the two FFN GEMM launches
+    # dominant kernel: one FFN GEMM launch (GEMM1 and GEMM2 do the same work when H == I).
+    # Algorithmic work per launch: 2*R*H*I FLOP; bytes = this rank's expert weights once, the
+    # R operand rows in and the R result rows out (R = routed pairs this rank's experts process).
+    gemm_flops = 2.0 * pairs_per_rank * cfg.H * cfg.I
+    gemm_bytes = (info.local_experts * cfg.I * cfg.H + pairs_per_rank * (cfg.H + cfg.I)) * 2.0
     gemm_ms = 0.5 * (phases["gemm1"] + phases["gemm2"])
     gemm_ms = max_over_ranks(gemm_ms)
-    achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12
+    tflops = gemm_flops / (gemm_ms * 1e-3) / 1e12
+    gbs = gemm_bytes / (gemm_ms * 1e-3) / 1e9
+    hbm_bound = gemm_bytes / (peaks["hbm"] * 1e9) > gemm_flops / (peaks["tflops"] * 1e12)
+    if hbm_bound:
+        roof = dict(bound="hbm", achieved=gbs, peak=peaks["hbm"], unit="GB/s", frac=gbs / peaks["hbm"])
+    else:
+        roof = dict(bound="tensor", achieved=tflops, peak=peaks["tflops"], unit="TFLOP/s",
+                    frac=tflops / peaks["tflops"])
+    # DRAM traffic per launch from the ncu capture of the quarter-size layer (155.3 MB, see
+    # profiles/), scaled by the units processed (experts x4, routed rows x4); one-GPU C3 only
+    roof["traffic"] = 621.2e6 if (world == 1 and args.workload == "C3") else None
+    roof.update(kernel="ffn_gemm_tc2 (mean of the GEMM1 and GEMM2 launches)",
+                peak_source=peaks["source"], tensor_tflops=tflops, hbm_gbs=gbs,
+                algorithmic_bytes=gemm_bytes, algorithmic_flops=gemm_flops,
+                launch_ms=gemm_ms)
     total_flops = 2.0 * cfg.S * cfg.H * cfg.E + 4.0 * cfg.H * cfg.I * pairs_per_rank
     remote_pairs = pairs_per_rank * (world - 1) / world
     link_bytes = 2.0 * remote_pairs * cfg.H * 2
@@ -313,10 +331,7 @@ def run_cuda(args):
                      h2d_bytes_per_step=act_elems * 2, d2h_bytes_per_step=act_elems * 2),
             gpu_launches=KERNELS_PER_FORWARD * args.steps,
             clocks=clocks,
-            roofline=dict(bound="tensor", achieved=achieved, peak=peaks["tflops"], unit="TFLOP/s",
-                          frac=achieved / peaks["tflops"], traffic=None,
-                          kernel="ffn_gemm_tc (mean of the GEMM1 and GEMM2 launches)",
-                          peak_source=peaks["source"]),
+            roofline=roof,
             layer_roofline=dict(t_roof_ms=t_roof_ms, frac=t_roof_ms / ms_per_step,
                                 flops=total_flops, link_bytes_each_way=link_bytes),
             phases_ms=phases,
