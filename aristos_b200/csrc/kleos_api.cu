@@ -78,6 +78,18 @@ struct State {
     const void* maps_for_iP = nullptr;
     CUtensorMap map_x{}, map_w1{}, map_y1{}, map_w2{}, map_act{}, map_wg{}, map_w1h{}, map_w2h{};
 
+    // pipelined host-buffer path (kleos_forward_host_async): double-buffered staging of the
+    // activations and of the layer output, one stream per direction
+    struct HostPipe {
+        bool ready = false;
+        cudaStream_t in = nullptr, out = nullptr;
+        char* act[2] = {};
+        char* res[2] = {};
+        CUtensorMap map_act[2] = {};
+        cudaEvent_t in_done[2] = {}, comp_done[2] = {}, out_done[2] = {};
+        unsigned long long step = 0;
+    } hp;
+
     ncclComm_t comm = nullptr;
     cudaEvent_t ev[kPhases + 1] = {};
     float phase_ms[kPhases] = {};
@@ -248,12 +260,26 @@ int launch_route(const RouteArgs& ra, cudaStream_t st) {
     return KLEOS_OK;
 }
 
+// Optional replacement of the activation input and the layer-output destination of one
+// forward (used by the pipelined host path, whose staging buffers live outside iP / oP).
+struct Staging {
+    const char* A;
+    char* out;
+    const CUtensorMap* map_act;
+};
+
 template <typename T>
-int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed) {
+int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed, const Staging* stg) {
     const LayerConfig& c = g.cfg;
-    const Sections s = slice(iP, oP);
+    Sections s = slice(iP, oP);
     int rc = ensure_maps(s);
     if (rc) return rc;
+    const CUtensorMap* act_map = &g.map_act;
+    if (stg) {
+        s.A = stg->A;
+        s.out = stg->out;
+        act_map = stg->map_act;
+    }
     g.epoch += 1;
     int evi = 0;
     auto mark = [&]() -> cudaError_t { return timed ? cudaEventRecord(g.ev[evi++], st) : cudaSuccess; };
@@ -271,10 +297,10 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed) {
             const int grid = (c.S + route_tc::BM - 1) / route_tc::BM;
             if (c.PX == 64)
                 route_tc_kernel<64><<<grid, 256, route_tc::Shape<64>::SMEM_BYTES, st>>>(
-                    g.map_act, g.map_wg, ra, g.status, g.wait_cycles, (int)g.epoch);
+                    *act_map, g.map_wg, ra, g.status, g.wait_cycles, (int)g.epoch);
             else
                 route_tc_kernel<128><<<grid, 256, route_tc::Shape<128>::SMEM_BYTES, st>>>(
-                    g.map_act, g.map_wg, ra, g.status, g.wait_cycles, (int)g.epoch);
+                    *act_map, g.map_wg, ra, g.status, g.wait_cycles, (int)g.epoch);
             refine_kernel<T><<<148, 256, 0, st>>>(ra);
         }
     } else if ((rc = launch_route<T>(ra, st))) {
@@ -307,7 +333,7 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed) {
     PlanArgs pa{};
     pa.arena = g.arena; pa.lay = g.lay; pa.panels = g.panels; pa.le_start = g.le_start;
     pa.cell_counts = g.cell_counts; pa.status = g.status; pa.world = g.world; pa.nLx = g.nLx;
-    pa.pEC = c.pEC; pa.epoch = g.epoch; pa.wait_cycles = g.wait_cycles;
+    pa.pEC = c.pEC; pa.epoch = g.epoch; pa.wait_cycles = g.wait_cycles; pa.rank = g.rank;
     if (!fused) {
         // 3. dispatch, all parts queued on the copy stream behind the slot kernel
         cudaStream_t cs = parts > 1 ? g.copy_stream : st;
@@ -431,11 +457,33 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed) {
     return KLEOS_OK;
 }
 
-int forward_any(const void* iP, void* oP, cudaStream_t st, bool timed) {
+int forward_any(const void* iP, void* oP, cudaStream_t st, bool timed, const Staging* stg = nullptr) {
     if (!g.initialised) return fail(KLEOS_E_STATE, "kleos_forward before kleos_initialize");
     if (!iP || !oP) return fail(KLEOS_E_ARG, "null buffer");
-    if (g.cfg.torch_dtype == 0) return forward_typed<float>(iP, oP, st, timed);
-    return forward_typed<__nv_bfloat16>(iP, oP, st, timed);
+    if (g.cfg.torch_dtype == 0) return forward_typed<float>(iP, oP, st, timed, stg);
+    return forward_typed<__nv_bfloat16>(iP, oP, st, timed, stg);
+}
+
+int ensure_host_pipe() {
+    State::HostPipe& hp = g.hp;
+    if (hp.ready) return KLEOS_OK;
+    const LayerConfig& c = g.cfg;
+    const size_t bytes = (size_t)c.S * c.H * c.elem_bytes;
+    KLEOS_CUDA(cudaStreamCreateWithFlags(&hp.in, cudaStreamNonBlocking));
+    KLEOS_CUDA(cudaStreamCreateWithFlags(&hp.out, cudaStreamNonBlocking));
+    for (int b = 0; b < 2; ++b) {
+        KLEOS_CUDA(cudaMalloc(reinterpret_cast<void**>(&hp.act[b]), bytes));
+        KLEOS_CUDA(cudaMalloc(reinterpret_cast<void**>(&hp.res[b]), bytes));
+        KLEOS_CUDA(cudaEventCreateWithFlags(&hp.in_done[b], cudaEventDisableTiming));
+        KLEOS_CUDA(cudaEventCreateWithFlags(&hp.comp_done[b], cudaEventDisableTiming));
+        KLEOS_CUDA(cudaEventCreateWithFlags(&hp.out_done[b], cudaEventDisableTiming));
+        if (g.use_tc && c.PX <= 128) {
+            int rc = make_map(&hp.map_act[b], hp.act[b], c.S, c.H, route_tc::BM);
+            if (rc) return rc;
+        }
+    }
+    hp.ready = true;
+    return KLEOS_OK;
 }
 
 void release_all() {
@@ -450,6 +498,13 @@ void release_all() {
         if (e) cudaEventDestroy(e);
     for (auto& e : g.ev_part)
         if (e) cudaEventDestroy(e);
+    if (g.hp.ready) {
+        for (int b = 0; b < 2; ++b) {
+            cudaFree(g.hp.act[b]); cudaFree(g.hp.res[b]);
+            cudaEventDestroy(g.hp.in_done[b]); cudaEventDestroy(g.hp.comp_done[b]); cudaEventDestroy(g.hp.out_done[b]);
+        }
+        cudaStreamDestroy(g.hp.in); cudaStreamDestroy(g.hp.out);
+    }
     if (g.ev_slots) cudaEventDestroy(g.ev_slots);
     if (g.copy_stream) cudaStreamDestroy(g.copy_stream);
     if (g.comm && nccl.CommDestroy) nccl.CommDestroy(g.comm);
@@ -720,6 +775,46 @@ int kleos_forward_host(const void* host_activations, void* iP, void* oP, void* h
     const char* out = static_cast<const char*>(oP) + (size_t)c.S * c.PX * c.elem_bytes;
     KLEOS_CUDA(cudaMemcpyAsync(host_output, out, act_bytes, cudaMemcpyDeviceToHost, st));
     KLEOS_CUDA(cudaStreamSynchronize(st));
+    return KLEOS_OK;
+}
+
+int kleos_forward_host_async(const void* host_activations, void* iP, void* oP, void* host_output) {
+    if (!g.initialised) return fail(KLEOS_E_STATE, "not initialised");
+    if (!host_activations || !iP || !oP || !host_output) return fail(KLEOS_E_ARG, "null buffer");
+    int rc = ensure_host_pipe();
+    if (rc) return rc;
+    State::HostPipe& hp = g.hp;
+    const LayerConfig& c = g.cfg;
+    const size_t bytes = (size_t)c.S * c.H * c.elem_bytes;
+    cudaStream_t st = cudaStreamPerThread;
+    const int b = (int)(hp.step & 1);
+    const bool reuse = hp.step >= 2;  // the step that last used these staging buffers
+    if (reuse) KLEOS_CUDA(cudaStreamWaitEvent(hp.in, hp.comp_done[b], 0));
+    KLEOS_CUDA(cudaMemcpyAsync(hp.act[b], host_activations, bytes, cudaMemcpyHostToDevice, hp.in));
+    KLEOS_CUDA(cudaEventRecord(hp.in_done[b], hp.in));
+    KLEOS_CUDA(cudaStreamWaitEvent(st, hp.in_done[b], 0));
+    if (reuse) KLEOS_CUDA(cudaStreamWaitEvent(st, hp.out_done[b], 0));
+    const Staging stg{hp.act[b], hp.res[b], &hp.map_act[b]};
+    if ((rc = forward_any(iP, oP, st, false, &stg))) return rc;
+    KLEOS_CUDA(cudaEventRecord(hp.comp_done[b], st));
+    KLEOS_CUDA(cudaStreamWaitEvent(hp.out, hp.comp_done[b], 0));
+    KLEOS_CUDA(cudaMemcpyAsync(host_output, hp.res[b], bytes, cudaMemcpyDeviceToHost, hp.out));
+    KLEOS_CUDA(cudaEventRecord(hp.out_done[b], hp.out));
+    hp.step += 1;
+    return KLEOS_OK;
+}
+
+int kleos_host_sync(void) {
+    if (!g.initialised) return fail(KLEOS_E_STATE, "not initialised");
+    if (g.hp.ready) {
+        KLEOS_CUDA(cudaStreamSynchronize(g.hp.in));
+        KLEOS_CUDA(cudaStreamSynchronize(cudaStreamPerThread));
+        KLEOS_CUDA(cudaStreamSynchronize(g.hp.out));
+    }
+    kleos_status s;
+    int rc = kleos_last_status(&s);
+    if (rc) return rc;
+    if (s.code) return fail(KLEOS_E_DEVICE, "device status: where=%d detail=%d epoch=%d", s.where, s.detail, s.epoch);
     return KLEOS_OK;
 }
 

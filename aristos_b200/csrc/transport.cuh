@@ -42,10 +42,14 @@ __global__ void __launch_bounds__(256) dispatch_kernel(DispatchArgs a) {
     __shared__ unsigned prefix[257];  // E <= 256
     __shared__ bool last_block;
     const int tid = threadIdx.x;
-    // routed rows per expert (zero outside this launch's local-expert range), then their prefix
-    for (int e = tid; e < a.E; e += blockDim.x) {
-        const int le = e % a.nLx;
-        prefix[e + 1] = (le >= a.le_begin && le < a.le_end) ? min(a.counts[e], (unsigned)a.EC) : 0u;
+    // Rows are sent in this order: local expert index first, and for each of them the owner
+    // ranks starting with the one after this rank.  At any moment the source ranks therefore
+    // write to DIFFERENT owners, instead of all pushing into the same GPU's NVLink ingress.
+    // prefix[i] = rows before order position i (zero-length outside this launch's range).
+    for (int i = tid; i < a.E; i += blockDim.x) {
+        const int le = i / a.world, owner = (a.rank + 1 + i % a.world) % a.world;
+        const int e = owner * a.nLx + le;
+        prefix[i + 1] = (le >= a.le_begin && le < a.le_end) ? min(a.counts[e], (unsigned)a.EC) : 0u;
     }
     __syncthreads();
     if (tid == 0) {
@@ -63,14 +67,14 @@ __global__ void __launch_bounds__(256) dispatch_kernel(DispatchArgs a) {
     const unsigned warps = gridDim.x * (blockDim.x >> 5);
     const unsigned row_chunks = (unsigned)((size_t)a.H * a.elem_bytes / 16);
     for (unsigned g = blockIdx.x * (blockDim.x >> 5) + (tid >> 5); g < total; g += warps) {
-        int lo = 0, hi = a.E;  // last e with prefix[e] <= g
+        int lo = 0, hi = a.E;  // last order position with prefix[] <= g
         while (hi - lo > 1) {
             const int mid = (lo + hi) >> 1;
             if (prefix[mid] <= g) lo = mid; else hi = mid;
         }
-        const int e = lo;
-        const unsigned slot = g - prefix[e];
-        const int owner = e / a.nLx, le = e - owner * a.nLx;
+        const unsigned slot = g - prefix[lo];
+        const int le = lo / a.world, owner = (a.rank + 1 + lo % a.world) % a.world;
+        const int e = owner * a.nLx + le;
         const int tok = a.cell_tokens[(size_t)e * a.pEC + slot];
         const uint4* src = reinterpret_cast<const uint4*>(
             static_cast<const char*>(a.A) + (size_t)tok * a.H * a.elem_bytes);
@@ -119,6 +123,7 @@ struct PlanArgs {
     uint32_t epoch;
     long long wait_cycles;
     int le_begin, le_end;    // local experts planned by this launch; panels are appended
+    int rank;
 };
 
 // Single block.  Waits (bounded) for the count flag of every (source, local expert) cell, then
@@ -147,15 +152,17 @@ __global__ void __launch_bounds__(1024) plan_kernel(PlanArgs a) {
         }
     }
     __syncthreads();
-    // plan order: local expert by local expert, sources ascending.  One thread scans the panel
-    // counts of the cells in that order, then every cell writes its own panels.
+    // plan order: local expert by local expert, sources starting with the rank after this one
+    // (so that the expert ranks' result stores fan out over different source ranks instead of
+    // converging on one).  One thread scans the panel counts of the cells in that order, then
+    // every cell writes its own panels.
     __shared__ int off_s[2049];
     const int ncell = (a.le_end - a.le_begin) * a.world;
     if (threadIdx.x == 0) {
         int n = a.le_begin == 0 ? 0 : a.le_start[a.le_begin];  // continue the previous launch's list
         for (int o = 0; o < ncell; ++o) {
-            const int le = a.le_begin + o / a.world, src = o % a.world;
-            if (src == 0) a.le_start[le] = n;
+            const int le = a.le_begin + o / a.world, src = (a.rank + 1 + o % a.world) % a.world;
+            if (o % a.world == 0) a.le_start[le] = n;
             off_s[o] = n;
             if (!failed) n += (cnt_s[src * a.nLx + le] + kTileM - 1) / kTileM;
         }
@@ -164,7 +171,7 @@ __global__ void __launch_bounds__(1024) plan_kernel(PlanArgs a) {
     __syncthreads();
     if (failed) return;
     for (int o = threadIdx.x; o < ncell; o += blockDim.x) {
-        const int le = a.le_begin + o / a.world, src = o % a.world;
+        const int le = a.le_begin + o / a.world, src = (a.rank + 1 + o % a.world) % a.world;
         const int c = src * a.nLx + le;
         const int cnt = cnt_s[c];
         int n = off_s[o];

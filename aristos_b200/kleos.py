@@ -24,7 +24,8 @@ LIB_PATH = os.path.join(_HERE, "libkleos_b200.so")
 
 EXPORTS = (
     "kleos_get_unique_id", "kleos_config_probe", "kleos_set_device", "kleos_initialize", "kleos_set_gate_bias",
-    "kleos_forward", "kleos_forward_bench", "kleos_forward_host", "kleos_get_rank",
+    "kleos_forward", "kleos_forward_bench", "kleos_forward_host", "kleos_forward_host_async",
+    "kleos_host_sync", "kleos_get_rank",
     "kleos_local_experts", "kleos_get_info", "kleos_last_status", "kleos_debug_routing",
     "kleos_phase_times", "kleos_debug_gemm_stats", "kleos_route_static", "kleos_finalize", "kleos_error_string",
 )
@@ -68,6 +69,7 @@ def load_library() -> ctypes.CDLL:
         lib.kleos_forward_bench.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int,
                                             ctypes.c_int, ctypes.POINTER(ctypes.c_float)]
         lib.kleos_forward_host.argtypes = [ctypes.c_void_p] * 4
+        lib.kleos_forward_host_async.argtypes = [ctypes.c_void_p] * 4
         lib.kleos_set_gate_bias.argtypes = [ctypes.c_void_p, ctypes.c_int]
         lib.kleos_debug_routing.argtypes = [ctypes.c_void_p] * 4
         lib.kleos_phase_times.argtypes = [ctypes.POINTER(ctypes.c_float), ctypes.c_int]
@@ -163,6 +165,17 @@ def forward_from_host(host_activations, iP, oP, host_output) -> None:
     """End-to-end step with host buffers: H2D activations, forward, D2H layer output, sync."""
     _check(load_library().kleos_forward_host(_ptr(host_activations), _ptr(iP), _ptr(oP),
                                              _ptr(host_output)), "kleos_forward_host")
+
+
+def forward_from_host_async(host_activations, iP, oP, host_output) -> None:
+    """Queue one end-to-end step (H2D, forward, D2H on three streams); see host_sync()."""
+    _check(load_library().kleos_forward_host_async(_ptr(host_activations), _ptr(iP), _ptr(oP),
+                                                   _ptr(host_output)), "kleos_forward_host_async")
+
+
+def host_sync() -> None:
+    """Wait for every queued end-to-end step and raise on a device-side error."""
+    _check(load_library().kleos_host_sync(), "kleos_host_sync")
 
 
 def phase_times() -> dict:

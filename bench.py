@@ -267,12 +267,16 @@ def run_cuda(args):
     host_in = torch.empty(act_elems, dtype=torch.bfloat16).pin_memory()
     host_in.copy_(iP[:act_elems].cpu())
     host_out = torch.empty(act_elems, dtype=torch.bfloat16).pin_memory()
-    for _ in range(max(1, args.warmup // 2)):
-        kleos.forward_from_host(host_in, iP, oP, host_out)
+    # every step copies its activations from pinned host memory and its layer output back; the
+    # library overlaps the copies of neighbouring steps with the forward (three streams)
+    for _ in range(max(2, args.warmup // 2)):
+        kleos.forward_from_host_async(host_in, iP, oP, host_out)
+    kleos.host_sync()
     barrier()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        kleos.forward_from_host(host_in, iP, oP, host_out)
+        kleos.forward_from_host_async(host_in, iP, oP, host_out)
+    kleos.host_sync()
     barrier()
     e2e_s = max_over_ranks(time.perf_counter() - t0)
     clocks = sampler.stop() if rank == 0 else None

@@ -99,6 +99,15 @@ int kleos_forward_bench(const void* iP, void* oP, int skip, int trials, float* m
  * (main.cu:64-66). */
 int kleos_forward_host(const void* host_activations, void* iP, void* oP, void* host_output);
 
+/* Pipelined form of kleos_forward_host for a stream of batches: returns as soon as the step is
+ * queued.  Activations and layer output are double-buffered inside the library, so the
+ * host->device copy of step i+1 and the device->host copy of step i-1 overlap the forward of
+ * step i (three streams).  host_output of a step is valid after kleos_host_sync(), which also
+ * reports device-side errors.  The gate probabilities still land in oP.  The reference has no
+ * counterpart (its driver copies once and loops on the device, main.cu:64-68). */
+int kleos_forward_host_async(const void* host_activations, void* iP, void* oP, void* host_output);
+int kleos_host_sync(void);
+
 /* Reference: getRank() (bootstrap.cuh:555-559) and hostBookkeeping.nLx (main.cu:22). */
 int kleos_get_rank(void);
 int kleos_local_experts(void);

@@ -89,3 +89,35 @@ def test_against_committed_golden_fixtures(name):
     ref = dict(expect[0])
     ref["margin"] = 1.0  # fixtures were generated from seeds whose margins were checked
     hz.check_against_oracle(cfg, ref, probs, out, routing)
+
+
+@pytest.mark.parametrize("dtype", [2, 0])
+def test_pipelined_host_path_matches_synchronous_path(dtype):
+    """Three queued end-to-end steps with alternating inputs and separate host outputs: each
+    must equal what the synchronous host-buffer call returns for the same input."""
+    import torch
+    from aristos_b200 import kleos
+    cfg = _small(dtype)
+    eb = cfg.elem_bytes
+    raws = [synth.encode(synth.packed_input(cfg, 0, 1, seed=s), dtype) for s in (0, 5)]
+    info = kleos.initialize(cfg, 0, 1)
+    try:
+        iP = torch.from_numpy(raws[0].view(np.uint8).copy()).cuda()
+        oP = torch.zeros(info.output_elems * eb, dtype=torch.uint8, device="cuda")
+        n = cfg.S * cfg.H
+        acts = [np.ascontiguousarray(r[:n]) for r in raws]
+        want = []
+        for a in acts:
+            o = np.zeros(n, dtype=a.dtype)
+            kleos.forward_from_host(a, iP, oP, o)
+            want.append(o)
+        pinned_in = [torch.from_numpy(a.view(np.uint8).copy()).pin_memory() for a in acts]
+        outs = [torch.zeros(n * eb, dtype=torch.uint8).pin_memory() for _ in range(3)]
+        for step, which in enumerate((0, 1, 0)):
+            kleos.forward_from_host_async(pinned_in[which], iP, oP, outs[step])
+        kleos.host_sync()
+        for step, which in enumerate((0, 1, 0)):
+            got = outs[step].numpy().view(acts[0].dtype)
+            assert np.array_equal(got, want[which]), f"step {step}"
+    finally:
+        kleos.finalize()
