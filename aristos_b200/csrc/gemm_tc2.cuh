@@ -51,6 +51,7 @@ constexpr int kFusedThreads = 256;
 constexpr int kDispatchUnit = 8;    // rows a mover copies between two publications
 constexpr int kRowBufBytes = STAGES * STAGE_BYTES;  // a dispatcher block's row buffers: the stage area
 constexpr int kMaxMovers = 8;       // mover warps per dispatcher block
+constexpr int kPubLag = 3;          // a unit is published this many iterations after its stores were issued
 
 
 struct Control {
@@ -71,6 +72,7 @@ struct Control {
     unsigned short own_s[256];               // routed count of this rank's tokens per expert, dispatch order
     unsigned long long mover_bar[kMaxMovers];  // one per dispatch row buffer
     unsigned short poff_s[257];              // first panel of each cell, cells in plan order
+    __align__(16) int4 pend_s[kMaxMovers][kPubLag + 1];  // units whose stores are still in flight
 };
 
 static_assert(sizeof(Control) <= 28672, "control block must fit the shared memory set aside for it");
@@ -501,26 +503,28 @@ ffn_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
             const int dblock = (int)blockIdx.x - ((int)gridDim.x - n_disp);
             const unsigned stride = n_disp * mwarps;
             const unsigned total_units = ctl->prefix_s[f.E];
-            int pend_e = -1, pend_rows = 0, pend_routed = 0, pend_owner = 0, pend_le = 0;
-            auto publish = [&]() {
-                if (lane < kDispatchUnit) bulk_store_wait_all();
+            // Publication lags the stores by kPubLag iterations: by then the unit's bulk stores
+            // have completed (each lane keeps at most kPubLag newer groups in flight), so no
+            // iteration waits for an NVLink round trip.
+            auto publish = [&](int4 d) {
                 __syncwarp();
                 if (lane == 0) {
-                    asm volatile("fence.proxy.async;" ::: "memory");
+                    const int pe = d.x, prow = d.y, prouted = d.z, powner = d.w & 0xff, ple = d.w >> 8;
                     __threadfence_system();
-                    const unsigned prev = atomicAdd(f.cell_done + pend_e, (unsigned)pend_rows);
-                    if ((int)prev + pend_rows == pend_routed) {
+                    const unsigned prev = atomicAdd(f.cell_done + pe, (unsigned)prow);
+                    if ((int)prev + prow == prouted) {
                         __threadfence_system();
-                        f.cell_done[pend_e] = 0u;
+                        f.cell_done[pe] = 0u;
                         unsigned long long* xf = reinterpret_cast<unsigned long long*>(
-                            g.peers.arena[pend_owner] + g.lay.xflag) +
-                            ((size_t)g.rank * g.nLx + pend_le);
-                        st_release_sys(xf, make_flag(g.epoch, (unsigned)pend_routed));
+                            g.peers.arena[powner] + g.lay.xflag) + ((size_t)g.rank * g.nLx + ple);
+                        st_release_sys(xf, make_flag(g.epoch, (unsigned)prouted));
                     }
                 }
                 __syncwarp();
             };
-            for (unsigned u = dblock * mwarps + warp; u < total_units; u += stride) {
+            unsigned iter = 0;
+            bool alive = true;
+            for (unsigned u = dblock * mwarps + warp; u < total_units; u += stride, ++iter) {
                 int lo = 0, hi = f.E;
                 while (hi - lo > 1) {
                     const int mid = (lo + hi) >> 1;
@@ -541,22 +545,32 @@ ffn_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
                 if (lane < nrows)
                     bulk_load(buf, static_cast<const char*>(f.tokens) + (size_t)tok * row_bytes,
                               row_bytes, bar);
-                if (pend_e >= 0) publish();
                 if (!mbar_wait(bar, phase, g.wait_cycles, abort_flag)) {
                     if (lane == 0) report_error(g.status, KLEOS_AT_GEMM_PRODUCER, 2000 + e, (int)g.epoch);
                     *abort_flag = 1;
-                    pend_e = -1;
+                    alive = false;
                     break;
                 }
                 phase ^= 1;
-                if (lane < nrows) {
-                    char* dst = g.peers.arena[owner] + g.lay.xcell +
-                                (((size_t)g.rank * g.nLx + le) * g.pEC + slot0 + lane) * row_bytes;
-                    bulk_store(dst, buf, row_bytes);
+                if (lane < kDispatchUnit) {
+                    if (lane < nrows) {
+                        char* dst = g.peers.arena[owner] + g.lay.xcell +
+                                    (((size_t)g.rank * g.nLx + le) * g.pEC + slot0 + lane) * row_bytes;
+                        bulk_store(dst, buf, row_bytes);  // commits its own group
+                    } else {
+                        bulk_commit_empty();  // keep every lane's group count in step
+                    }
+                    bulk_store_wait_pending<kPubLag>();
                 }
-                pend_e = e; pend_rows = nrows; pend_routed = routed; pend_owner = owner; pend_le = le;
+                if (lane == 0) ctl->pend_s[warp][iter % (kPubLag + 1)] = make_int4(e, nrows, routed, owner | (le << 8));
+                if (iter >= (unsigned)kPubLag) publish(ctl->pend_s[warp][(iter - kPubLag) % (kPubLag + 1)]);
             }
-            if (pend_e >= 0) publish();
+            if (lane < kDispatchUnit) bulk_store_wait_all();  // nothing in flight when the block leaves
+            if (alive) {
+                const unsigned done = iter;
+                for (unsigned k = done >= (unsigned)kPubLag ? done - kPubLag : 0; k < done; ++k)
+                    publish(ctl->pend_s[warp][k % (kPubLag + 1)]);
+            }
             if (g.stats && tid == 0) g.stats[blockIdx.x * kStatSlots + 10] = clock64() - t_kernel;
         }
     }

@@ -94,6 +94,14 @@ __device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uin
 __device__ __forceinline__ void bulk_store_wait_read() {
     asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
+// at most N of the issuing thread's most recent bulk groups are still in flight
+template <int N>
+__device__ __forceinline__ void bulk_store_wait_pending() {
+    asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void bulk_commit_empty() {
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
 // the issuing thread's bulk stores have completed
 __device__ __forceinline__ void bulk_store_wait_all() {
     asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
