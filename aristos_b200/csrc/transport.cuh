@@ -81,7 +81,16 @@ __global__ void __launch_bounds__(256) dispatch_kernel(DispatchArgs a) {
         uint4* dst = reinterpret_cast<uint4*>(
             a.peers.arena[owner] + a.lay.xcell +
             (((size_t)a.rank * a.nLx + le) * a.pEC + slot) * a.H * a.elem_bytes);
-        for (unsigned c = lane; c < row_chunks; c += 32) dst[c] = __ldg(src + c);
+        // eight 16-byte loads in flight per lane before the first store is issued
+        for (unsigned c0 = lane; c0 < row_chunks; c0 += 256) {
+            uint4 v[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                if (c0 + 32 * q < row_chunks) v[q] = __ldg(src + c0 + 32 * q);
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                if (c0 + 32 * q < row_chunks) dst[c0 + 32 * q] = v[q];
+        }
     }
     // publish: every block fences its peer stores, the last block to finish raises the flags
     __threadfence_system();
