@@ -48,10 +48,9 @@ constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 28672;
 constexpr uint32_t kInstrDesc = tc::make_instr_desc_bf16(2 * BM, BN);
 constexpr int kMaxFusedPanels = 384;
 constexpr int kFusedThreads = 256;
-constexpr int kDispatchUnit = 8;    // rows a mover copies between two publications
+constexpr int kDispatchUnit = 4;    // consecutive rows of one cell a mover lane copies between two publications
 constexpr int kRowBufBytes = STAGES * STAGE_BYTES;  // a dispatcher block's row buffers: the stage area
-constexpr int kMaxMovers = 8;       // mover warps per dispatcher block
-constexpr int kPubLag = 3;          // a unit is published this many iterations after its stores were issued
+constexpr int kMaxMovers = 48;      // mover lanes per dispatcher block, one row buffer each
 
 
 struct Control {
@@ -72,7 +71,6 @@ struct Control {
     unsigned short own_s[256];               // routed count of this rank's tokens per expert, dispatch order
     unsigned long long mover_bar[kMaxMovers];  // one per dispatch row buffer
     unsigned short poff_s[257];              // first panel of each cell, cells in plan order
-    __align__(16) int4 pend_s[kMaxMovers][kPubLag + 1];  // units whose stores are still in flight
 };
 
 static_assert(sizeof(Control) <= 28672, "control block must fit the shared memory set aside for it");
@@ -486,45 +484,38 @@ ffn_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
 
     if constexpr (kFused) {
         const int row_bytes = f.H * 2;
-        // mover warps of a dispatcher block: each needs 8 row buffers in the stage area
-        const int mwarps = min(8, kRowBufBytes / (kDispatchUnit * row_bytes));
-        if (dispatcher && warp < mwarps && !*abort_flag) {
+        const int movers = min(kMaxMovers, kRowBufBytes / row_bytes);
+        if (dispatcher && tid < movers && !*abort_flag) {
             // -------------------------------------------------------- dispatch (dispatcher blocks)
-            // A warp moves one unit = up to 8 consecutive rows of one cell per iteration
-            // (reference os/packet.cuh:147-166: unscaled rows, row i of a cell = the token that
-            // owns slot i): lanes 0..7 each bulk-load one token row into their buffer (one
-            // mbarrier per warp counts the bytes), then bulk-store it into the owner's cell.
-            // The unit is published one iteration later, while the next unit's loads are in
-            // flight: its stores have completed by then, so the NVLink round trip is hidden.
-            // The mover that completes a cell raises the cell's data flag on the owner.
-            uint8_t* buf = tiles + (size_t)(warp * kDispatchUnit + (lane & 7)) * row_bytes;
-            unsigned long long* bar = &ctl->mover_bar[warp];
+            // Every mover lane runs its own loop with its own row buffer (in the otherwise unused
+            // stage area) and mbarrier: bulk load of a token row, bulk store into the owner's
+            // cell (reference os/packet.cuh:147-166: unscaled rows, row i of a cell = the token
+            // that owns slot i).  Work comes in units of up to 4 consecutive rows of one cell,
+            // handed out round-robin in sending order, so all movers work on the same local
+            // expert at a time.  A unit is published (system fence + counter) after the NEXT
+            // unit's stores have been issued: its own stores have completed by then, so the
+            // NVLink round trip is not waited for.  The mover that completes a cell raises the
+            // cell's data flag on the owner.
+            uint8_t* buf = tiles + (size_t)tid * row_bytes;
+            unsigned long long* bar = &ctl->mover_bar[tid];
             uint32_t phase = 0;
             const int dblock = (int)blockIdx.x - ((int)gridDim.x - n_disp);
-            const unsigned stride = n_disp * mwarps;
+            const unsigned stride = n_disp * movers;
             const unsigned total_units = ctl->prefix_s[f.E];
-            // Publication lags the stores by kPubLag iterations: by then the unit's bulk stores
-            // have completed (each lane keeps at most kPubLag newer groups in flight), so no
-            // iteration waits for an NVLink round trip.
-            auto publish = [&](int4 d) {
-                __syncwarp();
-                if (lane == 0) {
-                    const int pe = d.x, prow = d.y, prouted = d.z, powner = d.w & 0xff, ple = d.w >> 8;
+            int pend_e = -1, pend_rows = 0, pend_routed = 0, pend_owner = 0, pend_le = 0;
+            auto publish = [&]() {
+                __threadfence_system();
+                const unsigned prev = atomicAdd(f.cell_done + pend_e, (unsigned)pend_rows);
+                if ((int)prev + pend_rows == pend_routed) {
                     __threadfence_system();
-                    const unsigned prev = atomicAdd(f.cell_done + pe, (unsigned)prow);
-                    if ((int)prev + prow == prouted) {
-                        __threadfence_system();
-                        f.cell_done[pe] = 0u;
-                        unsigned long long* xf = reinterpret_cast<unsigned long long*>(
-                            g.peers.arena[powner] + g.lay.xflag) + ((size_t)g.rank * g.nLx + ple);
-                        st_release_sys(xf, make_flag(g.epoch, (unsigned)prouted));
-                    }
+                    f.cell_done[pend_e] = 0u;
+                    unsigned long long* xf = reinterpret_cast<unsigned long long*>(
+                        g.peers.arena[pend_owner] + g.lay.xflag) + ((size_t)g.rank * g.nLx + pend_le);
+                    st_release_sys(xf, make_flag(g.epoch, (unsigned)pend_routed));
                 }
-                __syncwarp();
             };
-            unsigned iter = 0;
             bool alive = true;
-            for (unsigned u = dblock * mwarps + warp; u < total_units; u += stride, ++iter) {
+            for (unsigned u = dblock * movers + tid; u < total_units && alive; u += stride) {
                 int lo = 0, hi = f.E;
                 while (hi - lo > 1) {
                     const int mid = (lo + hi) >> 1;
@@ -535,42 +526,40 @@ ffn_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
                 const int routed = ctl->own_s[lo];
                 const int slot0 = (int)(u - ctl->prefix_s[lo]) * kDispatchUnit;
                 const int nrows = min(kDispatchUnit, routed - slot0);
-                int tok = 0;
-                if (lane < nrows) tok = f.cell_tokens[(size_t)e * g.pEC + slot0 + lane];
-                // the buffers' previous rows have left shared memory
-                if (lane < kDispatchUnit) bulk_store_wait_read();
-                __syncwarp();
-                if (lane == 0) mbar_expect_tx(bar, (uint32_t)(nrows * row_bytes));
-                __syncwarp();
-                if (lane < nrows)
-                    bulk_load(buf, static_cast<const char*>(f.tokens) + (size_t)tok * row_bytes,
-                              row_bytes, bar);
-                if (!mbar_wait(bar, phase, g.wait_cycles, abort_flag)) {
-                    if (lane == 0) report_error(g.status, KLEOS_AT_GEMM_PRODUCER, 2000 + e, (int)g.epoch);
-                    *abort_flag = 1;
-                    alive = false;
-                    break;
-                }
-                phase ^= 1;
-                if (lane < kDispatchUnit) {
-                    if (lane < nrows) {
-                        char* dst = g.peers.arena[owner] + g.lay.xcell +
-                                    (((size_t)g.rank * g.nLx + le) * g.pEC + slot0 + lane) * row_bytes;
-                        bulk_store(dst, buf, row_bytes);  // commits its own group
+                int toks[kDispatchUnit];
+#pragma unroll
+                for (int r = 0; r < kDispatchUnit; ++r)
+                    toks[r] = r < nrows ? f.cell_tokens[(size_t)e * g.pEC + slot0 + r] : 0;
+                char* cell = g.peers.arena[owner] + g.lay.xcell +
+                             (((size_t)g.rank * g.nLx + le) * g.pEC + slot0) * row_bytes;
+#pragma unroll
+                for (int r = 0; r < kDispatchUnit; ++r) {
+                    if (r < nrows) {
+                        bulk_store_wait_read();  // the buffer's previous row has left shared memory
+                        mbar_expect_tx(bar, row_bytes);
+                        bulk_load(buf, static_cast<const char*>(f.tokens) + (size_t)toks[r] * row_bytes,
+                                  row_bytes, bar);
+                        if (!mbar_wait(bar, phase, g.wait_cycles, abort_flag)) {
+                            report_error(g.status, KLEOS_AT_GEMM_PRODUCER, 2000 + e, (int)g.epoch);
+                            *abort_flag = 1;
+                            alive = false;
+                            break;
+                        }
+                        phase ^= 1;
+                        bulk_store(cell + (size_t)r * row_bytes, buf, row_bytes);
                     } else {
-                        bulk_commit_empty();  // keep every lane's group count in step
+                        bulk_commit_empty();  // four groups per unit, always
                     }
-                    bulk_store_wait_pending<kPubLag>();
                 }
-                if (lane == 0) ctl->pend_s[warp][iter % (kPubLag + 1)] = make_int4(e, nrows, routed, owner | (le << 8));
-                if (iter >= (unsigned)kPubLag) publish(ctl->pend_s[warp][(iter - kPubLag) % (kPubLag + 1)]);
+                if (!alive) break;
+                if (pend_e >= 0) {
+                    bulk_store_wait_pending<kDispatchUnit>();  // everything but this unit's stores
+                    publish();
+                }
+                pend_e = e; pend_rows = nrows; pend_routed = routed; pend_owner = owner; pend_le = le;
             }
-            if (lane < kDispatchUnit) bulk_store_wait_all();  // nothing in flight when the block leaves
-            if (alive) {
-                const unsigned done = iter;
-                for (unsigned k = done >= (unsigned)kPubLag ? done - kPubLag : 0; k < done; ++k)
-                    publish(ctl->pend_s[warp][k % (kPubLag + 1)]);
-            }
+            bulk_store_wait_all();  // nothing in flight when the block leaves
+            if (alive && pend_e >= 0) publish();
             if (g.stats && tid == 0) g.stats[blockIdx.x * kStatSlots + 10] = clock64() - t_kernel;
         }
     }
