@@ -50,7 +50,7 @@ struct State {
     long long wait_cycles = 4000000000LL;  // about two seconds of SM clock
     bool use_tc = false;
     bool use_pair = true;
-    bool use_fused = false; // dispatch + plan inside the GEMM1 kernel: default on from 4 ranks (KLEOS_FUSED=0|1)
+    bool use_fused = false; // experimental: dispatch + plan inside the GEMM1 kernel (KLEOS_FUSED=1)
     int dispatch_ctas = 16; // blocks of the fused kernel that only move tokens (KLEOS_DISPATCH_CTAS)
     int pipe_parts = 1;     // dispatch / GEMM1 software pipeline over groups of local experts (KLEOS_PIPE)
     cudaStream_t copy_stream = nullptr;
@@ -653,7 +653,6 @@ int kleos_initialize(const char* config_json_path, int rank, int world, const vo
                                         route_tc::Shape<128>::SMEM_BYTES));
     }
     if (const char* pr = std::getenv("KLEOS_GEMM_PAIR")) g.use_pair = pr[0] != '0';
-    g.use_fused = world >= 4;  // worth it once most dispatched rows cross NVLink
     if (const char* fu = std::getenv("KLEOS_FUSED")) g.use_fused = fu[0] != '0';
     if (const char* dc = std::getenv("KLEOS_DISPATCH_CTAS")) g.dispatch_ctas = std::max(2, std::atoi(dc) & ~1);
     // the fused kernel keeps its panel list and per-cell tables in shared memory
