@@ -49,6 +49,7 @@ struct State {
     uint32_t epoch = 0;
     long long wait_cycles = 4000000000LL;  // about two seconds of SM clock
     bool use_tc = false;
+    bool suppress_return_flag = false;  // test hook: see kleos_debug_suppress_return_flag
     bool use_pair = true;
     bool use_fused = false; // experimental: dispatch + plan inside the GEMM1 kernel (KLEOS_FUSED=1)
     int dispatch_ctas = 16; // blocks of the fused kernel that only move tokens (KLEOS_DISPATCH_CTAS)
@@ -176,7 +177,7 @@ EncodeTiledFn g_encode = nullptr;
 // bf16 matrix [rows][cols] with cols contiguous; box = 64 columns x box_rows rows, 128-byte
 // swizzle (64 bf16 = 128 bytes, the swizzle span).
 int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
-             uint32_t box_cols = 64, bool swizzle = true) {
+             uint32_t box_cols = 64, bool swizzle = true, int promo = 3) {
     if (!g_encode) {
         void* fn = nullptr;
         cudaDriverEntryPointQueryResult q;
@@ -192,7 +193,10 @@ int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, u
     const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base),
                                 dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                 swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
-                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                promo == 0 ? CU_TENSOR_MAP_L2_PROMOTION_NONE
+                                : promo == 1 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
+                                : promo == 2 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B
+                                             : CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(KLEOS_E_CUDA, "cuTensorMapEncodeTiled failed: %d", (int)r);
     return KLEOS_OK;
@@ -227,8 +231,9 @@ int ensure_maps(const Sections& s) {
     if ((rc = make_map(&g.map_w1, s.W1, (uint64_t)g.nLx * c.I, c.H, gemm_tc::BN))) return rc;
     if ((rc = make_map(&g.map_y1, g.y1, cell_rows, c.I, gemm_tc::BM))) return rc;
     if ((rc = make_map(&g.map_w2, s.W2, (uint64_t)g.nLx * c.H, c.I, gemm_tc::BN))) return rc;
-    if ((rc = make_map(&g.map_w1h, s.W1, (uint64_t)g.nLx * c.I, c.H, gemm_tc2::BN / 2))) return rc;
-    if ((rc = make_map(&g.map_w2h, s.W2, (uint64_t)g.nLx * c.H, c.I, gemm_tc2::BN / 2))) return rc;
+    const int promo = 3;  // 256-byte L2 promotion; 0/64/128 bytes measured the same on the C3 layer
+    if ((rc = make_map(&g.map_w1h, s.W1, (uint64_t)g.nLx * c.I, c.H, gemm_tc2::BN / 2, 64, true, promo))) return rc;
+    if ((rc = make_map(&g.map_w2h, s.W2, (uint64_t)g.nLx * c.H, c.I, gemm_tc2::BN / 2, 64, true, promo))) return rc;
     if (c.PX <= 128) {
         if ((rc = make_map(&g.map_act, s.A, c.S, c.H, route_tc::BM))) return rc;
         if ((rc = make_map(&g.map_wg, s.Wg, c.PX, c.H, c.PX))) return rc;
@@ -367,6 +372,7 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed, const S
     ga.elem_bytes = c.elem_bytes; ga.epoch = g.epoch; ga.le_begin = 0; ga.le_end = g.nLx;
     ga.ret.peers = g.peers; ga.ret.lay = g.lay; ga.ret.done_counter = g.done_gemm2;
     ga.ret.rank = g.rank; ga.ret.world = g.world; ga.ret.epoch = g.epoch;
+    ga.ret.suppress = g.suppress_return_flag ? 1 : 0;
 
     GemmArgs g1 = ga;
     g1.A = g.arena + g.lay.xcell; g1.B = s.W1; g1.bias = s.b1; g1.N = c.I; g1.Kd = c.H; g1.mode = 0;
@@ -845,6 +851,13 @@ int kleos_last_status(kleos_status* out) {
     return KLEOS_OK;
 }
 
+int kleos_clear_status(void) {
+    if (!g.initialised) return fail(KLEOS_E_STATE, "not initialised");
+    KLEOS_CUDA(cudaStreamSynchronize(cudaStreamPerThread));
+    KLEOS_CUDA(cudaMemset(g.status, 0, sizeof(DeviceStatus)));
+    return KLEOS_OK;
+}
+
 int kleos_debug_routing(int32_t* topk, int32_t* slots, uint32_t* counts, float* mcw) {
     if (!g.initialised) return fail(KLEOS_E_STATE, "not initialised");
     const LayerConfig& c = g.cfg;
@@ -865,6 +878,12 @@ int kleos_debug_gemm_stats(long long* out, int max_values) {
     KLEOS_CUDA(cudaStreamSynchronize(cudaStreamPerThread));
     KLEOS_CUDA(cudaMemcpy(out, g.gemm_stats, sizeof(long long) * n, cudaMemcpyDeviceToHost));
     return n;
+}
+
+int kleos_debug_suppress_return_flag(int on) {
+    if (!g.initialised) return fail(KLEOS_E_STATE, "not initialised");
+    g.suppress_return_flag = on != 0;
+    return KLEOS_OK;
 }
 
 int kleos_phase_times(float* ms, int n) {

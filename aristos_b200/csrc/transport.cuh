@@ -326,6 +326,7 @@ struct ReturnFlagArgs {
     unsigned* done_counter;
     int rank, world;
     uint32_t epoch;
+    int suppress;  // test hook: do not raise the flags (exercises the bounded wait in combine)
 };
 
 __device__ __forceinline__ void publish_return_flags(const ReturnFlagArgs& r, bool* smem_last) {
@@ -338,7 +339,7 @@ __device__ __forceinline__ void publish_return_flags(const ReturnFlagArgs& r, bo
     __syncthreads();
     if (*smem_last) {
         __threadfence_system();
-        if ((int)threadIdx.x < r.world) {
+        if ((int)threadIdx.x < r.world && !r.suppress) {
             unsigned long long* f = reinterpret_cast<unsigned long long*>(
                 r.peers.arena[threadIdx.x] + r.lay.yflag) + r.rank;
             st_release_sys(f, make_flag(r.epoch, 1u));

@@ -26,8 +26,8 @@ EXPORTS = (
     "kleos_get_unique_id", "kleos_config_probe", "kleos_set_device", "kleos_initialize", "kleos_set_gate_bias",
     "kleos_forward", "kleos_forward_bench", "kleos_forward_host", "kleos_forward_host_async",
     "kleos_host_sync", "kleos_get_rank",
-    "kleos_local_experts", "kleos_get_info", "kleos_last_status", "kleos_debug_routing",
-    "kleos_phase_times", "kleos_debug_gemm_stats", "kleos_route_static", "kleos_finalize", "kleos_error_string",
+    "kleos_local_experts", "kleos_get_info", "kleos_last_status", "kleos_clear_status", "kleos_debug_routing",
+    "kleos_phase_times", "kleos_debug_gemm_stats", "kleos_debug_suppress_return_flag", "kleos_route_static", "kleos_finalize", "kleos_error_string",
 )
 
 PHASE_NAMES = ("route", "slots", "dispatch", "plan", "gemm1", "gemm2", "combine", "total")

@@ -116,6 +116,8 @@ int kleos_get_info(kleos_layer_info* out);
 /* Device-side status of the last forward calls; synchronises the library's stream.
  * The reference has no equivalent: its device waits spin forever (atomics.cuh:96-138). */
 int kleos_last_status(kleos_status* out);
+/* Forget a recorded device-side error (the first one sticks until cleared). */
+int kleos_clear_status(void);
 
 /* Routing results of the last forward, copied to host memory (any pointer may be NULL):
  * topk [S*K] expert ids, slots [S*K] slot inside the expert cell or -1 when dropped,
@@ -154,6 +156,13 @@ int kleos_debug_gemm_stats(long long* out, int max_values);
 int kleos_route_static(const void* A, const void* Wg, const float* gate_bias, int S, int H, int E,
                        int K, int torch_dtype, void* probs, int32_t* topk, float* mcw,
                        void* stream);
+
+/* Test hook for the failure path: while on, the expert FFN does not raise its "results
+ * returned" flags, so the combine's bounded wait runs out, the forward records
+ * {KLEOS_E_DEVICE, KLEOS_AT_COMBINE_WAIT} and returns with the context intact.  Nothing is
+ * faulted or hung; the wait budget is KLEOS_WAIT_MS.  No counterpart in the reference, whose
+ * waits spin forever (atomics.cuh:96-138). */
+int kleos_debug_suppress_return_flag(int on);
 
 /* Free everything.  Replaces kleos::finalize() (bootstrap.cuh:561-588). */
 int kleos_finalize(void);

@@ -121,3 +121,68 @@ def test_pipelined_host_path_matches_synchronous_path(dtype):
             assert np.array_equal(got, want[which]), f"step {step}"
     finally:
         kleos.finalize()
+
+
+def test_bounded_wait_reports_status_and_context_survives():
+    """Failure path without faulting anything: with the return flags suppressed the combine's
+    wait runs out after KLEOS_WAIT_MS, the status says where, and after clearing it the same
+    layer runs correctly again."""
+    import os
+    import torch
+    from aristos_b200 import kleos
+    cfg = _small(2)
+    packed, views = hz.make_inputs(cfg, 1)
+    ref = moe_oracle.moe_forward(cfg, 1, views)[0]
+    raw = synth.encode(packed[0], 2)
+    old = os.environ.get("KLEOS_WAIT_MS")
+    os.environ["KLEOS_WAIT_MS"] = "50"
+    try:
+        info = kleos.initialize(cfg, 0, 1)
+    finally:
+        if old is None:
+            os.environ.pop("KLEOS_WAIT_MS", None)
+        else:
+            os.environ["KLEOS_WAIT_MS"] = old
+    try:
+        lib = kleos.load_library()
+        iP = torch.from_numpy(raw.view(np.uint8).copy()).cuda()
+        oP = torch.zeros(info.output_elems * 2, dtype=torch.uint8, device="cuda")
+        assert lib.kleos_debug_suppress_return_flag(1) == 0
+        kleos.forward_host(iP, oP)
+        st = kleos.last_status()
+        assert st.code == -6 and st.where == 2, (st.code, st.where)  # KLEOS_E_DEVICE at the combine wait
+        assert lib.kleos_debug_suppress_return_flag(0) == 0
+        assert lib.kleos_clear_status() == 0
+        kleos.forward_host(iP, oP)
+        st = kleos.last_status()
+        assert st.code == 0
+        o = oP.cpu().numpy().view(np.uint16)
+        out = synth.decode(o[cfg.S * cfg.PX:], 2).reshape(cfg.S, cfg.H)
+        err = np.abs(out - ref["out"]).max() / np.abs(ref["out"]).max()
+        assert err <= hz.TOL[2]
+    finally:
+        kleos.finalize()
+
+
+def test_top_k_equal_to_number_of_experts():
+    cfg = _small(2, num_experts=4, expert_top_k=4, sequence_len=128, hidden_size=128,
+                 intermediate_size=128)
+    packed, views = hz.make_inputs(cfg, 1)
+    ref = moe_oracle.moe_forward(cfg, 1, views)[0]
+    ref["margin"] = 1.0  # every expert is selected: no k-th / (k+1)-th gap exists
+    probs, out, routing = hz.run_layer_single_gpu(cfg, packed[0])
+    hz.check_against_oracle(cfg, ref, probs, out, routing)
+
+
+@pytest.mark.parametrize("name", ["C4", "C5"])
+def test_large_baseline_layers_single_gpu_sampled(name):
+    """The imbalanced 128-expert layer (Zipf gate bias, capacity 1.25, heavy drops) and the
+    large-FFN layer, all experts on one GPU: routing for every token, outputs for a sample."""
+    cfg, extra = baseline_config(name)
+    packed, views = hz.make_inputs(cfg, 1)
+    bias = synth.zipf_gate_bias(cfg, extra["zipf"]) if extra["zipf"] else None
+    rng = np.random.default_rng(1)
+    rows = np.sort(rng.choice(cfg.S, size=64, replace=False)).astype(np.int32)
+    ref = c_oracle.moe_forward_rank(cfg, 1, 0, views, gate_bias=bias, tokens=rows)
+    probs, out, routing = hz.run_layer_single_gpu(cfg, packed[0], gate_bias=bias)
+    hz.check_against_oracle(cfg, ref, probs, out, routing, rows=rows)
