@@ -1,8 +1,8 @@
 """Layer configuration: the keys of ``kleos_config.json`` and the sizes derived from them.
 
 Mirrors the compile-time ``ACC`` struct of the reference (csrc/include/kleos/types.cuh:442-513)
-as run-time arithmetic; the C++ host layer (csrc/config.cpp) computes the same numbers and
-``tests/test_config.py`` checks that the two agree.  Key names and enum values follow
+as run-time arithmetic; the C++ host layer (csrc/config.hpp) computes the same numbers and
+``tests/test_config_abi.py`` checks that the two agree.  Key names and enum values follow
 csrc/kleos_config.schema.json:5-89.
 
 Two documented extensions over the reference schema:
@@ -24,7 +24,7 @@ BLOCK_N = 64   # the gate pads the expert dimension to a multiple of this (types
 
 DTYPE_NAMES = {0: "fp32", 1: "tf32", 2: "bf16", 3: "fp16"}
 DTYPE_BYTES = {0: 4, 1: 4, 2: 2, 3: 2}
-SUPPORTED_DTYPES = (0, 2)
+SUPPORTED_DTYPES = (0, 2, 3)
 
 REQUIRED_KEYS = (
     "capacity_factor", "drop_tokens", "expert_top_k", "is_training", "hidden_act",

@@ -2,6 +2,7 @@
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -44,6 +45,32 @@ template <> struct Elem<__nv_bfloat16> {
     static __device__ __forceinline__ float round(float v) {
         return __bfloat162float(__float2bfloat16_rn(v));
     }
+};
+
+template <> struct Elem<__half> {
+    static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
+    static __device__ __forceinline__ __half from_f(float v) { return __float2half_rn(v); }
+    static __device__ __forceinline__ float round(float v) { return __half2float(__float2half_rn(v)); }
+};
+
+// Packed pairs of a 16-bit element type: conversions and single-rounding arithmetic, plus the
+// operand-format code of the tcgen05 instruction descriptor (0 = f16, 1 = bf16).
+template <typename T> struct Pack2;
+template <> struct Pack2<__nv_bfloat16> {
+    using type = __nv_bfloat162;
+    static constexpr uint32_t kMmaFormat = 1;
+    static __device__ __forceinline__ type from_f2(float a, float b) { return __floats2bfloat162_rn(a, b); }
+    static __device__ __forceinline__ float2 to_f2(type v) { return __bfloat1622float2(v); }
+    static __device__ __forceinline__ type mul(type a, type b) { return __hmul2(a, b); }
+    static __device__ __forceinline__ type add(type a, type b) { return __hadd2(a, b); }
+};
+template <> struct Pack2<__half> {
+    using type = __half2;
+    static constexpr uint32_t kMmaFormat = 0;
+    static __device__ __forceinline__ type from_f2(float a, float b) { return __floats2half2_rn(a, b); }
+    static __device__ __forceinline__ float2 to_f2(type v) { return __half22float2(v); }
+    static __device__ __forceinline__ type mul(type a, type b) { return __hmul2(a, b); }
+    static __device__ __forceinline__ type add(type a, type b) { return __hadd2(a, b); }
 };
 
 __device__ __forceinline__ float apply_act(float z, int hidden_act) {

@@ -31,7 +31,6 @@ constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int TMEM_COLS = 512;              // two 128x256 fp32 accumulators
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 12288 /*control*/;
 
-constexpr uint32_t kInstrDesc = make_instr_desc_bf16(BM, BN);
 
 struct Control {
     unsigned long long full[STAGES];
@@ -48,12 +47,14 @@ struct Control {
 
 // kEpi selects the fused epilogue at compile time (0: bias + ReLU, 1: bias + GELU, 2: bias only)
 // so the read-back loop stays a short straight-line sequence.
-template <int kEpi>
+template <typename TE, int kEpi>
 __global__ void __launch_bounds__(256, 1)
 ffn_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
             GemmArgs g) {
     using namespace tc;
     using namespace gemm_tc;
+    constexpr uint32_t kInstrDesc = make_instr_desc_16b(BM, BN, Pack2<TE>::kMmaFormat);
+    using TE2 = typename Pack2<TE>::type;
     extern __shared__ uint8_t smem_raw[];
     // operand stages need 1024-byte alignment for the 128-byte swizzle pattern
     uint8_t* tiles = reinterpret_cast<uint8_t*>(
@@ -177,7 +178,7 @@ ffn_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         // ------------------------------------------------------------ epilogue
         const int q = warp - 4;
         const int row = q * 32 + lane;
-        const __nv_bfloat16* bias = static_cast<const __nv_bfloat16*>(g.bias);
+        const TE* bias = static_cast<const TE*>(g.bias);
         uint32_t tile_n = 0;
         long long w_accfull = 0, w_tmem = 0;
         const long long t_begin = clock64();
@@ -197,10 +198,10 @@ ffn_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 if (nb < g.N) {
                     const uint4 raw = __ldg(reinterpret_cast<const uint4*>(
                         bias + (size_t)tcd.le * g.N + nb));
-                    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+                    const TE2* h2 = reinterpret_cast<const TE2*>(&raw);
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        const float2 f = __bfloat1622float2(h2[j]);
+                        const float2 f = Pack2<TE>::to_f2(h2[j]);
                         bs[2 * j] = f.x;
                         bs[2 * j + 1] = f.y;
                     }
@@ -215,7 +216,7 @@ ffn_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             tc_fence_after();
             const int n0 = tcd.nt * BN;
             const uint32_t taddr = tmem_base + buf * BN + (static_cast<uint32_t>(q * 32) << 16);
-            __nv_bfloat16* orow = (row < p.rows) ? out_ptr<__nv_bfloat16>(g, p, row, n0) : nullptr;
+            TE* orow = (row < p.rows) ? out_ptr<TE>(g, p, row, n0) : nullptr;
             // accumulator read-back, two 32-column chunks in flight; bias fetched as 16-byte
             // broadcast loads
             uint32_t r[2][32];
@@ -242,7 +243,7 @@ ffn_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                             v0 = apply_act(v0, 1);
                             v1 = apply_act(v1, 1);
                         }
-                        const __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
+                        const TE2 h = Pack2<TE>::from_f2(v0, v1);
                         packed[j] = *reinterpret_cast<const uint32_t*>(&h);
                     }
                     uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);

@@ -45,7 +45,6 @@ constexpr int B_STAGE_BYTES = (BN / 2) * BK * 2;  // 16 KiB: this block's half o
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int TMEM_COLS = 512;  // two accumulators of 256 fp32 columns
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 28672;
-constexpr uint32_t kInstrDesc = tc::make_instr_desc_bf16(2 * BM, BN);
 constexpr int kMaxFusedPanels = 384;
 constexpr int kFusedThreads = 256;
 constexpr int kDispatchUnit = 4;    // consecutive rows of one cell a mover lane copies between two publications
@@ -123,13 +122,15 @@ __device__ __forceinline__ int total_pair_tiles(const int* le_start, int le_begi
 
 // kEpi selects the fused epilogue at compile time (0: bias + ReLU, 1: bias + GELU, 2: bias only)
 // so the read-back loop stays a short straight-line sequence.
-template <int kEpi, bool kFused>
+template <typename TE, int kEpi, bool kFused>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFused ? gemm_tc2::kFusedThreads : 256, 1)
 ffn_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
              GemmArgs g, gemm_tc2::FusedArgs f) {
     using namespace tc;
     using namespace gemm_tc2;
     constexpr int NST = STAGES;
+    constexpr uint32_t kInstrDesc = make_instr_desc_16b(2 * BM, BN, Pack2<TE>::kMmaFormat);
+    using TE2 = typename Pack2<TE>::type;
     const long long t_kernel = clock64();
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = reinterpret_cast<uint8_t*>(
@@ -366,7 +367,7 @@ ffn_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
         // ------------------------------------------------------------ epilogue (both blocks)
         const int q = warp - 4;
         const int row = q * 32 + lane;
-        const __nv_bfloat16* bias = static_cast<const __nv_bfloat16*>(g.bias);
+        const TE* bias = static_cast<const TE*>(g.bias);
         uint32_t tile_n = 0;
         long long w_accfull = 0, w_tmem = 0;
         const long long t_begin = clock64();
@@ -388,10 +389,10 @@ ffn_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
                 if (nb < g.N) {
                     const uint4 raw = __ldg(reinterpret_cast<const uint4*>(
                         bias + (size_t)pt.le * g.N + nb));
-                    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+                    const TE2* h2 = reinterpret_cast<const TE2*>(&raw);
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        const float2 f = __bfloat1622float2(h2[j]);
+                        const float2 f = Pack2<TE>::to_f2(h2[j]);
                         bs[2 * j] = f.x;
                         bs[2 * j + 1] = f.y;
                     }
@@ -414,7 +415,7 @@ ffn_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
                 if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&ctl->acc_empty[buf]), 0));
                 continue;
             }
-            __nv_bfloat16* obase = out_ptr<__nv_bfloat16>(g, p, q * 32, n0);
+            TE* obase = out_ptr<TE>(g, p, q * 32, n0);
             uint4* stg = ctl->stage_s[q];
             // Accumulator read-back, two 32-column chunks in flight.  Every 64 columns the warp
             // transposes through a swizzled shared-memory tile so that each store instruction
@@ -450,7 +451,7 @@ ffn_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
                         v0 = apply_act(v0, 1);
                         v1 = apply_act(v1, 1);
                     }
-                    const __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
+                    const TE2 h = Pack2<TE>::from_f2(v0, v1);
                     packed[j] = *reinterpret_cast<const uint32_t*>(&h);
                 }
 #pragma unroll

@@ -190,7 +190,9 @@ int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, u
     const cuuint64_t strides[1] = {cols * 2};
     const cuuint32_t box[2] = {box_cols, box_rows};
     const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base),
+    const CUtensorMapDataType dt = g.cfg.torch_dtype == 3 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                          : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    const CUresult r = g_encode(map, dt, 2, const_cast<void*>(base),
                                 dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                 swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                                 promo == 0 ? CU_TENSOR_MAP_L2_PROMOTION_NONE
@@ -301,10 +303,10 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed, const S
         if constexpr (sizeof(T) == 2) {
             const int grid = (c.S + route_tc::BM - 1) / route_tc::BM;
             if (c.PX == 64)
-                route_tc_kernel<64><<<grid, 256, route_tc::Shape<64>::SMEM_BYTES, st>>>(
+                route_tc_kernel<T, 64><<<grid, 256, route_tc::Shape<64>::SMEM_BYTES, st>>>(
                     *act_map, g.map_wg, ra, g.status, g.wait_cycles, (int)g.epoch);
             else
-                route_tc_kernel<128><<<grid, 256, route_tc::Shape<128>::SMEM_BYTES, st>>>(
+                route_tc_kernel<T, 128><<<grid, 256, route_tc::Shape<128>::SMEM_BYTES, st>>>(
                     *act_map, g.map_wg, ra, g.status, g.wait_cycles, (int)g.epoch);
             refine_kernel<T><<<148, 256, 0, st>>>(ra);
         }
@@ -403,21 +405,21 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed, const S
                 if (fused) {
                     const int thr = gemm_tc2::kFusedThreads;
                     if (c.hidden_act == 0)
-                        ffn_gemm_tc2<0, true><<<grid, thr, gemm_tc2::SMEM_BYTES, st>>>(g.map_x, g.map_w1h, g1, fa);
+                        ffn_gemm_tc2<T, 0, true><<<grid, thr, gemm_tc2::SMEM_BYTES, st>>>(g.map_x, g.map_w1h, g1, fa);
                     else
-                        ffn_gemm_tc2<1, true><<<grid, thr, gemm_tc2::SMEM_BYTES, st>>>(g.map_x, g.map_w1h, g1, fa);
+                        ffn_gemm_tc2<T, 1, true><<<grid, thr, gemm_tc2::SMEM_BYTES, st>>>(g.map_x, g.map_w1h, g1, fa);
                 }
                 for (int p = 0; p < parts && !fused; ++p) {
                     if ((rc = next_part(p))) return rc;
                     g1.le_begin = p * g.nLx / parts;
                     g1.le_end = (p + 1) * g.nLx / parts;
                     if (c.hidden_act == 0)
-                        ffn_gemm_tc2<0, false><<<grid, 256, gemm_tc2::SMEM_BYTES, st>>>(g.map_x, g.map_w1h, g1, fa);
+                        ffn_gemm_tc2<T, 0, false><<<grid, 256, gemm_tc2::SMEM_BYTES, st>>>(g.map_x, g.map_w1h, g1, fa);
                     else
-                        ffn_gemm_tc2<1, false><<<grid, 256, gemm_tc2::SMEM_BYTES, st>>>(g.map_x, g.map_w1h, g1, fa);
+                        ffn_gemm_tc2<T, 1, false><<<grid, 256, gemm_tc2::SMEM_BYTES, st>>>(g.map_x, g.map_w1h, g1, fa);
                 }
                 KLEOS_CUDA(mark());
-                ffn_gemm_tc2<2, false><<<grid, 256, gemm_tc2::SMEM_BYTES, st>>>(g.map_y1, g.map_w2h, g2, fa);
+                ffn_gemm_tc2<T, 2, false><<<grid, 256, gemm_tc2::SMEM_BYTES, st>>>(g.map_y1, g.map_w2h, g2, fa);
                 KLEOS_CUDA(mark());
             } else {
                 for (int p = 0; p < parts; ++p) {
@@ -425,12 +427,12 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed, const S
                     g1.le_begin = p * g.nLx / parts;
                     g1.le_end = (p + 1) * g.nLx / parts;
                     if (c.hidden_act == 0)
-                        ffn_gemm_tc<0><<<g.sm_count, 256, gemm_tc::SMEM_BYTES, st>>>(g.map_x, g.map_w1, g1);
+                        ffn_gemm_tc<T, 0><<<g.sm_count, 256, gemm_tc::SMEM_BYTES, st>>>(g.map_x, g.map_w1, g1);
                     else
-                        ffn_gemm_tc<1><<<g.sm_count, 256, gemm_tc::SMEM_BYTES, st>>>(g.map_x, g.map_w1, g1);
+                        ffn_gemm_tc<T, 1><<<g.sm_count, 256, gemm_tc::SMEM_BYTES, st>>>(g.map_x, g.map_w1, g1);
                 }
                 KLEOS_CUDA(mark());
-                ffn_gemm_tc<2><<<g.sm_count, 256, gemm_tc::SMEM_BYTES, st>>>(g.map_y1, g.map_w2, g2);
+                ffn_gemm_tc<T, 2><<<g.sm_count, 256, gemm_tc::SMEM_BYTES, st>>>(g.map_y1, g.map_w2, g2);
                 KLEOS_CUDA(mark());
             }
         }
@@ -467,7 +469,24 @@ int forward_any(const void* iP, void* oP, cudaStream_t st, bool timed, const Sta
     if (!g.initialised) return fail(KLEOS_E_STATE, "kleos_forward before kleos_initialize");
     if (!iP || !oP) return fail(KLEOS_E_ARG, "null buffer");
     if (g.cfg.torch_dtype == 0) return forward_typed<float>(iP, oP, st, timed, stg);
+    if (g.cfg.torch_dtype == 3) return forward_typed<__half>(iP, oP, st, timed, stg);
     return forward_typed<__nv_bfloat16>(iP, oP, st, timed, stg);
+}
+
+template <typename TE>
+int set_tc_attributes() {
+    const auto dyn = cudaFuncAttributeMaxDynamicSharedMemorySize;
+    KLEOS_CUDA(cudaFuncSetAttribute(route_tc_kernel<TE, 64>, dyn, route_tc::Shape<64>::SMEM_BYTES));
+    KLEOS_CUDA(cudaFuncSetAttribute(route_tc_kernel<TE, 128>, dyn, route_tc::Shape<128>::SMEM_BYTES));
+    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<TE, 0, false>, dyn, gemm_tc2::SMEM_BYTES));
+    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<TE, 1, false>, dyn, gemm_tc2::SMEM_BYTES));
+    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<TE, 2, false>, dyn, gemm_tc2::SMEM_BYTES));
+    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<TE, 0, true>, dyn, gemm_tc2::SMEM_BYTES));
+    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<TE, 1, true>, dyn, gemm_tc2::SMEM_BYTES));
+    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc<TE, 0>, dyn, gemm_tc::SMEM_BYTES));
+    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc<TE, 1>, dyn, gemm_tc::SMEM_BYTES));
+    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc<TE, 2>, dyn, gemm_tc::SMEM_BYTES));
+    return KLEOS_OK;
 }
 
 int ensure_host_pipe() {
@@ -583,8 +602,8 @@ int kleos_initialize(const char* config_json_path, int rank, int world, const vo
     const std::string err = load_config(config_json_path, &cfg);
     if (!err.empty()) return fail(KLEOS_E_CONFIG, "%s: %s", config_json_path, err.c_str());
     if (cfg.E % world) return fail(KLEOS_E_CONFIG, "num_experts %d does not divide over %d ranks", cfg.E, world);
-    if (cfg.torch_dtype != 0 && cfg.torch_dtype != 2)
-        return fail(KLEOS_E_UNSUPPORTED, "torch_dtype %d: only 0 (float) and 2 (bf16) are implemented", cfg.torch_dtype);
+    if (cfg.torch_dtype == 1)
+        return fail(KLEOS_E_UNSUPPORTED, "torch_dtype 1 (tf32) is not implemented: use 0 (float), 2 (bf16) or 3 (fp16)");
     if (cfg.K > kMaxTopK) return fail(KLEOS_E_UNSUPPORTED, "expert_top_k > %d", kMaxTopK);
     if (cfg.E > 256) return fail(KLEOS_E_UNSUPPORTED, "num_experts > 256");
     if (world > 1 && !nccl_id) return fail(KLEOS_E_ARG, "world > 1 needs an NCCL unique id");
@@ -610,7 +629,7 @@ int kleos_initialize(const char* config_json_path, int rank, int world, const vo
         g.wait_cycles = (long long)(std::atof(w) * 1e-3 * prop.clockRate * 1e3);
     }
     const char* simt = std::getenv("KLEOS_DEBUG_SIMT_GEMM");
-    g.use_tc = (cfg.torch_dtype == 2) && !(simt && simt[0] == '1');
+    g.use_tc = (cfg.torch_dtype == 2 || cfg.torch_dtype == 3) && !(simt && simt[0] == '1');
 
     const size_t eb = cfg.elem_bytes;
     const size_t cell_bytes = (size_t)cfg.E * cfg.pEC * cfg.H * eb;  // world*nLx == E
@@ -653,10 +672,9 @@ int kleos_initialize(const char* config_json_path, int rank, int world, const vo
         if (gs[0] == '1' && (rc = dev_alloc(&g.gemm_stats, (size_t)2 * g.sm_count * kStatSlots))) return rc;
 
     if (g.use_tc) {
-        KLEOS_CUDA(cudaFuncSetAttribute(route_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        route_tc::Shape<64>::SMEM_BYTES));
-        KLEOS_CUDA(cudaFuncSetAttribute(route_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        route_tc::Shape<128>::SMEM_BYTES));
+        if (cfg.torch_dtype == 2) rc = set_tc_attributes<__nv_bfloat16>();
+        else rc = set_tc_attributes<__half>();
+        if (rc) return rc;
     }
     if (const char* pr = std::getenv("KLEOS_GEMM_PAIR")) g.use_pair = pr[0] != '0';
     if (const char* fu = std::getenv("KLEOS_FUSED")) g.use_fused = fu[0] != '0';
@@ -665,17 +683,6 @@ int kleos_initialize(const char* config_json_path, int rank, int world, const vo
     if ((size_t)cfg.E * cfg.pEC / kTileM > (size_t)gemm_tc2::kMaxFusedPanels || cfg.E > 256 || g.nLx > 255 ||
         cfg.H * 2 > gemm_tc2::kRowBufBytes)
         g.use_fused = false;
-    if (g.use_tc)
-    {
-        KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm_tc2::SMEM_BYTES));
-        KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm_tc2::SMEM_BYTES));
-        KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm_tc2::SMEM_BYTES));
-        KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm_tc2::SMEM_BYTES));
-        KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm_tc2::SMEM_BYTES));
-        KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm_tc::SMEM_BYTES));
-        KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm_tc::SMEM_BYTES));
-        KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm_tc::SMEM_BYTES));
-    }
 
     for (int r = 0; r < kMaxWorld; ++r) g.peers.arena[r] = nullptr;
     g.peers.arena[rank] = g.arena;

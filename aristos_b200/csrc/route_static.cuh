@@ -59,7 +59,7 @@ extern "C" int kleos_route_static(const void* A, const void* Wg, const float* ga
     if (K < 1 || K > E || K > kMaxTopK) return complain(KLEOS_E_ARG, "top-k out of range");
     if (H < 64 || H % 64) return complain(KLEOS_E_ARG, "H must be a positive multiple of 64");
     if (torch_dtype != 0 && torch_dtype != 2)
-        return complain(KLEOS_E_UNSUPPORTED, "torch_dtype must be 0 (float) or 2 (bf16)");
+        return complain(KLEOS_E_UNSUPPORTED, "torch_dtype must be 0 (float) or 2 (bf16)");  // fp16: use the layer API
 
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices)

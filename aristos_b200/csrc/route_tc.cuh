@@ -36,7 +36,7 @@ struct Control {
 
 }  // namespace route_tc
 
-template <int PXT>
+template <typename TE, int PXT>
 __global__ void __launch_bounds__(256, 1)
 route_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_wg,
                 RouteArgs a, DeviceStatus* status, long long wait_cycles, int epoch) {
@@ -56,7 +56,7 @@ route_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     volatile int* abort_flag = &ctl->abort;
     const int row0 = blockIdx.x * BM;
     const int KB = a.H / BK;
-    constexpr uint32_t idesc = make_instr_desc_bf16(BM, PXT);
+    constexpr uint32_t idesc = make_instr_desc_16b(BM, PXT, Pack2<TE>::kMmaFormat);
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -157,7 +157,7 @@ route_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         // the four epilogue warps share the logit tile: meet before the coalesced store
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (ok && !*abort_flag) {
-            __nv_bfloat16* probs = static_cast<__nv_bfloat16*>(a.probs);
+            TE* probs = static_cast<TE*>(a.probs);
             const int et = tid - 128;
             // two adjacent probabilities per thread, 4-byte stores (PX == PXT)
             for (int idx = 2 * et; idx < BM * PXT; idx += 256) {
@@ -166,8 +166,8 @@ route_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const float m = rowmax[rr], inv = rowden[rr];
                 const float p0 = e < a.E ? __expf(Ls[rr * Sh::LDL + e] - m) * inv : 0.f;
                 const float p1 = e + 1 < a.E ? __expf(Ls[rr * Sh::LDL + e + 1] - m) * inv : 0.f;
-                *reinterpret_cast<__nv_bfloat162*>(probs + (size_t)(row0 + rr) * PXT + e) =
-                    __floats2bfloat162_rn(p0, p1);
+                *reinterpret_cast<typename Pack2<TE>::type*>(probs + (size_t)(row0 + rr) * PXT + e) =
+                    Pack2<TE>::from_f2(p0, p1);
             }
         }
     }

@@ -119,11 +119,15 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
     return d;
 }
 
-// Instruction descriptor: D fp32 (bits 4-5 = 1), A and B bf16 (bits 7-9, 10-12 = 1), both
-// K-major (bits 15, 16 = 0), N >> 3 in bits 17-22, M >> 4 in bits 24-28.
-__host__ __device__ constexpr uint32_t make_instr_desc_bf16(int m, int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+// Instruction descriptor of kind::f16: D fp32 (bits 4-5 = 1), A and B format in bits 7-9 and
+// 10-12 (0 = f16, 1 = bf16), both K-major (bits 15, 16 = 0), N >> 3 in bits 17-22, M >> 4 in
+// bits 24-28.
+__host__ __device__ constexpr uint32_t make_instr_desc_16b(int m, int n, uint32_t fmt) {
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
            (static_cast<uint32_t>(m >> 4) << 24);
+}
+__host__ __device__ constexpr uint32_t make_instr_desc_bf16(int m, int n) {
+    return make_instr_desc_16b(m, n, 1u);
 }
 
 __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,

@@ -265,24 +265,25 @@ __global__ void __launch_bounds__(256) combine_kernel(CombineArgs a) {
                 if (c >= chunks) break;
                 uint4 o;
                 if constexpr (sizeof(T) == 2) {
-                    // bf16: Element(y / mCw) is one fp32 multiply and a packed round; the product
+                    // 16-bit elements: Element(y / mCw) is one fp32 multiply and a packed round; the product
                     // with the bf16 probability and the running sum are single-rounding bf16x2
                     // instructions, which is exactly the element-type arithmetic of the
                     // reference's combine
-                    __nv_bfloat162 acc2[4];
+                    using P2 = Pack2<T>;
+                    typename P2::type acc2[4];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) acc2[i] = __floats2bfloat162_rn(0.f, 0.f);
+                    for (int i = 0; i < 4; ++i) acc2[i] = P2::from_f2(0.f, 0.f);
 #pragma unroll
                     for (int j = 0; j < KMAX; ++j)
                         if (j < K && yrow[j] != nullptr) {
-                            const __nv_bfloat162* y2 = reinterpret_cast<const __nv_bfloat162*>(&raw[u][j]);
-                            const __nv_bfloat162 pj = __floats2bfloat162_rn(p[j], p[j]);
+                            const typename P2::type* y2 = reinterpret_cast<const typename P2::type*>(&raw[u][j]);
+                            const typename P2::type pj = P2::from_f2(p[j], p[j]);
 #pragma unroll
                             for (int i = 0; i < 4; ++i) {
                                 if (K > 1) {
-                                    const float2 yf = __bfloat1622float2(y2[i]);
-                                    const __nv_bfloat162 v = __floats2bfloat162_rn(yf.x * inv_w, yf.y * inv_w);
-                                    acc2[i] = __hadd2(acc2[i], __hmul2(pj, v));
+                                    const float2 yf = P2::to_f2(y2[i]);
+                                    const typename P2::type v = P2::from_f2(yf.x * inv_w, yf.y * inv_w);
+                                    acc2[i] = P2::add(acc2[i], P2::mul(pj, v));
                                 } else {
                                     acc2[i] = y2[i];
                                 }

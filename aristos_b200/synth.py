@@ -45,6 +45,8 @@ def round_to_dtype(x: np.ndarray, torch_dtype: int) -> np.ndarray:
         return np.asarray(x, dtype=np.float32)
     if torch_dtype == 2:
         return round_bf16(x)
+    if torch_dtype == 3:
+        return np.asarray(x, dtype=np.float32).astype(np.float16).astype(np.float32)
     raise NotImplementedError(f"torch_dtype {torch_dtype}")
 
 
@@ -99,6 +101,8 @@ def encode(buf_f32: np.ndarray, torch_dtype: int) -> np.ndarray:
         return np.ascontiguousarray(buf_f32, dtype=np.float32)
     if torch_dtype == 2:
         return to_bf16_bits(buf_f32)
+    if torch_dtype == 3:
+        return np.asarray(buf_f32, dtype=np.float32).astype(np.float16).view(np.uint16)
     raise NotImplementedError(f"torch_dtype {torch_dtype}")
 
 
@@ -107,6 +111,8 @@ def decode(raw: np.ndarray, torch_dtype: int) -> np.ndarray:
         return np.asarray(raw, dtype=np.float32)
     if torch_dtype == 2:
         return from_bf16_bits(np.asarray(raw, dtype=np.uint16))
+    if torch_dtype == 3:
+        return np.asarray(raw, dtype=np.uint16).view(np.float16).astype(np.float32)
     raise NotImplementedError(f"torch_dtype {torch_dtype}")
 
 

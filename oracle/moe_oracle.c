@@ -37,7 +37,7 @@
 
 typedef struct {
     int S, H, I, E, K, EC, PX;
-    int dtype;      /* 0 fp32, 2 bf16 */
+    int dtype;      /* 0 fp32, 2 bf16, 3 fp16 */
     int hidden_act; /* 0 relu, 1 gelu */
     int world;
 } oracle_cfg;
@@ -60,12 +60,16 @@ static inline float round_bf16(float x) {
     return x;
 }
 
-static inline float round_elem(float x, int dtype) { return dtype == 2 ? round_bf16(x) : x; }
+static inline float round_f16(float x) { return (float)(_Float16)x; }
+
+static inline float round_elem(float x, int dtype) {
+    return dtype == 2 ? round_bf16(x) : dtype == 3 ? round_f16(x) : x;
+}
 
 void oracle_round(float* x, size_t n, int dtype) {
-    if (dtype != 2) return;
+    if (dtype != 2 && dtype != 3) return;
 #pragma omp parallel for schedule(static)
-    for (size_t i = 0; i < n; ++i) x[i] = round_bf16(x[i]);
+    for (size_t i = 0; i < n; ++i) x[i] = round_elem(x[i], dtype);
 }
 
 /* Y[r][j] = sum_k X[r][k] * W[j][k] + bias[j], fp64 or fp32 accumulation. */

@@ -46,7 +46,11 @@ def _round_bf16(x: np.ndarray) -> np.ndarray:
 
 def round_elem(x: np.ndarray, torch_dtype: int) -> np.ndarray:
     x = np.asarray(x, dtype=np.float32)
-    return _round_bf16(x) if torch_dtype == 2 else x
+    if torch_dtype == 2:
+        return _round_bf16(x)
+    if torch_dtype == 3:
+        return x.astype(np.float16).astype(np.float32)
+    return x
 
 
 def _gelu(x: np.ndarray) -> np.ndarray:

@@ -7,8 +7,8 @@ import numpy as np
 from aristos_b200 import kleos, synth
 from aristos_b200.config import KleosConfig
 
-TOL = {0: 1e-5, 2: 2e-2}  # max_abs(y - y_ref) / max_abs(y_ref): fp32, bf16 (fp32 accumulation)
-PROB_TOL = {0: 2e-6, 2: 4e-3}  # absolute, gate probabilities (bf16: one ulp at p ~ 0.5)
+TOL = {0: 1e-5, 2: 2e-2, 3: 4e-3}  # max_abs(y - y_ref) / max_abs(y_ref): fp32, bf16, fp16 (fp32 accumulation)
+PROB_TOL = {0: 2e-6, 2: 4e-3, 3: 5e-4}  # absolute, gate probabilities (one element ulp at p ~ 0.5)
 
 
 def make_inputs(cfg: KleosConfig, world: int, seed: int = 0):

@@ -17,7 +17,7 @@ def _small(dtype, **kw):
     return KleosConfig(**base)
 
 
-@pytest.mark.parametrize("dtype", [0, 2])
+@pytest.mark.parametrize("dtype", [0, 2, 3])
 def test_c1_shape_full_parity(dtype):
     cfg = _small(dtype)
     packed, views = hz.make_inputs(cfg, 1)
@@ -45,6 +45,8 @@ def test_repeat_forwards_and_host_path(dtype):
     (2, dict(num_experts=8, sequence_len=256, hidden_size=256, intermediate_size=512, expert_top_k=4)),
     (2, dict(hidden_act=1)),                  # GELU
     (0, dict(hidden_act=1)),
+    (3, dict(hidden_act=1, num_experts=128, sequence_len=512, hidden_size=256,
+             intermediate_size=320)),          # fp16, GELU, PX = 128
     (2, dict(drop_tokens=0, sequence_len=128, hidden_size=128, intermediate_size=128)),
 ])
 def test_shapes_and_modes(dtype, kw):
