@@ -47,7 +47,7 @@ struct State {
     LayerConfig cfg;
     int rank = 0, world = 1, nLx = 0;
     uint32_t epoch = 0;
-    long long wait_cycles = 4000000000LL;  // about two seconds of SM clock
+    long long wait_cycles = 20000000000LL;  // about ten seconds of SM clock (ranks may start far apart)
     bool use_tc = false;
     bool suppress_return_flag = false;  // test hook: see kleos_debug_suppress_return_flag
     bool use_pair = true;

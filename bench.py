@@ -28,7 +28,7 @@ sys.path.insert(0, ROOT)
 from aristos_b200.config import baseline_config  # noqa: E402
 
 METRIC = "moe_layer_fwd_tokens_per_s"
-KERNELS_PER_FORWARD = 8  # route, refine, slots, dispatch, plan, GEMM1, GEMM2, combine
+KERNELS_PER_FORWARD = 9  # route, refine, tile histogram, slots, dispatch, plan, GEMM1, GEMM2, combine
 
 
 def workload(name: str):
@@ -75,7 +75,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "50"],
+                 "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -227,6 +227,9 @@ def run_cuda(args):
     kleos.set_device(local_rank)
     info = kleos.initialize(cfg, rank, world, uid)
     iP = synth_on_device(cfg, rank, world, device)
+    if args.workload == "C4":
+        from aristos_b200 import synth
+        kleos.set_gate_bias(synth.zipf_gate_bias(cfg, 1.2))  # Zipf(1.2) expert popularity
     oP = torch.zeros(info.output_elems, dtype=torch.bfloat16, device=device)
     stream = torch.cuda.current_stream().cuda_stream
 
@@ -244,6 +247,7 @@ def run_cuda(args):
         return float(t.item())
 
     # ---------------------------------------------------------------- device-resident timing
+    barrier()  # ranks finish generating their inputs at different times
     for _ in range(args.warmup):
         kleos.forward_host(iP, oP, stream)
     barrier()
@@ -289,15 +293,21 @@ def run_cuda(args):
     # pairs this rank's experts processed: under even sharding and random routing this equals
     # the pairs it dispatched to within sampling noise; the all-rank sum is identical
     pairs = torch.tensor([routed_here], dtype=torch.float64, device=device)
+    routed_vec = torch.from_numpy(np.minimum(routing["counts"], info.EC).astype(np.float64)).to(device)
     if world > 1:
         dist.all_reduce(pairs)
+        dist.all_reduce(routed_vec)
     pairs_per_rank = float(pairs.item()) / world
+    # experts of this rank that received at least one row (the weights of the others are never read)
+    lo = rank * info.local_experts
+    active_experts = int((routed_vec[lo:lo + info.local_experts] > 0).sum().item())
     peaks = load_peaks()
     # dominant kernel: one FFN GEMM launch (GEMM1 and GEMM2 do the same work when H == I).
-    # Algorithmic work per launch: 2*R*H*I FLOP; bytes = this rank's expert weights once, the
-    # R operand rows in and the R result rows out (R = routed pairs this rank's experts process).
+    # Algorithmic work per launch: 2*R*H*I FLOP; bytes = the weights of this rank's experts that
+    # received rows, once, plus the R operand rows in and the R result rows out (R = routed
+    # pairs this rank's experts process).
     gemm_flops = 2.0 * pairs_per_rank * cfg.H * cfg.I
-    gemm_bytes = (info.local_experts * cfg.I * cfg.H + pairs_per_rank * (cfg.H + cfg.I)) * 2.0
+    gemm_bytes = (active_experts * cfg.I * cfg.H + pairs_per_rank * (cfg.H + cfg.I)) * 2.0
     gemm_ms = 0.5 * (phases["gemm1"] + phases["gemm2"])
     gemm_ms = max_over_ranks(gemm_ms)
     tflops = gemm_flops / (gemm_ms * 1e-3) / 1e12
@@ -361,7 +371,8 @@ def main():
     ap.add_argument("--steps", type=int, default=32)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
-    ap.add_argument("--workload", default="C3", help="C3 (default), C3q (profiling size), C5")
+    ap.add_argument("--workload", default="C3",
+                    help="C3 (default), C4 (Zipf-imbalanced), C5 (large FFN), C3q / C3r8 (profiling sizes)")
     ap.add_argument("--cpu-sample", type=int, default=0,
                     help="tokens in the CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
