@@ -333,10 +333,28 @@ __global__ void __launch_bounds__(256) slot_kernel(SlotArgs a) {
     const int tid = threadIdx.x, b = blockIdx.x;
     const int tok0 = b * kSlotTile;
     const bool last = b == (int)gridDim.x - 1;
-    for (int e = tid; e < a.E; e += blockDim.x) {
+    // base slot of every expert = sum of the earlier tiles' histograms; the tiles are split
+    // over the threads that share an expert so the loads are independent and coalesced
+    __shared__ int part[256];
+    {
+        int ep = 1;
+        while (ep < a.E) ep <<= 1;            // experts rounded up to a power of two (<= 256)
+        const int groups = blockDim.x / ep;   // threads per expert
+        const int e = tid % ep, grp = tid / ep;
         int run = 0;
-        for (int t = 0; t < b; ++t) run += a.tile_hist[(size_t)t * a.E + e];
-        base[e] = run;
+        if (e < a.E && grp < groups)
+            for (int t = grp; t < b; t += groups) run += a.tile_hist[(size_t)t * a.E + e];
+        part[tid] = run;
+        __syncthreads();
+        if (tid < a.E) {
+            int sum = 0;
+            for (int gi = 0; gi < groups; ++gi) sum += part[gi * ep + tid];
+            base[tid] = sum;
+        }
+        __syncthreads();
+    }
+    for (int e = tid; e < a.E; e += blockDim.x) {
+        const int run = base[e];
         if (last) {
             const int total = run + a.tile_hist[(size_t)b * a.E + e];
             a.counts[e] = (unsigned)total;
