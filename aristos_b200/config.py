@@ -66,7 +66,7 @@ class KleosConfig:
         return self.hidden_size
 
     @property
-    def I(self) -> int:  # noqa: E743 - the reference calls it P, BASELINE calls it I
+    def I(self) -> int:  # noqa: E743 - the reference calls it P (types.cuh:472)
         return self.intermediate_size
 
     @property

@@ -28,7 +28,7 @@ def test_cpp_and_python_derive_the_same_sizes(tmp_path, name, world):
     assert info.elem_bytes == cfg.elem_bytes
 
 
-def test_survey_table_values():
+def test_benchmark_layer_table_values():
     """EC / pEC / PX of the five benchmark layers."""
     expect = {"C1": (64, 128, 64), "C2": (512, 512, 64), "C3": (256, 256, 64),
               "C4": (320, 384, 128), "C5": (1024, 1024, 64)}
