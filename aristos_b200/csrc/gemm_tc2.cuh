@@ -39,22 +39,23 @@
 namespace kleos {
 namespace gemm_tc2 {
 
-constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16, STAGES = 6;
-constexpr int A_STAGE_BYTES = BM * BK * 2;        // 16 KiB: this block's panel
-constexpr int B_STAGE_BYTES = (BN / 2) * BK * 2;  // 16 KiB: this block's half of the weight tile
-constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16;
+constexpr int kSlices = 6;                        // 64-wide K slices of shared memory in total
+constexpr int A_STAGE_BYTES = BM * BK * 2;        // 16 KiB: one K slice of this block's panel
+constexpr int B_STAGE_BYTES = (BN / 2) * BK * 2;  // 16 KiB: one K slice of this block's half weight tile
+constexpr int SLICE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int TMEM_COLS = 512;  // two accumulators of 256 fp32 columns
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 28672;
+constexpr int SMEM_BYTES = kSlices * SLICE_BYTES + 1024 + 28672;
 constexpr int kMaxFusedPanels = 384;
 constexpr int kFusedThreads = 256;
 constexpr int kDispatchUnit = 4;    // consecutive rows of one cell a mover lane copies between two publications
-constexpr int kRowBufBytes = STAGES * STAGE_BYTES;  // a dispatcher block's row buffers: the stage area
+constexpr int kRowBufBytes = kSlices * SLICE_BYTES;  // a dispatcher block's row buffers: the stage area
 constexpr int kMaxMovers = 48;      // mover lanes per dispatcher block, one row buffer each
 
 
 struct Control {
-    unsigned long long full[STAGES];   // used on the leader
-    unsigned long long empty[STAGES];  // one per block
+    unsigned long long full[kSlices];   // used on the leader (one per pipeline stage)
+    unsigned long long empty[kSlices];  // one per block
     unsigned long long acc_full[2];    // one per block
     unsigned long long acc_empty[2];   // used on the leader, 8 arrivals (4 warps x 2 blocks)
     uint32_t tmem_base;
@@ -122,12 +123,16 @@ __device__ __forceinline__ int total_pair_tiles(const int* le_start, int le_begi
 
 // kEpi selects the fused epilogue at compile time (0: bias + ReLU, 1: bias + GELU, 2: bias only)
 // so the read-back loop stays a short straight-line sequence.
-template <typename TE, int kEpi, bool kFused>
+// kSub = 64-wide K slices per pipeline stage: 1 gives six shallow stages (best when the weights
+// stream from HBM), 2 gives three deep stages and half the barrier round trips (best when the
+// operands come from L2 and the tensor pipe is the limit).
+template <typename TE, int kEpi, bool kFused, int kSub>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFused ? gemm_tc2::kFusedThreads : 256, 1)
 ffn_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
              GemmArgs g, gemm_tc2::FusedArgs f) {
     using namespace tc;
     using namespace gemm_tc2;
+    constexpr int SUB = kSub, STAGES = kSlices / kSub, STAGE_BYTES = kSub * SLICE_BYTES;
     constexpr int NST = STAGES;
     constexpr uint32_t kInstrDesc = make_instr_desc_16b(2 * BM, BN, Pack2<TE>::kMmaFormat);
     using TE2 = typename Pack2<TE>::type;
@@ -135,7 +140,7 @@ ffn_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = reinterpret_cast<uint8_t*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    Control* ctl = reinterpret_cast<Control*>(tiles + STAGES * STAGE_BYTES);
+    Control* ctl = reinterpret_cast<Control*>(tiles + kSlices * SLICE_BYTES);
     __shared__ bool last_block;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -253,7 +258,8 @@ ffn_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
 
     const int NT = (g.N + BN - 1) / BN;
     const int total = total_pair_tiles(ctl->le_start, g.le_begin, g.le_end, NT);
-    const int KB = g.Kd / BK;
+    const int KS = g.Kd / BK;                 // 64-wide K slices
+    const int KB = (KS + SUB - 1) / SUB;      // pipeline stages per tile
     const int n_clusters = ((int)gridDim.x - n_disp) >> 1, cluster_id = blockIdx.x >> 1;
 
     if (dispatcher) {
@@ -299,11 +305,16 @@ ffn_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
                         break;
                     }
                     // the leader announces the bytes of both blocks on its own barrier
-                    if (leader) mbar_expect_tx(&ctl->full[s], 2 * STAGE_BYTES);
+                    const int nsub = min(SUB, KS - kb * SUB);
+                    if (leader) mbar_expect_tx(&ctl->full[s], 2 * nsub * SLICE_BYTES);
                     const uint32_t full_leader = map_to_cta(smem_u32(&ctl->full[s]), 0);
                     uint8_t* sa = tiles + s * STAGE_BYTES;
-                    tma_load_2d_pair(sa, &map_a, kb * BK, p.row_base, full_leader);
-                    tma_load_2d_pair(sa + A_STAGE_BYTES, &map_b, kb * BK, brow, full_leader);
+                    for (int sub = 0; sub < nsub; ++sub) {
+                        const int kx = (kb * SUB + sub) * BK;
+                        tma_load_2d_pair(sa + sub * SLICE_BYTES, &map_a, kx, p.row_base, full_leader);
+                        tma_load_2d_pair(sa + sub * SLICE_BYTES + A_STAGE_BYTES, &map_b, kx, brow,
+                                         full_leader);
+                    }
                 }
             }
             if (g.stats) {
@@ -340,12 +351,15 @@ ffn_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
                     }
                     tc_fence_after();
                     const uint32_t sa = smem_u32(tiles + s * STAGE_BYTES);
-                    const uint64_t da = make_smem_desc(sa);
-                    const uint64_t db = make_smem_desc(sa + A_STAGE_BYTES);
+                    const int nsub = min(SUB, KS - kb * SUB);
+                    for (int sub = 0; sub < nsub; ++sub) {
+                        const uint64_t da = make_smem_desc(sa + sub * SLICE_BYTES);
+                        const uint64_t db = make_smem_desc(sa + sub * SLICE_BYTES + A_STAGE_BYTES);
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k)
-                        umma_bf16_pair(d_tmem, da + 2 * k, db + 2 * k, kInstrDesc,
-                                       (kb | k) != 0 ? 1u : 0u);
+                        for (int k = 0; k < BK / UMMA_K; ++k)
+                            umma_bf16_pair(d_tmem, da + 2 * k, db + 2 * k, kInstrDesc,
+                                           (kb | sub | k) != 0 ? 1u : 0u);
+                    }
                     // the stage is free in both blocks once these MMAs have read it
                     const uint32_t e_local = smem_u32(&ctl->empty[s]);
                     umma_commit_pair(map_to_cta(e_local, 0));

@@ -267,6 +267,17 @@ int launch_route(const RouteArgs& ra, cudaStream_t st) {
     return KLEOS_OK;
 }
 
+// The paired GEMM comes in two pipeline shapes (see gemm_tc2.cuh): deep = three 128-wide stages,
+// otherwise six 64-wide stages.
+template <typename TE, int kEpi, bool kFused>
+void launch_tc2(bool deep, int grid, int threads, cudaStream_t st, const CUtensorMap& map_a,
+                const CUtensorMap& map_b, const GemmArgs& ga, const gemm_tc2::FusedArgs& fa) {
+    if (deep)
+        ffn_gemm_tc2<TE, kEpi, kFused, 2><<<grid, threads, gemm_tc2::SMEM_BYTES, st>>>(map_a, map_b, ga, fa);
+    else
+        ffn_gemm_tc2<TE, kEpi, kFused, 1><<<grid, threads, gemm_tc2::SMEM_BYTES, st>>>(map_a, map_b, ga, fa);
+}
+
 // Optional replacement of the activation input and the layer-output destination of one
 // forward (used by the pipelined host path, whose staging buffers live outside iP / oP).
 struct Staging {
@@ -397,6 +408,9 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed, const S
         if constexpr (sizeof(T) == 2) {
             if (g.use_pair) {
                 const int grid = g.sm_count & ~1;
+                // deep stages when an expert sees enough rows for the tensor pipe, not the weight
+                // stream from HBM, to be the limit (about 260 FLOP per weight byte on this part)
+                const bool deep = (long long)g.world * c.EC >= 512;
                 gemm_tc2::FusedArgs fa{};
                 fa.tokens = s.A; fa.cell_tokens = g.cell_tokens; fa.counts = g.counts;
                 fa.cell_done = g.cell_done; fa.panels_out = g.panels; fa.le_start_out = g.le_start;
@@ -405,21 +419,21 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed, const S
                 if (fused) {
                     const int thr = gemm_tc2::kFusedThreads;
                     if (c.hidden_act == 0)
-                        ffn_gemm_tc2<T, 0, true><<<grid, thr, gemm_tc2::SMEM_BYTES, st>>>(g.map_x, g.map_w1h, g1, fa);
+                        launch_tc2<T, 0, true>(deep, grid, thr, st, g.map_x, g.map_w1h, g1, fa);
                     else
-                        ffn_gemm_tc2<T, 1, true><<<grid, thr, gemm_tc2::SMEM_BYTES, st>>>(g.map_x, g.map_w1h, g1, fa);
+                        launch_tc2<T, 1, true>(deep, grid, thr, st, g.map_x, g.map_w1h, g1, fa);
                 }
                 for (int p = 0; p < parts && !fused; ++p) {
                     if ((rc = next_part(p))) return rc;
                     g1.le_begin = p * g.nLx / parts;
                     g1.le_end = (p + 1) * g.nLx / parts;
                     if (c.hidden_act == 0)
-                        ffn_gemm_tc2<T, 0, false><<<grid, 256, gemm_tc2::SMEM_BYTES, st>>>(g.map_x, g.map_w1h, g1, fa);
+                        launch_tc2<T, 0, false>(deep, grid, 256, st, g.map_x, g.map_w1h, g1, fa);
                     else
-                        ffn_gemm_tc2<T, 1, false><<<grid, 256, gemm_tc2::SMEM_BYTES, st>>>(g.map_x, g.map_w1h, g1, fa);
+                        launch_tc2<T, 1, false>(deep, grid, 256, st, g.map_x, g.map_w1h, g1, fa);
                 }
                 KLEOS_CUDA(mark());
-                ffn_gemm_tc2<T, 2, false><<<grid, 256, gemm_tc2::SMEM_BYTES, st>>>(g.map_y1, g.map_w2h, g2, fa);
+                launch_tc2<T, 2, false>(deep, grid, 256, st, g.map_y1, g.map_w2h, g2, fa);
                 KLEOS_CUDA(mark());
             } else {
                 for (int p = 0; p < parts; ++p) {
@@ -478,11 +492,16 @@ int set_tc_attributes() {
     const auto dyn = cudaFuncAttributeMaxDynamicSharedMemorySize;
     KLEOS_CUDA(cudaFuncSetAttribute(route_tc_kernel<TE, 64>, dyn, route_tc::Shape<64>::SMEM_BYTES));
     KLEOS_CUDA(cudaFuncSetAttribute(route_tc_kernel<TE, 128>, dyn, route_tc::Shape<128>::SMEM_BYTES));
-    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<TE, 0, false>, dyn, gemm_tc2::SMEM_BYTES));
-    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<TE, 1, false>, dyn, gemm_tc2::SMEM_BYTES));
-    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<TE, 2, false>, dyn, gemm_tc2::SMEM_BYTES));
-    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<TE, 0, true>, dyn, gemm_tc2::SMEM_BYTES));
-    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<TE, 1, true>, dyn, gemm_tc2::SMEM_BYTES));
+    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<TE, 0, false, 1>, dyn, gemm_tc2::SMEM_BYTES));
+    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<TE, 0, false, 2>, dyn, gemm_tc2::SMEM_BYTES));
+    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<TE, 1, false, 1>, dyn, gemm_tc2::SMEM_BYTES));
+    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<TE, 1, false, 2>, dyn, gemm_tc2::SMEM_BYTES));
+    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<TE, 2, false, 1>, dyn, gemm_tc2::SMEM_BYTES));
+    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<TE, 2, false, 2>, dyn, gemm_tc2::SMEM_BYTES));
+    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<TE, 0, true, 1>, dyn, gemm_tc2::SMEM_BYTES));
+    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<TE, 0, true, 2>, dyn, gemm_tc2::SMEM_BYTES));
+    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<TE, 1, true, 1>, dyn, gemm_tc2::SMEM_BYTES));
+    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<TE, 1, true, 2>, dyn, gemm_tc2::SMEM_BYTES));
     KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc<TE, 0>, dyn, gemm_tc::SMEM_BYTES));
     KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc<TE, 1>, dyn, gemm_tc::SMEM_BYTES));
     KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc<TE, 2>, dyn, gemm_tc::SMEM_BYTES));
