@@ -43,19 +43,36 @@ __global__ void __launch_bounds__(256) ffn_gemm_simt(GemmArgs g) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
 
-        for (int k0 = 0; k0 < g.Kd; k0 += BK) {
-            float av[8], bv[8];
+        // software pipeline: the global loads of K step k+1 are in flight while step k is
+        // multiplied out of shared memory
+        float av[8], bv[8];
+        auto fetch = [&](int k0) {
+            // eight consecutive K elements per thread, as 16-byte loads
+            constexpr int NV = 8 * sizeof(T) / 16;
+            uint4 ra[NV], rb[NV];
+#pragma unroll
+            for (int v = 0; v < NV; ++v) {
+                ra[v] = __ldg(reinterpret_cast<const uint4*>(arow + k0 + lk) + v);
+                rb[v] = brow_ok ? __ldg(reinterpret_cast<const uint4*>(brow + k0 + lk) + v)
+                                : make_uint4(0u, 0u, 0u, 0u);
+            }
+            const T* ea = reinterpret_cast<const T*>(ra);
+            const T* eb = reinterpret_cast<const T*>(rb);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                av[i] = Elem<T>::to_f(arow[k0 + lk + i]);
-                bv[i] = brow_ok ? Elem<T>::to_f(brow[k0 + lk + i]) : 0.f;
+                av[i] = Elem<T>::to_f(ea[i]);
+                bv[i] = Elem<T>::to_f(eb[i]);
             }
+        };
+        fetch(0);
+        for (int k0 = 0; k0 < g.Kd; k0 += BK) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 As[lk + i][lrow] = av[i];
                 Bs[lk + i][lrow] = bv[i];
             }
             __syncthreads();
+            if (k0 + BK < g.Kd) fetch(k0 + BK);
 #pragma unroll
             for (int k = 0; k < BK; ++k) {
                 const float4 a0 = *reinterpret_cast<const float4*>(&As[k][ty * 8]);

@@ -113,27 +113,33 @@ class ClockSampler:
                     samples=len(sm))
 
 
+def torch_dtype_of(cfg):
+    import torch
+    return {0: torch.float32, 2: torch.bfloat16, 3: torch.float16}[cfg.torch_dtype]
+
+
 def synth_on_device(cfg, rank, world, device):
     """Packed bf16 input of one rank, generated on the GPU: activations N(0,1) seeded by rank,
     gate and expert weights N(0, 1/sqrt(fan_in)) seeded per global expert, zero biases."""
     import torch
+    tdt = torch_dtype_of(cfg)
     off = cfg.input_offsets(world)
     nlx = cfg.local_experts(world)
-    buf = torch.zeros(off["end"], dtype=torch.bfloat16, device=device)
+    buf = torch.zeros(off["end"], dtype=tdt, device=device)
     gen = torch.Generator(device=device)
     gen.manual_seed(1000 + rank)
-    buf[off["A"]:off["Wg"]] = torch.randn(cfg.S * cfg.H, generator=gen, device=device).bfloat16()
+    buf[off["A"]:off["Wg"]] = torch.randn(cfg.S * cfg.H, generator=gen, device=device).to(tdt)
     gen.manual_seed(7)
     buf[off["Wg"]:off["Wg"] + cfg.E * cfg.H] = (
-        torch.randn(cfg.E * cfg.H, generator=gen, device=device) / cfg.H ** 0.5).bfloat16()
+        torch.randn(cfg.E * cfg.H, generator=gen, device=device) / cfg.H ** 0.5).to(tdt)
     ih = cfg.I * cfg.H
     for le in range(nlx):
         e = rank * nlx + le
         gen.manual_seed(100000 + e)
         buf[off["W1"] + le * ih: off["W1"] + (le + 1) * ih] = (
-            torch.randn(ih, generator=gen, device=device) / cfg.H ** 0.5).bfloat16()
+            torch.randn(ih, generator=gen, device=device) / cfg.H ** 0.5).to(tdt)
         buf[off["W2"] + le * ih: off["W2"] + (le + 1) * ih] = (
-            torch.randn(ih, generator=gen, device=device) / cfg.I ** 0.5).bfloat16()
+            torch.randn(ih, generator=gen, device=device) / cfg.I ** 0.5).to(tdt)
     return buf
 
 
@@ -222,15 +228,15 @@ def run_cuda(args):
         uid = bytes(idt.cpu().numpy().tobytes())
 
     cfg, workload_desc = workload(args.workload)
-    if cfg.torch_dtype != 2:
-        raise SystemExit("bench.py drives the bf16 layers")
+    tdt = torch_dtype_of(cfg)
+    eb = cfg.elem_bytes
     kleos.set_device(local_rank)
     info = kleos.initialize(cfg, rank, world, uid)
     iP = synth_on_device(cfg, rank, world, device)
     if args.workload == "C4":
         from aristos_b200 import synth
         kleos.set_gate_bias(synth.zipf_gate_bias(cfg, 1.2))  # Zipf(1.2) expert popularity
-    oP = torch.zeros(info.output_elems, dtype=torch.bfloat16, device=device)
+    oP = torch.zeros(info.output_elems, dtype=tdt, device=device)
     stream = torch.cuda.current_stream().cuda_stream
 
     def barrier():
@@ -268,9 +274,9 @@ def run_cuda(args):
 
     # ---------------------------------------------------------------- end to end, host buffers
     act_elems = cfg.S * cfg.H
-    host_in = torch.empty(act_elems, dtype=torch.bfloat16).pin_memory()
+    host_in = torch.empty(act_elems, dtype=tdt).pin_memory()
     host_in.copy_(iP[:act_elems].cpu())
-    host_out = torch.empty(act_elems, dtype=torch.bfloat16).pin_memory()
+    host_out = torch.empty(act_elems, dtype=tdt).pin_memory()
     # every step copies its activations from pinned host memory and its layer output back; the
     # library overlaps the copies of neighbouring steps with the forward (three streams)
     for _ in range(max(2, args.warmup // 2)):
@@ -307,11 +313,14 @@ def run_cuda(args):
     # received rows, once, plus the R operand rows in and the R result rows out (R = routed
     # pairs this rank's experts process).
     gemm_flops = 2.0 * pairs_per_rank * cfg.H * cfg.I
-    gemm_bytes = (active_experts * cfg.I * cfg.H + pairs_per_rank * (cfg.H + cfg.I)) * 2.0
+    gemm_bytes = (active_experts * cfg.I * cfg.H + pairs_per_rank * (cfg.H + cfg.I)) * float(eb)
     gemm_ms = 0.5 * (phases["gemm1"] + phases["gemm2"])
     gemm_ms = max_over_ranks(gemm_ms)
     tflops = gemm_flops / (gemm_ms * 1e-3) / 1e12
     gbs = gemm_bytes / (gemm_ms * 1e-3) / 1e9
+    if cfg.torch_dtype == 0:
+        # float layers run on FP32 FMA (as in the reference): nominal 148 SMs x 128 FMA x 1.965 GHz
+        peaks = dict(peaks, tflops=74.4, source="nominal fp32 FMA rate (no measured figure)")
     hbm_bound = gemm_bytes / (peaks["hbm"] * 1e9) > gemm_flops / (peaks["tflops"] * 1e12)
     if hbm_bound:
         roof = dict(bound="hbm", achieved=gbs, peak=peaks["hbm"], unit="GB/s", frac=gbs / peaks["hbm"])
@@ -321,13 +330,14 @@ def run_cuda(args):
     # DRAM traffic per launch from the ncu capture of the quarter-size layer (155.3 MB, see
     # profiles/), scaled by the units processed (experts x4, routed rows x4); one-GPU C3 only
     roof["traffic"] = 621.2e6 if (world == 1 and args.workload == "C3") else None
-    roof.update(kernel="ffn_gemm_tc2 (mean of the GEMM1 and GEMM2 launches)",
+    roof.update(kernel=("ffn_gemm_simt" if cfg.torch_dtype == 0 else "ffn_gemm_tc2") +
+                " (mean of the GEMM1 and GEMM2 launches)",
                 peak_source=peaks["source"], tensor_tflops=tflops, hbm_gbs=gbs,
                 algorithmic_bytes=gemm_bytes, algorithmic_flops=gemm_flops,
                 launch_ms=gemm_ms)
     total_flops = 2.0 * cfg.S * cfg.H * cfg.E + 4.0 * cfg.H * cfg.I * pairs_per_rank
     remote_pairs = pairs_per_rank * (world - 1) / world
-    link_bytes = 2.0 * remote_pairs * cfg.H * 2
+    link_bytes = 2.0 * remote_pairs * cfg.H * eb
     t_roof_ms = max(total_flops / (peaks["tflops"] * 1e12), link_bytes / 770e9) * 1e3
     ms_per_step = ms_total / args.steps
 
@@ -336,13 +346,13 @@ def run_cuda(args):
         line = dict(
             metric=METRIC, value=tokens / (ms_per_step * 1e-3), unit="tokens/s", n_gpus=world,
             steps=args.steps, warmup=args.warmup, ms_per_step=ms_per_step,
-            higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16",
+            higher_is_better=True, scaling="weak", vs_baseline=None, dtype=cfg.dtype_name,
             data="synthetic",
             config=dict(workload=workload_desc,
                         experts_per_rank=info.local_experts, parallelism=f"ep{world}",
                         l2="working set per step (weights + cells + activations) exceeds L2"),
             e2e=dict(value=tokens * args.steps / e2e_s, unit="tokens/s",
-                     h2d_bytes_per_step=act_elems * 2, d2h_bytes_per_step=act_elems * 2),
+                     h2d_bytes_per_step=act_elems * eb, d2h_bytes_per_step=act_elems * eb),
             gpu_launches=KERNELS_PER_FORWARD * args.steps,
             clocks=clocks,
             roofline=roof,
@@ -372,7 +382,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
     ap.add_argument("--workload", default="C3",
-                    help="C3 (default), C4 (Zipf-imbalanced), C5 (large FFN), C3q / C3r8 (profiling sizes)")
+                    help="C3 (default), C4 (Zipf-imbalanced), C5 (large FFN), C1 / C2 (float), "
+                         "C3q / C3r8 (profiling sizes)")
     ap.add_argument("--cpu-sample", type=int, default=0,
                     help="tokens in the CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
