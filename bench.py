@@ -147,6 +147,7 @@ def cpu_sample_tokens_per_s(cfg, views, sample_tokens: int, repeats: int = 1):
     """Times the C restatement of the reference's math (fp32 accumulation, all host threads)
     on the first `sample_tokens` tokens of one rank; routing covers all S tokens."""
     from oracle import c_oracle
+    c_oracle.use_all_cores()
     rows = np.arange(sample_tokens, dtype=np.int32)
     best = None
     for _ in range(repeats):

@@ -45,6 +45,18 @@ def num_threads() -> int:
     return lib().oracle_num_threads()
 
 
+def use_all_cores() -> int:
+    """Let the oracle use every core this process may run on (launchers such as torchrun export
+    OMP_NUM_THREADS=1); returns the thread count now in effect."""
+    import os
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    lib().oracle_set_threads(n)
+    return num_threads()
+
+
 def moe_forward_rank(cfg, world, rank, inputs, gate_bias=None, tokens=None, accum64=True):
     """Layer output for the tokens of one source rank; same result keys as the NumPy twin."""
     L = lib()

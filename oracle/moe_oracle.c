@@ -50,6 +50,15 @@ int oracle_num_threads(void) {
 #endif
 }
 
+/* Launchers often export OMP_NUM_THREADS=1; the timed baseline asks for the cores it may use. */
+void oracle_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 static inline float round_bf16(float x) {
     uint32_t u;
     memcpy(&u, &x, 4);
