@@ -2,8 +2,11 @@
 // neighbouring SMs computes a 256 x 256 output tile -- two 128-row panels of the same local
 // expert against the same 256 weight rows.  Each block TMA-loads its own panel (A) and only
 // HALF of the weight tile (B), so the bytes pulled into an SM per FLOP drop by a third compared
-// with one block per 128 x 256 tile, and the freed shared memory deepens the pipeline to six
-// stages.  No load is multicast: every block fetches exactly the bytes it keeps.
+// with one block per 128 x 256 tile.  Shared memory holds six 64-wide K slices per block, used
+// as six shallow or three deep pipeline stages (template parameter kSub).  The epilogue stages
+// its rows through a swizzled shared-memory tile so that every store instruction writes whole
+// 128-byte lines, also when the destination is a peer's cell.  No load is multicast: every block
+// fetches exactly the bytes it keeps.
 //
 // Per block, 256 threads:
 //   warp 0      TMA producer (one lane): waits on its own `empty`, loads into its own shared
@@ -26,7 +29,9 @@
 //     shared-memory row buffer -> the peer's cell over NVLink), local expert by local expert,
 //     and the mover that completes a cell raises that cell's data flag on the owner.  Movers
 //     placed inside the GEMM blocks were tried first and ran at a third of this speed: their
-//     copies queue behind the operand loads on the same SM's copy engine;
+//     copies queue behind the operand loads on the same SM's copy engine.  This variant is
+//     slower than the separate dispatch kernel at every world size measured so far and is
+//     therefore opt-in;
 //   * the TMA producer waits (bounded) for the data flag of a panel's cell before its first
 //     load of that cell, so expert GEMMs start while later cells are still in flight on NVLink.
 #pragma once

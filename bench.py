@@ -172,6 +172,8 @@ def run_reference(args):
         return
     import torch
     from aristos_b200 import synth
+    from oracle import c_oracle
+    torch.set_num_threads(c_oracle.use_all_cores())  # launchers export OMP_NUM_THREADS=1
     cfg, _ = baseline_config("C3")
     torch.manual_seed(0)
     off = cfg.input_offsets(1)
