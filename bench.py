@@ -257,12 +257,15 @@ def run_cuda(args):
 
     # ---------------------------------------------------------------- device-resident timing
     barrier()  # ranks finish generating their inputs at different times
-    for _ in range(args.warmup):
-        kleos.forward_host(iP, oP, stream)
-    barrier()
+    # clocks are sampled from the warm-up on (nvidia-smi needs some tens of milliseconds to
+    # deliver its first sample, longer than a short timed region) until the end-to-end pass ends
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+        time.sleep(0.2)
+    for _ in range(max(args.warmup, 64)):
+        kleos.forward_host(iP, oP, stream)
+    barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
