@@ -101,8 +101,15 @@ class KleosConfig:
     def dtype_name(self) -> str:
         return DTYPE_NAMES[self.torch_dtype]
 
+    @property
+    def dense(self) -> bool:
+        """A single-expert layer is the plain FFN (the reference switches kernels at E == 1,
+        moe/moe.cuh:174-177): no gate weight in the packed input, no probabilities in the
+        packed output (moe/fffn.cuh:47-53), and every rank holds the one expert."""
+        return self.E == 1
+
     def local_experts(self, world: int) -> int:
-        return self.E // world
+        return 1 if self.dense else self.E // world
 
     def owner(self, expert: int, world: int) -> int:
         """Contiguous even sharding (bootstrap.cuh:48-51)."""
@@ -111,18 +118,18 @@ class KleosConfig:
     # packed buffer sizes in elements (moe.cuh:92-98, main.cu:17-30)
     def input_elems(self, world: int) -> int:
         nlx = self.local_experts(world)
-        return (self.S * self.H + self.PX * self.H + 2 * nlx * self.I * self.H
-                + nlx * (self.I + self.H))
+        gate = 0 if self.dense else self.PX * self.H
+        return self.S * self.H + gate + 2 * nlx * self.I * self.H + nlx * (self.I + self.H)
 
     def output_elems(self) -> int:
-        return self.S * self.PX + self.S * self.H
+        return (0 if self.dense else self.S * self.PX) + self.S * self.H
 
     def input_offsets(self, world: int) -> dict:
         """Element offsets of the sections of the packed input buffer."""
         nlx = self.local_experts(world)
         a = 0
         wg = a + self.S * self.H
-        w1 = wg + self.PX * self.H
+        w1 = wg + (0 if self.dense else self.PX * self.H)
         w2 = w1 + nlx * self.I * self.H
         b1 = w2 + nlx * self.H * self.I
         b2 = b1 + nlx * self.I
@@ -145,7 +152,7 @@ class KleosConfig:
             raise ValueError("num_experts must be in [1, 65535]")
         if float(self.capacity_factor) < 1:
             raise ValueError("capacity_factor must be >= 1")
-        if world < 1 or self.num_experts % world:
+        if world < 1 or (not self.dense and self.num_experts % world):
             raise ValueError("num_experts must divide evenly over the world size")
 
     def to_json(self, path: str) -> None:

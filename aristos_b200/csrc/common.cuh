@@ -74,8 +74,10 @@ template <> struct Pack2<__half> {
 };
 
 __device__ __forceinline__ float apply_act(float z, int hidden_act) {
-    // 0: ReLU, 1: GELU (erf form), as selected by hidden_act (reference types.cuh:143-159)
+    // 0: ReLU, 1: GELU (erf form), as selected by hidden_act (reference types.cuh:143-159);
+    // 2: identity (second GEMM of the dense layer)
     if (hidden_act == 0) return fmaxf(z, 0.f);
+    if (hidden_act == 2) return z;
     return 0.5f * z * (1.f + erff(z * 0.70710678118654752f));
 }
 

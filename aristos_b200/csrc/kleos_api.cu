@@ -49,6 +49,10 @@ struct State {
     uint32_t epoch = 0;
     long long wait_cycles = 20000000000LL;  // about ten seconds of SM clock (ranks may start far apart)
     bool use_tc = false;
+    // num_experts == 1: the layer is a plain FFN over this rank's tokens (the reference switches
+    // to its fffn kernel, moe/moe.cuh:174-177,197-204): no gate, no exchange, and the packed
+    // buffers carry no gate weight and no probabilities (moe/fffn.cuh:47-53)
+    bool dense = false;
     bool suppress_return_flag = false;  // test hook: see kleos_debug_suppress_return_flag
     bool use_pair = true;
     bool use_fused = false; // experimental: dispatch + plan inside the GEMM1 kernel (KLEOS_FUSED=1)
@@ -215,28 +219,29 @@ Sections slice(const void* iP, void* oP) {
     Sections s;
     s.A = static_cast<const char*>(iP);
     s.Wg = s.A + (size_t)c.S * c.H * eb;
-    s.W1 = s.Wg + (size_t)c.PX * c.H * eb;
+    s.W1 = s.Wg + (g.dense ? 0 : (size_t)c.PX * c.H * eb);
     s.W2 = s.W1 + (size_t)g.nLx * c.I * c.H * eb;
     s.b1 = s.W2 + (size_t)g.nLx * c.H * c.I * eb;
     s.b2 = s.b1 + (size_t)g.nLx * c.I * eb;
     s.probs = static_cast<char*>(oP);
-    s.out = s.probs + (size_t)c.S * c.PX * eb;
+    s.out = s.probs + (g.dense ? 0 : (size_t)c.S * c.PX * eb);
     return s;
 }
 
 int ensure_maps(const Sections& s) {
     if (!g.use_tc || g.maps_for_iP == s.A) return KLEOS_OK;
     const LayerConfig& c = g.cfg;
-    const uint64_t cell_rows = (uint64_t)g.world * g.nLx * c.pEC;
+    // the dense layer multiplies the activations where they lie: S rows instead of the cells
+    const uint64_t cell_rows = g.dense ? (uint64_t)c.S : (uint64_t)g.world * g.nLx * c.pEC;
     int rc;
-    if ((rc = make_map(&g.map_x, g.arena + g.lay.xcell, cell_rows, c.H, gemm_tc::BM))) return rc;
+    if ((rc = make_map(&g.map_x, g.dense ? s.A : g.arena + g.lay.xcell, cell_rows, c.H, gemm_tc::BM))) return rc;
     if ((rc = make_map(&g.map_w1, s.W1, (uint64_t)g.nLx * c.I, c.H, gemm_tc::BN))) return rc;
     if ((rc = make_map(&g.map_y1, g.y1, cell_rows, c.I, gemm_tc::BM))) return rc;
     if ((rc = make_map(&g.map_w2, s.W2, (uint64_t)g.nLx * c.H, c.I, gemm_tc::BN))) return rc;
     const int promo = 3;  // 256-byte L2 promotion; 0/64/128 bytes measured the same on the C3 layer
     if ((rc = make_map(&g.map_w1h, s.W1, (uint64_t)g.nLx * c.I, c.H, gemm_tc2::BN / 2, 64, true, promo))) return rc;
     if ((rc = make_map(&g.map_w2h, s.W2, (uint64_t)g.nLx * c.H, c.I, gemm_tc2::BN / 2, 64, true, promo))) return rc;
-    if (c.PX <= 128) {
+    if (c.PX <= 128 && !g.dense) {
         if ((rc = make_map(&g.map_act, s.A, c.S, c.H, route_tc::BM))) return rc;
         if ((rc = make_map(&g.map_wg, s.Wg, c.PX, c.H, c.PX))) return rc;
     }
@@ -286,6 +291,60 @@ struct Staging {
     const CUtensorMap* map_act;
 };
 
+// num_experts == 1: out = (act(A W1^T + b1)) W2^T + b2 over this rank's S tokens, both GEMMs by
+// the expert-FFN kernels in their local-output mode over a fixed panel list (one panel per 128
+// tokens, written once at initialisation).  Follows the reference's dense kernel
+// (moe/fffn.cuh:31-167): intermediate rounded to the element type, identity epilogue on the
+// second GEMM, no gate, no scaling.
+template <typename T>
+int forward_dense(const Sections& s, const CUtensorMap* map_a, cudaStream_t st, bool timed) {
+    const LayerConfig& c = g.cfg;
+    int evi = 0;
+    auto mark = [&]() -> cudaError_t { return timed ? cudaEventRecord(g.ev[evi++], st) : cudaSuccess; };
+    for (int i = 0; i < 5; ++i) KLEOS_CUDA(mark());  // start, route, slots, dispatch, plan: nothing to do
+    GemmArgs ga{};
+    ga.panels = g.panels; ga.le_start = g.le_start; ga.peers = g.peers; ga.lay = g.lay;
+    ga.status = g.status; ga.wait_cycles = g.wait_cycles; ga.stats = nullptr;
+    ga.nLx = 1; ga.pEC = c.S; ga.rank = g.rank; ga.elem_bytes = c.elem_bytes; ga.epoch = g.epoch;
+    ga.le_begin = 0; ga.le_end = 1; ga.mode = 0;
+    GemmArgs g1 = ga;
+    g1.A = s.A; g1.B = s.W1; g1.bias = s.b1; g1.y1 = g.y1; g1.N = c.I; g1.Kd = c.H;
+    g1.hidden_act = c.hidden_act;
+    GemmArgs g2 = ga;
+    g2.A = g.y1; g2.B = s.W2; g2.bias = s.b2; g2.y1 = s.out; g2.N = c.H; g2.Kd = c.I;
+    g2.hidden_act = 2;  // identity
+    if (g.use_tc) {
+        if constexpr (sizeof(T) == 2) {
+            if (g.use_pair) {
+                const int grid = g.sm_count & ~1;
+                const bool deep = c.S >= 512;
+                const gemm_tc2::FusedArgs fa{};
+                if (c.hidden_act == 0)
+                    launch_tc2<T, 0, false>(deep, grid, 256, st, *map_a, g.map_w1h, g1, fa);
+                else
+                    launch_tc2<T, 1, false>(deep, grid, 256, st, *map_a, g.map_w1h, g1, fa);
+                KLEOS_CUDA(mark());
+                launch_tc2<T, 2, false>(deep, grid, 256, st, g.map_y1, g.map_w2h, g2, fa);
+            } else {
+                if (c.hidden_act == 0)
+                    ffn_gemm_tc<T, 0><<<g.sm_count, 256, gemm_tc::SMEM_BYTES, st>>>(*map_a, g.map_w1, g1);
+                else
+                    ffn_gemm_tc<T, 1><<<g.sm_count, 256, gemm_tc::SMEM_BYTES, st>>>(*map_a, g.map_w1, g1);
+                KLEOS_CUDA(mark());
+                ffn_gemm_tc<T, 2><<<g.sm_count, 256, gemm_tc::SMEM_BYTES, st>>>(g.map_y1, g.map_w2, g2);
+            }
+        }
+    } else {
+        ffn_gemm_simt<T><<<g.sm_count * 2, 256, 0, st>>>(g1);
+        KLEOS_CUDA(mark());
+        ffn_gemm_simt<T><<<g.sm_count * 2, 256, 0, st>>>(g2);
+    }
+    KLEOS_CUDA(mark());
+    KLEOS_CUDA(mark());  // combine: nothing to do
+    KLEOS_CUDA(cudaGetLastError());
+    return KLEOS_OK;
+}
+
 template <typename T>
 int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed, const Staging* stg) {
     const LayerConfig& c = g.cfg;
@@ -299,6 +358,7 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed, const S
         act_map = stg->map_act;
     }
     g.epoch += 1;
+    if (g.dense) return forward_dense<T>(s, stg ? stg->map_act : &g.map_x, st, timed);
     int evi = 0;
     auto mark = [&]() -> cudaError_t { return timed ? cudaEventRecord(g.ev[evi++], st) : cudaSuccess; };
     KLEOS_CUDA(mark());
@@ -555,6 +615,21 @@ void release_all() {
     g = State();
 }
 
+// Sizes reported to the caller.  A single-expert layer is the dense FFN: its packed input has no
+// gate weight and its packed output no probabilities (reference moe/fffn.cuh:47-53), and every
+// rank holds the one expert.
+void fill_info(const LayerConfig& c, int rank, int world, kleos_layer_info* out) {
+    const bool dense = c.E == 1;
+    const int nlx = dense ? 1 : c.E / world;
+    out->rank = rank; out->world = world; out->local_experts = nlx;
+    out->S = c.S; out->H = c.H; out->I = c.I; out->E = c.E; out->K = c.K; out->EC = c.EC;
+    out->pEC = c.pEC; out->PX = c.PX; out->torch_dtype = c.torch_dtype;
+    out->hidden_act = c.hidden_act; out->elem_bytes = c.elem_bytes;
+    out->input_elems = (int64_t)c.S * c.H + (dense ? 0 : (int64_t)c.PX * c.H) + 2LL * nlx * c.I * c.H +
+                       (int64_t)nlx * (c.I + c.H);
+    out->output_elems = (dense ? 0 : (int64_t)c.S * c.PX) + (int64_t)c.S * c.H;
+}
+
 }  // namespace
 }  // namespace kleos
 
@@ -593,16 +668,9 @@ int kleos_config_probe(const char* config_json_path, int world, kleos_layer_info
     LayerConfig c;
     const std::string err = load_config(config_json_path, &c);
     if (!err.empty()) return fail(KLEOS_E_CONFIG, "%s: %s", config_json_path, err.c_str());
-    if (world < 1 || world > kMaxWorld || c.E % world)
+    if (world < 1 || world > kMaxWorld || (c.E != 1 && c.E % world))
         return fail(KLEOS_E_CONFIG, "num_experts %d does not divide over %d ranks", c.E, world);
-    const int nlx = c.E / world;
-    out->rank = 0; out->world = world; out->local_experts = nlx;
-    out->S = c.S; out->H = c.H; out->I = c.I; out->E = c.E; out->K = c.K; out->EC = c.EC;
-    out->pEC = c.pEC; out->PX = c.PX; out->torch_dtype = c.torch_dtype;
-    out->hidden_act = c.hidden_act; out->elem_bytes = c.elem_bytes;
-    out->input_elems = (int64_t)c.S * c.H + (int64_t)c.PX * c.H + 2LL * nlx * c.I * c.H +
-                       (int64_t)nlx * (c.I + c.H);
-    out->output_elems = (int64_t)c.S * c.PX + (int64_t)c.S * c.H;
+    fill_info(c, 0, world, out);
     return KLEOS_OK;
 }
 
@@ -620,12 +688,14 @@ int kleos_initialize(const char* config_json_path, int rank, int world, const vo
     LayerConfig cfg;
     const std::string err = load_config(config_json_path, &cfg);
     if (!err.empty()) return fail(KLEOS_E_CONFIG, "%s: %s", config_json_path, err.c_str());
-    if (cfg.E % world) return fail(KLEOS_E_CONFIG, "num_experts %d does not divide over %d ranks", cfg.E, world);
+    const bool dense = cfg.E == 1;
+    if (!dense && cfg.E % world)
+        return fail(KLEOS_E_CONFIG, "num_experts %d does not divide over %d ranks", cfg.E, world);
     if (cfg.torch_dtype == 1)
         return fail(KLEOS_E_UNSUPPORTED, "torch_dtype 1 (tf32) is not implemented: use 0 (float), 2 (bf16) or 3 (fp16)");
     if (cfg.K > kMaxTopK) return fail(KLEOS_E_UNSUPPORTED, "expert_top_k > %d", kMaxTopK);
     if (cfg.E > 256) return fail(KLEOS_E_UNSUPPORTED, "num_experts > 256");
-    if (world > 1 && !nccl_id) return fail(KLEOS_E_ARG, "world > 1 needs an NCCL unique id");
+    if (world > 1 && !nccl_id && !dense) return fail(KLEOS_E_ARG, "world > 1 needs an NCCL unique id");
 
     int ndev = 0;
     if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0)
@@ -641,7 +711,8 @@ int kleos_initialize(const char* config_json_path, int rank, int world, const vo
     g.cfg = cfg;
     g.rank = rank;
     g.world = world;
-    g.nLx = cfg.E / world;
+    g.dense = dense;
+    g.nLx = dense ? 1 : cfg.E / world;
     g.epoch = 0;
     if (const char* w = std::getenv("KLEOS_WAIT_MS")) {
         // device wait budget in milliseconds (converted with the SM clock rate)
@@ -705,7 +776,17 @@ int kleos_initialize(const char* config_json_path, int rank, int world, const vo
 
     for (int r = 0; r < kMaxWorld; ++r) g.peers.arena[r] = nullptr;
     g.peers.arena[rank] = g.arena;
-    if (world > 1) {
+    if (dense) {
+        // fixed work list of the dense layer: one panel per 128 tokens, one "expert"
+        const int np = (cfg.S + kTileM - 1) / kTileM;
+        std::vector<PanelEntry> panels(np);
+        for (int i = 0; i < np; ++i) panels[i] = PanelEntry{i * kTileM, std::min(kTileM, cfg.S - i * kTileM), 0, rank};
+        const int le_start[2] = {0, np};
+        KLEOS_CUDA(cudaMemcpy(g.panels, panels.data(), sizeof(PanelEntry) * np, cudaMemcpyHostToDevice));
+        KLEOS_CUDA(cudaMemcpy(g.le_start, le_start, sizeof(le_start), cudaMemcpyHostToDevice));
+    }
+    // ranks of a dense layer never exchange anything, so they are not connected
+    if (world > 1 && !dense) {
         if ((rc = load_nccl())) return rc;
         ncclUniqueId id;
         std::memcpy(&id, nccl_id, sizeof(id));
@@ -804,7 +885,7 @@ int kleos_forward_host(const void* host_activations, void* iP, void* oP, void* h
     KLEOS_CUDA(cudaMemcpyAsync(iP, host_activations, act_bytes, cudaMemcpyHostToDevice, st));
     int rc = forward_any(iP, oP, st, false);
     if (rc) return rc;
-    const char* out = static_cast<const char*>(oP) + (size_t)c.S * c.PX * c.elem_bytes;
+    const char* out = static_cast<const char*>(oP) + (g.dense ? 0 : (size_t)c.S * c.PX * c.elem_bytes);
     KLEOS_CUDA(cudaMemcpyAsync(host_output, out, act_bytes, cudaMemcpyDeviceToHost, st));
     KLEOS_CUDA(cudaStreamSynchronize(st));
     return KLEOS_OK;
@@ -856,14 +937,7 @@ int kleos_local_experts(void) { return g.initialised ? g.nLx : KLEOS_E_STATE; }
 int kleos_get_info(kleos_layer_info* out) {
     if (!g.initialised) return fail(KLEOS_E_STATE, "not initialised");
     if (!out) return fail(KLEOS_E_ARG, "null info");
-    const LayerConfig& c = g.cfg;
-    out->rank = g.rank; out->world = g.world; out->local_experts = g.nLx;
-    out->S = c.S; out->H = c.H; out->I = c.I; out->E = c.E; out->K = c.K; out->EC = c.EC;
-    out->pEC = c.pEC; out->PX = c.PX; out->torch_dtype = c.torch_dtype;
-    out->hidden_act = c.hidden_act; out->elem_bytes = c.elem_bytes;
-    out->input_elems = (int64_t)c.S * c.H + (int64_t)c.PX * c.H + 2LL * g.nLx * c.I * c.H +
-                       (int64_t)g.nLx * (c.I + c.H);
-    out->output_elems = (int64_t)c.S * c.PX + (int64_t)c.S * c.H;
+    fill_info(g.cfg, g.rank, g.world, out);
     return KLEOS_OK;
 }
 
@@ -886,6 +960,7 @@ int kleos_clear_status(void) {
 
 int kleos_debug_routing(int32_t* topk, int32_t* slots, uint32_t* counts, float* mcw) {
     if (!g.initialised) return fail(KLEOS_E_STATE, "not initialised");
+    if (g.dense) return fail(KLEOS_E_UNSUPPORTED, "a single-expert layer does no routing");
     const LayerConfig& c = g.cfg;
     KLEOS_CUDA(cudaStreamSynchronize(cudaStreamPerThread));
     const size_t sk = (size_t)c.S * c.K;

@@ -38,12 +38,15 @@ struct RowDecision {
     float max, inv_den, kth, margin;
 };
 
-__device__ __forceinline__ RowDecision decide_row(const float* l, int E, int K, int* topk_out,
-                                                  float* mcw_out) {
-    float val[kMaxTopK + 1];
-    int idx[kMaxTopK + 1];
+// KT is a compile-time bound on K: the insertion chain is KT+1 registers long, so a top-2
+// layer does not pay for the eight-deep chain of the largest supported k.
+template <int KT>
+__device__ __forceinline__ RowDecision decide_row_k(const float* l, int E, int K, int* topk_out,
+                                                    float* mcw_out) {
+    float val[KT + 1];
+    int idx[KT + 1];
 #pragma unroll
-    for (int j = 0; j <= kMaxTopK; ++j) {
+    for (int j = 0; j <= KT; ++j) {
         val[j] = -INFINITY;
         idx[j] = 0;
     }
@@ -51,7 +54,7 @@ __device__ __forceinline__ RowDecision decide_row(const float* l, int E, int K, 
         float v = l[e];
         int id = e;
 #pragma unroll
-        for (int j = 0; j <= kMaxTopK; ++j) {
+        for (int j = 0; j <= KT; ++j) {
             if (j <= K && v > val[j]) {
                 const float tv = val[j];
                 const int ti = idx[j];
@@ -68,7 +71,7 @@ __device__ __forceinline__ RowDecision decide_row(const float* l, int E, int K, 
     const float inv = 1.f / d;
     float w = 0.f, kth = 0.f, next = -INFINITY;
 #pragma unroll
-    for (int j = 0; j <= kMaxTopK; ++j) {
+    for (int j = 0; j <= KT; ++j) {
         if (j < K) {
             topk_out[j] = idx[j];
             w += __expf(val[j] - m) * inv;
@@ -84,6 +87,14 @@ __device__ __forceinline__ RowDecision decide_row(const float* l, int E, int K, 
     r.kth = kth;
     r.margin = (K < E) ? kth - next : INFINITY;
     return r;
+}
+
+__device__ __forceinline__ RowDecision decide_row(const float* l, int E, int K, int* topk_out,
+                                                  float* mcw_out) {
+    if (K <= 1) return decide_row_k<1>(l, E, K, topk_out, mcw_out);
+    if (K <= 2) return decide_row_k<2>(l, E, K, topk_out, mcw_out);
+    if (K <= 4) return decide_row_k<4>(l, E, K, topk_out, mcw_out);
+    return decide_row_k<kMaxTopK>(l, E, K, topk_out, mcw_out);
 }
 
 // One block = 64 tokens x PXT experts, 256 threads, each thread a 4 x (PXT/16) register tile.
@@ -329,7 +340,6 @@ __global__ void __launch_bounds__(256) tile_hist_kernel(SlotArgs a) {
 
 __global__ void __launch_bounds__(256) slot_kernel(SlotArgs a) {
     __shared__ int base[256];
-    __shared__ int sel_s[kSlotTile * kMaxTopK];
     const int tid = threadIdx.x, b = blockIdx.x;
     const int tok0 = b * kSlotTile;
     const bool last = b == (int)gridDim.x - 1;
@@ -364,23 +374,39 @@ __global__ void __launch_bounds__(256) slot_kernel(SlotArgs a) {
                            make_flag(a.epoch, (unsigned)min(total, a.EC)));
         }
     }
+    // Rank of every (token, choice) entry among the earlier entries of the tile that chose the
+    // same expert.  Entries are taken in order, 256 at a time: inside a warp the rank comes from
+    // a match mask, across the eight warps from a per-warp count table, and `base` carries the
+    // running total into the next group of 256.
+    __shared__ int wcount[8][256];
+    for (int i = tid; i < 8 * 256; i += blockDim.x) (&wcount[0][0])[i] = 0;
     const int n_own = min(kSlotTile, a.S - tok0) * a.K;
-    for (int i = tid; i < kSlotTile * a.K; i += blockDim.x)
-        sel_s[i] = i < n_own ? a.topk[(size_t)tok0 * a.K + i] : -1;
+    const int warp = tid >> 5, lane = tid & 31;
     __syncthreads();
-    if (tid < kSlotTile && tok0 + tid < a.S) {
-        for (int j = 0; j < a.K; ++j) {
-            const int e = sel_s[tid * a.K + j];
-            int rank = 0;
-            for (int i = 0; i < tid * a.K; ++i) rank += (sel_s[i] == e);
-            const int pos = base[e] + rank;
+    for (int i0 = 0; i0 < n_own; i0 += 256) {
+        const int i = i0 + tid;
+        const int e = i < n_own ? a.topk[(size_t)tok0 * a.K + i] : -1;
+        const unsigned peers = __match_any_sync(0xffffffffu, e);
+        const int before = __popc(peers & ((1u << lane) - 1u));
+        const bool leader = e >= 0 && before == 0;
+        if (leader) wcount[warp][e] = __popc(peers);
+        __syncthreads();
+        if (e >= 0) {
+            int pos = base[e] + before;
+            for (int w = 0; w < warp; ++w) pos += wcount[w][e];
             if (pos < a.EC) {
-                a.slots[(size_t)(tok0 + tid) * a.K + j] = pos;
-                a.cell_tokens[(size_t)e * a.pEC + pos] = tok0 + tid;
+                a.slots[(size_t)tok0 * a.K + i] = pos;
+                a.cell_tokens[(size_t)e * a.pEC + pos] = tok0 + i / a.K;
             } else {
-                a.slots[(size_t)(tok0 + tid) * a.K + j] = kDropped;
+                a.slots[(size_t)tok0 * a.K + i] = kDropped;
             }
         }
+        __syncthreads();
+        if (leader) {
+            atomicAdd(&base[e], wcount[warp][e]);
+            wcount[warp][e] = 0;
+        }
+        __syncthreads();
     }
 }
 

@@ -15,7 +15,7 @@ import numpy as np
 
 from .config import KleosConfig
 
-_STREAM_ACT, _STREAM_GATE, _STREAM_W1, _STREAM_W2, _STREAM_PERM = 1, 2, 3, 4, 5
+_STREAM_ACT, _STREAM_GATE, _STREAM_W1, _STREAM_W2, _STREAM_PERM, _STREAM_B1, _STREAM_B2 = 1, 2, 3, 4, 5, 6, 7
 
 
 def _normal(seed: int, stream: int, index: int, n: int) -> np.ndarray:
@@ -67,6 +67,14 @@ def expert_weights(cfg: KleosConfig, expert: int, seed: int = 0):
     return (w1 * np.float32(1.0 / np.sqrt(cfg.H)), w2 * np.float32(1.0 / np.sqrt(cfg.I)))
 
 
+def expert_biases(cfg: KleosConfig, expert: int, scale: float, seed: int = 0):
+    """(b1[i], b2[h]) of one global expert, N(0, scale).  The benchmark layers use zero biases;
+    the parity tests also run with scale > 0 so the bias path of both GEMM epilogues is checked."""
+    b1 = _normal(seed, _STREAM_B1, expert, cfg.I) * np.float32(scale)
+    b2 = _normal(seed, _STREAM_B2, expert, cfg.H) * np.float32(scale)
+    return b1, b2
+
+
 def zipf_gate_bias(cfg: KleosConfig, s: float = 1.2, seed: int = 0) -> np.ndarray:
     """Per-expert logit bias that makes expert popularity follow Zipf(s) over a seeded
     random permutation of the experts: b_e = log(pmf(rank_pi(e)))."""
@@ -79,19 +87,27 @@ def zipf_gate_bias(cfg: KleosConfig, s: float = 1.2, seed: int = 0) -> np.ndarra
     return np.log(pmf).astype(np.float32)
 
 
-def packed_input(cfg: KleosConfig, rank: int, world: int, seed: int = 0) -> np.ndarray:
+def packed_input(cfg: KleosConfig, rank: int, world: int, seed: int = 0,
+                 bias_scale: float = 0.0) -> np.ndarray:
     """fp32 packed input of one rank, already rounded to the layer's element type
-    (layout: moe.cuh:92-98).  Rows E..PX-1 of the gate weight are zero."""
+    (layout: moe.cuh:92-98).  Rows E..PX-1 of the gate weight are zero.  A single-expert
+    (dense) layer has no gate weight section (moe/fffn.cuh:47-53)."""
     off = cfg.input_offsets(world)
     buf = np.zeros(off["end"], dtype=np.float32)
     buf[off["A"]:off["Wg"]] = activations(cfg, rank, seed).ravel()
-    buf[off["Wg"]:off["Wg"] + cfg.E * cfg.H] = gate_weight(cfg, seed).ravel()
+    if not cfg.dense:
+        buf[off["Wg"]:off["Wg"] + cfg.E * cfg.H] = gate_weight(cfg, seed).ravel()
     nlx = cfg.local_experts(world)
     ih = cfg.I * cfg.H
     for le in range(nlx):
-        w1, w2 = expert_weights(cfg, rank * nlx + le, seed)
+        e = 0 if cfg.dense else rank * nlx + le
+        w1, w2 = expert_weights(cfg, e, seed)
         buf[off["W1"] + le * ih: off["W1"] + (le + 1) * ih] = w1.ravel()
         buf[off["W2"] + le * ih: off["W2"] + (le + 1) * ih] = w2.ravel()
+        if bias_scale:
+            b1, b2 = expert_biases(cfg, e, bias_scale, seed)
+            buf[off["b1"] + le * cfg.I: off["b1"] + (le + 1) * cfg.I] = b1
+            buf[off["b2"] + le * cfg.H: off["b2"] + (le + 1) * cfg.H] = b2
     return round_to_dtype(buf, cfg.torch_dtype)
 
 
@@ -122,7 +138,7 @@ def split_packed(cfg: KleosConfig, buf: np.ndarray, world: int) -> dict:
     nlx = cfg.local_experts(world)
     return dict(
         A=buf[off["A"]:off["Wg"]].reshape(cfg.S, cfg.H),
-        Wg=buf[off["Wg"]:off["W1"]].reshape(cfg.PX, cfg.H),
+        Wg=buf[off["Wg"]:off["W1"]].reshape(-1, cfg.H),
         W1=buf[off["W1"]:off["W2"]].reshape(nlx, cfg.I, cfg.H),
         W2=buf[off["W2"]:off["b1"]].reshape(nlx, cfg.H, cfg.I),
         b1=buf[off["b1"]:off["b2"]].reshape(nlx, cfg.I),

@@ -45,6 +45,16 @@ def workload(name: str):
         return (KleosConfig(sequence_len=8192, hidden_size=2048, intermediate_size=2048,
                             num_experts=8, torch_dtype=2),
                 "C3r8: S=8192 tokens, H=I=2048, E=8, top-2, CF=1, bf16 (per-rank shape of C3 at 8 ranks)")
+    if name == "F3":
+        # single-expert layer = the plain FFN (the reference's dense kernel); 16384 tokens so
+        # that activations, intermediate and output (208 MB with the weights) exceed L2
+        return (KleosConfig(sequence_len=16384, hidden_size=2048, intermediate_size=2048,
+                            num_experts=1, expert_top_k=1, torch_dtype=2),
+                "F3: dense FFN (num_experts=1), S=16384 tokens/rank, H=I=2048, bf16")
+    if name == "F3q":
+        return (KleosConfig(sequence_len=4096, hidden_size=2048, intermediate_size=2048,
+                            num_experts=1, expert_top_k=1, torch_dtype=2),
+                "F3q: dense FFN (num_experts=1), S=4096 tokens/rank, H=I=2048, bf16 (profiling size)")
     cfg, _ = baseline_config(name)
     return cfg, (f"{name}: S={cfg.S} tokens/rank, H={cfg.H}, I={cfg.I}, E={cfg.E}, "
                  f"top-{cfg.K}, CF={cfg.capacity_factor}, {cfg.dtype_name}")
@@ -130,11 +140,12 @@ def synth_on_device(cfg, rank, world, device):
     gen.manual_seed(1000 + rank)
     buf[off["A"]:off["Wg"]] = torch.randn(cfg.S * cfg.H, generator=gen, device=device).to(tdt)
     gen.manual_seed(7)
-    buf[off["Wg"]:off["Wg"] + cfg.E * cfg.H] = (
-        torch.randn(cfg.E * cfg.H, generator=gen, device=device) / cfg.H ** 0.5).to(tdt)
+    if not cfg.dense:
+        buf[off["Wg"]:off["Wg"] + cfg.E * cfg.H] = (
+            torch.randn(cfg.E * cfg.H, generator=gen, device=device) / cfg.H ** 0.5).to(tdt)
     ih = cfg.I * cfg.H
     for le in range(nlx):
-        e = rank * nlx + le
+        e = 0 if cfg.dense else rank * nlx + le
         gen.manual_seed(100000 + e)
         buf[off["W1"] + le * ih: off["W1"] + (le + 1) * ih] = (
             torch.randn(ih, generator=gen, device=device) / cfg.H ** 0.5).to(tdt)
@@ -152,7 +163,10 @@ def cpu_sample_tokens_per_s(cfg, views, sample_tokens: int, repeats: int = 1):
     best = None
     for _ in range(repeats):
         t0 = time.perf_counter()
-        c_oracle.moe_forward_rank(cfg, 1, 0, views, tokens=rows, accum64=False)
+        if cfg.dense:
+            c_oracle.dense_ffn(cfg, views[0], tokens=rows, accum64=False)
+        else:
+            c_oracle.moe_forward_rank(cfg, 1, 0, views, tokens=rows, accum64=False)
         dt = time.perf_counter() - t0
         best = dt if best is None else min(best, dt)
     return sample_tokens / best, best, c_oracle.num_threads()
@@ -300,7 +314,8 @@ def run_cuda(args):
     # ---------------------------------------------------------------- per-phase times, roofline
     kleos.forward_host_bench(iP, oP, skip=2, trials=max(4, min(args.steps, 16)))
     phases = kleos.phase_times()
-    routing = kleos.debug_routing(info)
+    # a single-expert layer has no routing: every token of every rank goes through the one expert
+    routing = dict(counts=np.array([cfg.S], dtype=np.uint32)) if cfg.dense else kleos.debug_routing(info)
     routed_here = int(np.minimum(routing["counts"], info.EC).sum())  # pairs this rank dispatched
     # pairs this rank's experts processed: under even sharding and random routing this equals
     # the pairs it dispatched to within sampling noise; the all-rank sum is identical
@@ -313,6 +328,8 @@ def run_cuda(args):
     # experts of this rank that received at least one row (the weights of the others are never read)
     lo = rank * info.local_experts
     active_experts = int((routed_vec[lo:lo + info.local_experts] > 0).sum().item())
+    if cfg.dense:
+        pairs_per_rank, active_experts = float(cfg.S), 1
     peaks = load_peaks()
     # dominant kernel: one FFN GEMM launch (GEMM1 and GEMM2 do the same work when H == I).
     # Algorithmic work per launch: 2*R*H*I FLOP; bytes = the weights of this rank's experts that
@@ -341,8 +358,8 @@ def run_cuda(args):
                 peak_source=peaks["source"], tensor_tflops=tflops, hbm_gbs=gbs,
                 algorithmic_bytes=gemm_bytes, algorithmic_flops=gemm_flops,
                 launch_ms=gemm_ms)
-    total_flops = 2.0 * cfg.S * cfg.H * cfg.E + 4.0 * cfg.H * cfg.I * pairs_per_rank
-    remote_pairs = pairs_per_rank * (world - 1) / world
+    total_flops = (0.0 if cfg.dense else 2.0 * cfg.S * cfg.H * cfg.E) + 4.0 * cfg.H * cfg.I * pairs_per_rank
+    remote_pairs = 0.0 if cfg.dense else pairs_per_rank * (world - 1) / world
     link_bytes = 2.0 * remote_pairs * cfg.H * eb
     t_roof_ms = max(total_flops / (peaks["tflops"] * 1e12), link_bytes / 770e9) * 1e3
     ms_per_step = ms_total / args.steps
@@ -355,11 +372,12 @@ def run_cuda(args):
             higher_is_better=True, scaling="weak", vs_baseline=None, dtype=cfg.dtype_name,
             data="synthetic",
             config=dict(workload=workload_desc,
-                        experts_per_rank=info.local_experts, parallelism=f"ep{world}",
+                        experts_per_rank=info.local_experts,
+                        parallelism=f"replicas{world}" if cfg.dense else f"ep{world}",
                         l2="working set per step (weights + cells + activations) exceeds L2"),
             e2e=dict(value=tokens * args.steps / e2e_s, unit="tokens/s",
                      h2d_bytes_per_step=act_elems * eb, d2h_bytes_per_step=act_elems * eb),
-            gpu_launches=KERNELS_PER_FORWARD * args.steps,
+            gpu_launches=(2 if cfg.dense else KERNELS_PER_FORWARD) * args.steps,
             clocks=clocks,
             roofline=roof,
             layer_roofline=dict(t_roof_ms=t_roof_ms, frac=t_roof_ms / ms_per_step,
@@ -373,8 +391,10 @@ def run_cuda(args):
             v, dt, threads = cpu_sample_tokens_per_s(cfg, views, sample)
             line["cpu_baseline"] = dict(
                 value=v, unit="tokens/s", cores=threads, kind="port",
-                sample=f"first {sample} of {cfg.S} tokens of rank 0 through all {cfg.E} experts "
-                       f"(routing over all {cfg.S} tokens), fp32 accumulation, {dt:.1f} s")
+                sample=(f"first {sample} of {cfg.S} tokens through the FFN, fp32 accumulation, {dt:.1f} s"
+                        if cfg.dense else
+                        f"first {sample} of {cfg.S} tokens of rank 0 through all {cfg.E} experts "
+                        f"(routing over all {cfg.S} tokens), fp32 accumulation, {dt:.1f} s"))
         print(json.dumps(line), flush=True)
     kleos.finalize()
     if world > 1:
@@ -389,7 +409,7 @@ def main():
     ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
     ap.add_argument("--workload", default="C3",
                     help="C3 (default), C4 (Zipf-imbalanced), C5 (large FFN), C1 / C2 (float), "
-                         "C3q / C3r8 (profiling sizes)")
+                         "C3q / C3r8 (profiling sizes), F3 / F3q (dense FFN, num_experts=1)")
     ap.add_argument("--cpu-sample", type=int, default=0,
                     help="tokens in the CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")

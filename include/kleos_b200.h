@@ -86,6 +86,11 @@ int kleos_set_gate_bias(const float* host_bias, int n);
  * packed buffers of moe.cuh:92-98:
  *   iP = [A S*H][Wg PX*H][W1 nLx*I*H][W2 nLx*H*I][b1 nLx*I][b2 nLx*H]
  *   oP = [gate probabilities S*PX][layer output S*H]
+ * With num_experts == 1 the layer is the plain FFN over the rank's own tokens, as in the
+ * reference (moe/moe.cuh:197-204 launches moe/fffn.cuh:31-167): no gate and no exchange, every
+ * rank holds the one expert (nLx = 1, any world size, no NCCL id needed), and the packed
+ * buffers lose their gate sections:
+ *   iP = [A S*H][W1 I*H][W2 H*I][b1 I][b2 H]      oP = [layer output S*H]
  * Replaces kleos::moe::forwardHost(iP, oP) (moe/moe.cuh:186-205). */
 int kleos_forward(const void* iP, void* oP, void* stream);
 

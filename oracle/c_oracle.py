@@ -57,6 +57,21 @@ def use_all_cores() -> int:
     return num_threads()
 
 
+def dense_ffn(cfg, inp, tokens=None, accum64=True):
+    """Single-expert layer (plain FFN) for one rank's tokens; twin of moe_oracle.dense_ffn."""
+    L = lib()
+    c = _cfg(cfg, 1)
+    a = inp["A"] if tokens is None else inp["A"][np.asarray(tokens)]
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    arrs = [np.ascontiguousarray(inp[k][0], dtype=np.float32) for k in ("W1", "W2", "b1", "b2")]
+    out = np.zeros((a.shape[0], cfg.H), dtype=np.float32)
+    rc = L.oracle_expert_ffn(ctypes.byref(c), ctypes.c_int(a.shape[0]), _fp(a), *[_fp(x) for x in arrs],
+                             _fp(out), ctypes.c_int(1 if accum64 else 0))
+    if rc:
+        raise RuntimeError(f"oracle_expert_ffn failed: {rc}")
+    return out
+
+
 def moe_forward_rank(cfg, world, rank, inputs, gate_bias=None, tokens=None, accum64=True):
     """Layer output for the tokens of one source rank; same result keys as the NumPy twin."""
     L = lib()

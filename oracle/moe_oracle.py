@@ -22,6 +22,7 @@ Reference lines followed (paths inside the reference project):
                                   activations types.cuh:143-159
   * combine: out[t] += Element(y2 / mCw) * Element(prob[t,e])   processor.cuh:110-168
   * expert -> rank map (contiguous, even)   bootstrap.cuh:36-52
+  * single-expert (dense) layer   moe/moe.cuh:174-177, moe/fffn.cuh:31-167
 
 Deliberate choices where the reference leaves the outcome open:
   * slot order inside an expert is ascending token index (the reference orders by
@@ -96,6 +97,14 @@ def expert_ffn(cfg, x: np.ndarray, w1, w2, b1, b2) -> np.ndarray:
     y1 = round_elem(z.astype(np.float32), cfg.torch_dtype)
     y2 = y1.astype(np.float64) @ w2.astype(np.float64).T + b2.astype(np.float64)[None, :]
     return round_elem(y2.astype(np.float32), cfg.torch_dtype)
+
+
+def dense_ffn(cfg, inp: dict, token_subset=None) -> np.ndarray:
+    """Single-expert layer: the plain FFN over one rank's tokens, no gate and no scaling
+    (the reference runs its dense kernel when E == 1, moe/moe.cuh:174-177; arithmetic
+    moe/fffn.cuh:31-167: act(A W1^T + b1) rounded to the element type, then W2^T + b2 rounded)."""
+    a = inp["A"] if token_subset is None else inp["A"][np.asarray(token_subset)]
+    return expert_ffn(cfg, a, inp["W1"][0], inp["W2"][0], inp["b1"][0], inp["b2"][0])
 
 
 def moe_forward(cfg, world: int, inputs: list, gate_bias=None, token_subset=None) -> list:

@@ -11,8 +11,8 @@ TOL = {0: 1e-5, 2: 2e-2, 3: 4e-3}  # max_abs(y - y_ref) / max_abs(y_ref): fp32, 
 PROB_TOL = {0: 2e-6, 2: 4e-3, 3: 5e-4}  # absolute, gate probabilities (one element ulp at p ~ 0.5)
 
 
-def make_inputs(cfg: KleosConfig, world: int, seed: int = 0):
-    packed = [synth.packed_input(cfg, r, world, seed) for r in range(world)]
+def make_inputs(cfg: KleosConfig, world: int, seed: int = 0, bias_scale: float = 0.0):
+    packed = [synth.packed_input(cfg, r, world, seed, bias_scale) for r in range(world)]
     views = [synth.split_packed(cfg, p, world) for p in packed]
     return packed, views
 
@@ -40,10 +40,14 @@ def run_layer_single_gpu(cfg: KleosConfig, packed: np.ndarray, gate_bias=None, f
                 kleos.forward_host(iP, oP)
         st = kleos.last_status()
         assert st.code == 0, f"device status code={st.code} where={st.where} detail={st.detail}"
-        routing = kleos.debug_routing(info)
         o = oP.cpu().numpy().view(raw.dtype)
-        probs = synth.decode(o[: cfg.S * cfg.PX], cfg.torch_dtype).reshape(cfg.S, cfg.PX)
-        out = synth.decode(o[cfg.S * cfg.PX:], cfg.torch_dtype).reshape(cfg.S, cfg.H)
+        if cfg.dense:  # no gate: the packed output is the S x H result alone
+            routing, probs = None, None
+            out = synth.decode(o, cfg.torch_dtype).reshape(cfg.S, cfg.H)
+        else:
+            routing = kleos.debug_routing(info)
+            probs = synth.decode(o[: cfg.S * cfg.PX], cfg.torch_dtype).reshape(cfg.S, cfg.PX)
+            out = synth.decode(o[cfg.S * cfg.PX:], cfg.torch_dtype).reshape(cfg.S, cfg.H)
         if via_host:
             out_h = synth.decode(host_out, cfg.torch_dtype).reshape(cfg.S, cfg.H)
             assert np.array_equal(out_h, out)

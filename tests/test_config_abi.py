@@ -28,6 +28,21 @@ def test_cpp_and_python_derive_the_same_sizes(tmp_path, name, world):
     assert info.elem_bytes == cfg.elem_bytes
 
 
+@pytest.mark.parametrize("world", [1, 4])
+def test_single_expert_layer_is_dense(tmp_path, world):
+    """E == 1 is the plain FFN: no gate weight in the packed input, no probabilities in the
+    packed output, one local expert on every rank (reference moe/fffn.cuh:47-53)."""
+    cfg = KleosConfig(sequence_len=256, hidden_size=128, intermediate_size=192, num_experts=1,
+                      expert_top_k=1, torch_dtype=2)
+    cfg.validate(world)
+    p = tmp_path / "kleos_config.json"
+    cfg.to_json(str(p))
+    info = kleos.config_probe(str(p), world)
+    assert info.local_experts == 1 == cfg.local_experts(world)
+    assert info.input_elems == cfg.input_elems(world) == 256 * 128 + 2 * 192 * 128 + 192 + 128
+    assert info.output_elems == cfg.output_elems() == 256 * 128
+
+
 def test_benchmark_layer_table_values():
     """EC / pEC / PX of the five benchmark layers."""
     expect = {"C1": (64, 128, 64), "C2": (512, 512, 64), "C3": (256, 256, 64),

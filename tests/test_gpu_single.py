@@ -57,6 +57,40 @@ def test_shapes_and_modes(dtype, kw):
     hz.check_against_oracle(cfg, ref, probs, out, routing)
 
 
+@pytest.mark.parametrize("dtype,kw", [
+    (0, dict()), (2, dict()), (3, dict(hidden_act=1)),
+    (2, dict(num_experts=128, sequence_len=512, hidden_size=256, intermediate_size=320,
+             hidden_act=1)),
+])
+def test_nonzero_ffn_biases(dtype, kw):
+    """b1 and b2 drawn from N(0, 0.5): the bias path of both GEMM epilogues (the benchmark
+    layers themselves use zero biases)."""
+    cfg = _small(dtype, **kw)
+    packed, views = hz.make_inputs(cfg, 1, bias_scale=0.5)
+    assert np.abs(views[0]["b1"]).max() > 0.5 and np.abs(views[0]["b2"]).max() > 0.5
+    ref = moe_oracle.moe_forward(cfg, 1, views)[0]
+    probs, out, routing = hz.run_layer_single_gpu(cfg, packed[0])
+    hz.check_against_oracle(cfg, ref, probs, out, routing)
+
+
+@pytest.mark.parametrize("dtype,kw,via_host", [
+    (0, dict(sequence_len=256, hidden_size=192, intermediate_size=320), False),
+    (2, dict(sequence_len=384, hidden_size=256, intermediate_size=320), False),   # odd panel count, N tail
+    (2, dict(sequence_len=1024, hidden_size=512, intermediate_size=1024, hidden_act=1), True),
+    (3, dict(sequence_len=256, hidden_size=128, intermediate_size=256, hidden_act=1), False),
+])
+def test_single_expert_layer_is_the_dense_ffn(dtype, kw, via_host):
+    """num_experts == 1: packed buffers without gate weight / probabilities, output = FFN(A)
+    (reference moe/moe.cuh:174-177, moe/fffn.cuh:31-167)."""
+    cfg = _small(dtype, num_experts=1, expert_top_k=1, **kw)
+    packed, views = hz.make_inputs(cfg, 1, bias_scale=0.5)
+    ref = c_oracle.dense_ffn(cfg, views[0])
+    _, out, _ = hz.run_layer_single_gpu(cfg, packed[0], forwards=3 if via_host else 1,
+                                        via_host=via_host)
+    err = np.abs(out - ref).max() / np.abs(ref).max()
+    assert err <= hz.TOL[dtype], f"dense layer error {err}"
+
+
 def test_zipf_bias_hot_experts_and_drops():
     """Skewed routing: hot experts overflow their capacity, cold experts receive nothing."""
     cfg = _small(2, num_experts=32, sequence_len=1024, hidden_size=256, intermediate_size=256,
@@ -93,13 +127,13 @@ def test_against_committed_golden_fixtures(name):
     hz.check_against_oracle(cfg, ref, probs, out, routing)
 
 
-@pytest.mark.parametrize("dtype", [2, 0])
-def test_pipelined_host_path_matches_synchronous_path(dtype):
+@pytest.mark.parametrize("dtype,experts", [(2, 8), (0, 8), (2, 1)])
+def test_pipelined_host_path_matches_synchronous_path(dtype, experts):
     """Three queued end-to-end steps with alternating inputs and separate host outputs: each
     must equal what the synchronous host-buffer call returns for the same input."""
     import torch
     from aristos_b200 import kleos
-    cfg = _small(dtype)
+    cfg = _small(dtype, num_experts=experts, expert_top_k=min(2, experts))
     eb = cfg.elem_bytes
     raws = [synth.encode(synth.packed_input(cfg, 0, 1, seed=s), dtype) for s in (0, 5)]
     info = kleos.initialize(cfg, 0, 1)

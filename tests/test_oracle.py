@@ -88,3 +88,22 @@ def test_capacity_formula_and_drops():
     kept = (res["slots"] >= 0).sum()
     assert kept == res["routed"].sum()
     assert res["slots"].max() < cfg.EC
+
+
+@pytest.mark.parametrize("dtype", [0, 2, 3])
+def test_dense_layer_twins_agree_and_match_the_general_path(dtype):
+    """E == 1: the dense FFN of both twins is the same, and it equals what the routed path gives
+    for one expert with top-1 (every token kept, plain copy in the combine)."""
+    cfg = KleosConfig(sequence_len=128, hidden_size=64, intermediate_size=192, num_experts=1,
+                      expert_top_k=1, torch_dtype=dtype, hidden_act=1)
+    packed = synth.packed_input(cfg, 0, 1, seed=3, bias_scale=0.5)
+    v = synth.split_packed(cfg, packed, 1)
+    assert np.abs(v["b1"]).max() > 0 and np.abs(v["b2"]).max() > 0
+    a = moe_oracle.dense_ffn(cfg, v)
+    b = c_oracle.dense_ffn(cfg, v)
+    assert np.abs(a - b).max() <= 1e-6 * np.abs(a).max()
+    sub = moe_oracle.dense_ffn(cfg, v, token_subset=[5, 77])
+    assert np.array_equal(sub, a[[5, 77]])
+    routed = dict(v, Wg=np.zeros((cfg.PX, cfg.H), dtype=np.float32))
+    full = moe_oracle.moe_forward(cfg, 1, [routed])[0]
+    assert np.array_equal(full["out"], a)
