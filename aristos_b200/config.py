@@ -24,7 +24,7 @@ BLOCK_N = 64   # the gate pads the expert dimension to a multiple of this (types
 
 DTYPE_NAMES = {0: "fp32", 1: "tf32", 2: "bf16", 3: "fp16"}
 DTYPE_BYTES = {0: 4, 1: 4, 2: 2, 3: 2}
-SUPPORTED_DTYPES = (0, 2, 3)
+SUPPORTED_DTYPES = (0, 1, 2, 3)
 
 REQUIRED_KEYS = (
     "capacity_factor", "drop_tokens", "expert_top_k", "is_training", "hidden_act",

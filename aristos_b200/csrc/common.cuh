@@ -5,6 +5,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <string.h>
 
 #include "../../include/kleos_b200.h"
 
@@ -51,6 +52,33 @@ template <> struct Elem<__half> {
     static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
     static __device__ __forceinline__ __half from_f(float v) { return __float2half_rn(v); }
     static __device__ __forceinline__ float round(float v) { return __half2float(__float2half_rn(v)); }
+};
+
+// TF32 element (torch_dtype 1): an fp32 word whose low 13 mantissa bits are zero, the storage the
+// reference uses for cute::tfloat32_t (types.cuh:128-131).  Rounding is to nearest, ties to even.
+struct tf32_t {
+    float v;
+};
+__host__ __device__ __forceinline__ float round_tf32(float x) {
+#ifdef __CUDA_ARCH__
+    uint32_t u = __float_as_uint(x);
+#else
+    uint32_t u;
+    memcpy(&u, &x, 4);
+#endif
+    if ((u & 0x7f800000u) != 0x7f800000u) u = (u + 0xfffu + ((u >> 13) & 1u)) & 0xffffe000u;
+#ifdef __CUDA_ARCH__
+    return __uint_as_float(u);
+#else
+    float r;
+    memcpy(&r, &u, 4);
+    return r;
+#endif
+}
+template <> struct Elem<tf32_t> {
+    static __device__ __forceinline__ float to_f(tf32_t v) { return v.v; }
+    static __device__ __forceinline__ tf32_t from_f(float v) { return tf32_t{round_tf32(v)}; }
+    static __device__ __forceinline__ float round(float v) { return round_tf32(v); }
 };
 
 // Packed pairs of a 16-bit element type: conversions and single-rounding arithmetic, plus the

@@ -22,6 +22,7 @@
 #include "gemm_simt.cuh"
 #include "gemm_tc.cuh"
 #include "gemm_tc2.cuh"
+#include "gemm_tf32.cuh"
 #include "route.cuh"
 #include "route_tc.cuh"
 #include "transport.cuh"
@@ -48,7 +49,8 @@ struct State {
     int rank = 0, world = 1, nLx = 0;
     uint32_t epoch = 0;
     long long wait_cycles = 20000000000LL;  // about ten seconds of SM clock (ranks may start far apart)
-    bool use_tc = false;
+    bool use_tc = false;       // 16-bit layers: tcgen05 router and FFN GEMMs
+    bool use_tf32_tc = false;  // TF32 layers: tcgen05 kind::tf32 FFN GEMMs (the router stays on FP32 FMA)
     // num_experts == 1: the layer is a plain FFN over this rank's tokens (the reference switches
     // to its fffn kernel, moe/moe.cuh:174-177,197-204): no gate, no exchange, and the packed
     // buffers carry no gate weight and no probabilities (moe/fffn.cuh:47-53)
@@ -178,8 +180,8 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiledFn g_encode = nullptr;
 
-// bf16 matrix [rows][cols] with cols contiguous; box = 64 columns x box_rows rows, 128-byte
-// swizzle (64 bf16 = 128 bytes, the swizzle span).
+// Matrix [rows][cols] of the layer's element type with cols contiguous; box = box_cols columns x
+// box_rows rows, 128-byte swizzle (64 16-bit or 32 4-byte elements = 128 bytes, the swizzle span).
 int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
              uint32_t box_cols = 64, bool swizzle = true, int promo = 3) {
     if (!g_encode) {
@@ -191,11 +193,12 @@ int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, u
         g_encode = reinterpret_cast<EncodeTiledFn>(fn);
     }
     const cuuint64_t dims[2] = {cols, rows};
-    const cuuint64_t strides[1] = {cols * 2};
+    const cuuint64_t strides[1] = {cols * (cuuint64_t)g.cfg.elem_bytes};
     const cuuint32_t box[2] = {box_cols, box_rows};
     const cuuint32_t estr[2] = {1, 1};
-    const CUtensorMapDataType dt = g.cfg.torch_dtype == 3 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
-                                                          : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    const CUtensorMapDataType dt = g.cfg.torch_dtype == 3   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                   : g.cfg.torch_dtype == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                            : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
     const CUresult r = g_encode(map, dt, 2, const_cast<void*>(base),
                                 dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                 swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
@@ -229,11 +232,20 @@ Sections slice(const void* iP, void* oP) {
 }
 
 int ensure_maps(const Sections& s) {
-    if (!g.use_tc || g.maps_for_iP == s.A) return KLEOS_OK;
+    if ((!g.use_tc && !g.use_tf32_tc) || g.maps_for_iP == s.A) return KLEOS_OK;
     const LayerConfig& c = g.cfg;
     // the dense layer multiplies the activations where they lie: S rows instead of the cells
     const uint64_t cell_rows = g.dense ? (uint64_t)c.S : (uint64_t)g.world * g.nLx * c.pEC;
     int rc;
+    if (g.use_tf32_tc) {
+        const uint32_t bk = gemm_tf32::BK;
+        if ((rc = make_map(&g.map_x, g.dense ? s.A : g.arena + g.lay.xcell, cell_rows, c.H, gemm_tf32::BM, bk))) return rc;
+        if ((rc = make_map(&g.map_w1, s.W1, (uint64_t)g.nLx * c.I, c.H, gemm_tf32::BN, bk))) return rc;
+        if ((rc = make_map(&g.map_y1, g.y1, cell_rows, c.I, gemm_tf32::BM, bk))) return rc;
+        if ((rc = make_map(&g.map_w2, s.W2, (uint64_t)g.nLx * c.H, c.I, gemm_tf32::BN, bk))) return rc;
+        g.maps_for_iP = s.A;
+        return KLEOS_OK;
+    }
     if ((rc = make_map(&g.map_x, g.dense ? s.A : g.arena + g.lay.xcell, cell_rows, c.H, gemm_tc::BM))) return rc;
     if ((rc = make_map(&g.map_w1, s.W1, (uint64_t)g.nLx * c.I, c.H, gemm_tc::BN))) return rc;
     if ((rc = make_map(&g.map_y1, g.y1, cell_rows, c.I, gemm_tc::BM))) return rc;
@@ -281,6 +293,15 @@ void launch_tc2(bool deep, int grid, int threads, cudaStream_t st, const CUtenso
         ffn_gemm_tc2<TE, kEpi, kFused, 2><<<grid, threads, gemm_tc2::SMEM_BYTES, st>>>(map_a, map_b, ga, fa);
     else
         ffn_gemm_tc2<TE, kEpi, kFused, 1><<<grid, threads, gemm_tc2::SMEM_BYTES, st>>>(map_a, map_b, ga, fa);
+}
+
+// TF32 layers: one launch of the kind::tf32 GEMM with the epilogue chosen at compile time.
+void launch_tf32(int epi, cudaStream_t st, const CUtensorMap& map_a, const CUtensorMap& map_b,
+                 const GemmArgs& ga) {
+    const int grid = g.sm_count, smem = gemm_tf32::SMEM_BYTES;
+    if (epi == 0) ffn_gemm_tf32<0><<<grid, 256, smem, st>>>(map_a, map_b, ga);
+    else if (epi == 1) ffn_gemm_tf32<1><<<grid, 256, smem, st>>>(map_a, map_b, ga);
+    else ffn_gemm_tf32<2><<<grid, 256, smem, st>>>(map_a, map_b, ga);
 }
 
 // Optional replacement of the activation input and the layer-output destination of one
@@ -334,6 +355,10 @@ int forward_dense(const Sections& s, const CUtensorMap* map_a, cudaStream_t st, 
                 ffn_gemm_tc<T, 2><<<g.sm_count, 256, gemm_tc::SMEM_BYTES, st>>>(g.map_y1, g.map_w2, g2);
             }
         }
+    } else if (g.use_tf32_tc) {
+        launch_tf32(c.hidden_act, st, *map_a, g.map_w1, g1);
+        KLEOS_CUDA(mark());
+        launch_tf32(2, st, g.map_y1, g.map_w2, g2);
     } else {
         ffn_gemm_simt<T><<<g.sm_count * 2, 256, 0, st>>>(g1);
         KLEOS_CUDA(mark());
@@ -510,6 +535,16 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed, const S
                 KLEOS_CUDA(mark());
             }
         }
+    } else if (g.use_tf32_tc) {
+        for (int p = 0; p < parts; ++p) {
+            if ((rc = next_part(p))) return rc;
+            g1.le_begin = p * g.nLx / parts;
+            g1.le_end = (p + 1) * g.nLx / parts;
+            launch_tf32(c.hidden_act, st, g.map_x, g.map_w1, g1);
+        }
+        KLEOS_CUDA(mark());
+        launch_tf32(2, st, g.map_y1, g.map_w2, g2);
+        KLEOS_CUDA(mark());
     } else {
         for (int p = 0; p < parts; ++p) {
             if ((rc = next_part(p))) return rc;
@@ -543,6 +578,7 @@ int forward_any(const void* iP, void* oP, cudaStream_t st, bool timed, const Sta
     if (!g.initialised) return fail(KLEOS_E_STATE, "kleos_forward before kleos_initialize");
     if (!iP || !oP) return fail(KLEOS_E_ARG, "null buffer");
     if (g.cfg.torch_dtype == 0) return forward_typed<float>(iP, oP, st, timed, stg);
+    if (g.cfg.torch_dtype == 1) return forward_typed<tf32_t>(iP, oP, st, timed, stg);
     if (g.cfg.torch_dtype == 3) return forward_typed<__half>(iP, oP, st, timed, stg);
     return forward_typed<__nv_bfloat16>(iP, oP, st, timed, stg);
 }
@@ -583,6 +619,9 @@ int ensure_host_pipe() {
         KLEOS_CUDA(cudaEventCreateWithFlags(&hp.out_done[b], cudaEventDisableTiming));
         if (g.use_tc && c.PX <= 128) {
             int rc = make_map(&hp.map_act[b], hp.act[b], c.S, c.H, route_tc::BM);
+            if (rc) return rc;
+        } else if (g.use_tf32_tc && g.dense) {
+            int rc = make_map(&hp.map_act[b], hp.act[b], c.S, c.H, gemm_tf32::BM, gemm_tf32::BK);
             if (rc) return rc;
         }
     }
@@ -691,8 +730,6 @@ int kleos_initialize(const char* config_json_path, int rank, int world, const vo
     const bool dense = cfg.E == 1;
     if (!dense && cfg.E % world)
         return fail(KLEOS_E_CONFIG, "num_experts %d does not divide over %d ranks", cfg.E, world);
-    if (cfg.torch_dtype == 1)
-        return fail(KLEOS_E_UNSUPPORTED, "torch_dtype 1 (tf32) is not implemented: use 0 (float), 2 (bf16) or 3 (fp16)");
     if (cfg.K > kMaxTopK) return fail(KLEOS_E_UNSUPPORTED, "expert_top_k > %d", kMaxTopK);
     if (cfg.E > 256) return fail(KLEOS_E_UNSUPPORTED, "num_experts > 256");
     if (world > 1 && !nccl_id && !dense) return fail(KLEOS_E_ARG, "world > 1 needs an NCCL unique id");
@@ -720,6 +757,7 @@ int kleos_initialize(const char* config_json_path, int rank, int world, const vo
     }
     const char* simt = std::getenv("KLEOS_DEBUG_SIMT_GEMM");
     g.use_tc = (cfg.torch_dtype == 2 || cfg.torch_dtype == 3) && !(simt && simt[0] == '1');
+    g.use_tf32_tc = cfg.torch_dtype == 1 && !(simt && simt[0] == '1');
 
     const size_t eb = cfg.elem_bytes;
     const size_t cell_bytes = (size_t)cfg.E * cfg.pEC * cfg.H * eb;  // world*nLx == E
@@ -765,6 +803,12 @@ int kleos_initialize(const char* config_json_path, int rank, int world, const vo
         if (cfg.torch_dtype == 2) rc = set_tc_attributes<__nv_bfloat16>();
         else rc = set_tc_attributes<__half>();
         if (rc) return rc;
+    }
+    if (g.use_tf32_tc) {
+        const auto dyn = cudaFuncAttributeMaxDynamicSharedMemorySize;
+        KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tf32<0>, dyn, gemm_tf32::SMEM_BYTES));
+        KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tf32<1>, dyn, gemm_tf32::SMEM_BYTES));
+        KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tf32<2>, dyn, gemm_tf32::SMEM_BYTES));
     }
     if (const char* pr = std::getenv("KLEOS_GEMM_PAIR")) g.use_pair = pr[0] != '0';
     if (const char* fu = std::getenv("KLEOS_FUSED")) g.use_fused = fu[0] != '0';

@@ -31,6 +31,13 @@ def round_bf16(x: np.ndarray) -> np.ndarray:
     return r.astype(np.uint32).view(np.float32)
 
 
+def round_tf32(x: np.ndarray) -> np.ndarray:
+    """Round fp32 to TF32 (10-bit mantissa, ties to even), returned as fp32 words."""
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    r = (u + np.uint32(0xFFF) + ((u >> np.uint32(13)) & np.uint32(1))) & np.uint32(0xFFFFE000)
+    return r.astype(np.uint32).view(np.float32)
+
+
 def to_bf16_bits(x: np.ndarray) -> np.ndarray:
     """fp32 -> uint16 bf16 bit patterns (round to nearest even)."""
     return (round_bf16(x).view(np.uint32) >> 16).astype(np.uint16)
@@ -43,6 +50,8 @@ def from_bf16_bits(b: np.ndarray) -> np.ndarray:
 def round_to_dtype(x: np.ndarray, torch_dtype: int) -> np.ndarray:
     if torch_dtype == 0:
         return np.asarray(x, dtype=np.float32)
+    if torch_dtype == 1:
+        return round_tf32(x)
     if torch_dtype == 2:
         return round_bf16(x)
     if torch_dtype == 3:
@@ -112,8 +121,8 @@ def packed_input(cfg: KleosConfig, rank: int, world: int, seed: int = 0,
 
 
 def encode(buf_f32: np.ndarray, torch_dtype: int) -> np.ndarray:
-    """fp32 values -> the byte image the device expects (fp32 words or bf16 halves)."""
-    if torch_dtype == 0:
+    """fp32 values -> the byte image the device expects (fp32 words, or bf16 / fp16 halves)."""
+    if torch_dtype in (0, 1):
         return np.ascontiguousarray(buf_f32, dtype=np.float32)
     if torch_dtype == 2:
         return to_bf16_bits(buf_f32)
@@ -123,7 +132,7 @@ def encode(buf_f32: np.ndarray, torch_dtype: int) -> np.ndarray:
 
 
 def decode(raw: np.ndarray, torch_dtype: int) -> np.ndarray:
-    if torch_dtype == 0:
+    if torch_dtype in (0, 1):
         return np.asarray(raw, dtype=np.float32)
     if torch_dtype == 2:
         return from_bf16_bits(np.asarray(raw, dtype=np.uint16))

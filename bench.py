@@ -45,6 +45,11 @@ def workload(name: str):
         return (KleosConfig(sequence_len=8192, hidden_size=2048, intermediate_size=2048,
                             num_experts=8, torch_dtype=2),
                 "C3r8: S=8192 tokens, H=I=2048, E=8, top-2, CF=1, bf16 (per-rank shape of C3 at 8 ranks)")
+    if name == "C2t":
+        # the float benchmark layer C2 with torch_dtype 1: TF32 words on the tensor cores
+        return (KleosConfig(sequence_len=4096, hidden_size=2048, intermediate_size=2048,
+                            num_experts=16, torch_dtype=1),
+                "C2t: S=4096 tokens/rank, H=I=2048, E=16, top-2, CF=1, tf32")
     if name == "F3":
         # single-expert layer = the plain FFN (the reference's dense kernel); 16384 tokens so
         # that activations, intermediate and output (208 MB with the weights) exceed L2
@@ -125,7 +130,7 @@ class ClockSampler:
 
 def torch_dtype_of(cfg):
     import torch
-    return {0: torch.float32, 2: torch.bfloat16, 3: torch.float16}[cfg.torch_dtype]
+    return {0: torch.float32, 1: torch.float32, 2: torch.bfloat16, 3: torch.float16}[cfg.torch_dtype]
 
 
 def synth_on_device(cfg, rank, world, device):
@@ -151,6 +156,10 @@ def synth_on_device(cfg, rank, world, device):
             torch.randn(ih, generator=gen, device=device) / cfg.H ** 0.5).to(tdt)
         buf[off["W2"] + le * ih: off["W2"] + (le + 1) * ih] = (
             torch.randn(ih, generator=gen, device=device) / cfg.I ** 0.5).to(tdt)
+    if cfg.torch_dtype == 1:
+        # TF32 words: 10-bit mantissa, round to nearest even, low 13 bits clear
+        u = buf.view(torch.int32)
+        u.copy_((u + 0xFFF + ((u >> 13) & 1)) & ~0x1FFF)
     return buf
 
 
@@ -344,6 +353,8 @@ def run_cuda(args):
     if cfg.torch_dtype == 0:
         # float layers run on FP32 FMA (as in the reference): nominal 148 SMs x 128 FMA x 1.965 GHz
         peaks = dict(peaks, tflops=74.4, source="nominal fp32 FMA rate (no measured figure)")
+    elif cfg.torch_dtype == 1:
+        peaks = dict(peaks, tflops=1125.0, source="nominal dense TF32 rate, half the bf16 figure (no measured figure)")
     hbm_bound = gemm_bytes / (peaks["hbm"] * 1e9) > gemm_flops / (peaks["tflops"] * 1e12)
     if hbm_bound:
         roof = dict(bound="hbm", achieved=gbs, peak=peaks["hbm"], unit="GB/s", frac=gbs / peaks["hbm"])
@@ -353,7 +364,7 @@ def run_cuda(args):
     # DRAM traffic per launch from the ncu capture of the quarter-size layer (155.3 MB, see
     # profiles/), scaled by the units processed (experts x4, routed rows x4); one-GPU C3 only
     roof["traffic"] = 621.2e6 if (world == 1 and args.workload == "C3") else None
-    roof.update(kernel=("ffn_gemm_simt" if cfg.torch_dtype == 0 else "ffn_gemm_tc2") +
+    roof.update(kernel={0: "ffn_gemm_simt", 1: "ffn_gemm_tf32"}.get(cfg.torch_dtype, "ffn_gemm_tc2") +
                 " (mean of the GEMM1 and GEMM2 launches)",
                 peak_source=peaks["source"], tensor_tflops=tflops, hbm_gbs=gbs,
                 algorithmic_bytes=gemm_bytes, algorithmic_flops=gemm_flops,
@@ -409,7 +420,7 @@ def main():
     ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
     ap.add_argument("--workload", default="C3",
                     help="C3 (default), C4 (Zipf-imbalanced), C5 (large FFN), C1 / C2 (float), "
-                         "C3q / C3r8 (profiling sizes), F3 / F3q (dense FFN, num_experts=1)")
+                         "C2t (C2 as tf32), C3q / C3r8 (profiling sizes), F3 / F3q (dense FFN, num_experts=1)")
     ap.add_argument("--cpu-sample", type=int, default=0,
                     help="tokens in the CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")

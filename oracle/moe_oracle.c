@@ -71,12 +71,22 @@ static inline float round_bf16(float x) {
 
 static inline float round_f16(float x) { return (float)(_Float16)x; }
 
+/* TF32 (dtype 1): an fp32 word with a 10-bit mantissa, round to nearest even; the reference
+ * stores cute::tfloat32_t this way (types.cuh:128-131). */
+static inline float round_tf32(float x) {
+    uint32_t u;
+    memcpy(&u, &x, 4);
+    if ((u & 0x7f800000u) != 0x7f800000u) u = (u + 0xfffu + ((u >> 13) & 1u)) & 0xffffe000u;
+    memcpy(&x, &u, 4);
+    return x;
+}
+
 static inline float round_elem(float x, int dtype) {
-    return dtype == 2 ? round_bf16(x) : dtype == 3 ? round_f16(x) : x;
+    return dtype == 2 ? round_bf16(x) : dtype == 3 ? round_f16(x) : dtype == 1 ? round_tf32(x) : x;
 }
 
 void oracle_round(float* x, size_t n, int dtype) {
-    if (dtype != 2 && dtype != 3) return;
+    if (dtype < 1 || dtype > 3) return;
 #pragma omp parallel for schedule(static)
     for (size_t i = 0; i < n; ++i) x[i] = round_elem(x[i], dtype);
 }

@@ -45,8 +45,19 @@ def _round_bf16(x: np.ndarray) -> np.ndarray:
     return ((u + 0x7FFF + lsb) & 0xFFFF0000).astype(np.uint32).view(np.float32)
 
 
+def _round_tf32(x: np.ndarray) -> np.ndarray:
+    """fp32 word with a 10-bit mantissa, round to nearest even (reference element type
+    cute::tfloat32_t, types.cuh:128-131)."""
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    r = ((u + np.uint32(0xFFF) + ((u >> np.uint32(13)) & np.uint32(1))) & np.uint32(0xFFFFE000)).astype(np.uint32)
+    finite = (u & np.uint32(0x7F800000)) != np.uint32(0x7F800000)
+    return np.where(finite, r, u).astype(np.uint32).view(np.float32)
+
+
 def round_elem(x: np.ndarray, torch_dtype: int) -> np.ndarray:
     x = np.asarray(x, dtype=np.float32)
+    if torch_dtype == 1:
+        return _round_tf32(x)
     if torch_dtype == 2:
         return _round_bf16(x)
     if torch_dtype == 3:

@@ -7,8 +7,10 @@ import numpy as np
 from aristos_b200 import kleos, synth
 from aristos_b200.config import KleosConfig
 
-TOL = {0: 1e-5, 2: 2e-2, 3: 4e-3}  # max_abs(y - y_ref) / max_abs(y_ref): fp32, bf16, fp16 (fp32 accumulation)
-PROB_TOL = {0: 2e-6, 2: 4e-3, 3: 5e-4}  # absolute, gate probabilities (one element ulp at p ~ 0.5)
+# max_abs(y - y_ref) / max_abs(y_ref): fp32, tf32, bf16, fp16 (fp32 accumulation; tf32 and fp16
+# both keep a 10-bit mantissa)
+TOL = {0: 1e-5, 1: 4e-3, 2: 2e-2, 3: 4e-3}
+PROB_TOL = {0: 2e-6, 1: 5e-4, 2: 4e-3, 3: 5e-4}  # absolute, gate probabilities (one element ulp at p ~ 0.5)
 
 
 def make_inputs(cfg: KleosConfig, world: int, seed: int = 0, bias_scale: float = 0.0):

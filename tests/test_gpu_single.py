@@ -91,6 +91,34 @@ def test_single_expert_layer_is_the_dense_ffn(dtype, kw, via_host):
     assert err <= hz.TOL[dtype], f"dense layer error {err}"
 
 
+@pytest.mark.parametrize("simt", [False, True], ids=["tcgen05", "fp32-fma"])
+@pytest.mark.parametrize("kw", [
+    dict(),                                                     # C1 shape
+    dict(num_experts=16, sequence_len=384, hidden_size=192, intermediate_size=320,
+         hidden_act=1),                                         # GELU, N tail (320 % 256), K = 6 slices of 32
+    dict(num_experts=1, expert_top_k=1, sequence_len=384, hidden_size=256, intermediate_size=320),  # dense
+], ids=["c1", "gelu-tail", "dense"])
+def test_tf32_layer(monkeypatch, kw, simt):
+    """torch_dtype 1: fp32 words with a 10-bit mantissa.  Both GEMM back ends (tcgen05 kind::tf32
+    and the FP32 FMA kernel, selected by KLEOS_DEBUG_SIMT_GEMM) against the oracle, nonzero
+    biases, routing bit-exact."""
+    if simt:
+        monkeypatch.setenv("KLEOS_DEBUG_SIMT_GEMM", "1")
+    else:
+        monkeypatch.delenv("KLEOS_DEBUG_SIMT_GEMM", raising=False)
+    cfg = _small(1, **kw)
+    packed, views = hz.make_inputs(cfg, 1, bias_scale=0.5)
+    probs, out, routing = hz.run_layer_single_gpu(cfg, packed[0])
+    assert np.all((out.view(np.uint32) & 0x1FFF) == 0), "outputs must be TF32 words"
+    if cfg.dense:
+        ref = c_oracle.dense_ffn(cfg, views[0])
+        err = np.abs(out - ref).max() / np.abs(ref).max()
+        assert err <= hz.TOL[1], f"dense tf32 error {err}"
+    else:
+        ref = moe_oracle.moe_forward(cfg, 1, views)[0]
+        hz.check_against_oracle(cfg, ref, probs, out, routing)
+
+
 def test_zipf_bias_hot_experts_and_drops():
     """Skewed routing: hot experts overflow their capacity, cold experts receive nothing."""
     cfg = _small(2, num_experts=32, sequence_len=1024, hidden_size=256, intermediate_size=256,

@@ -35,7 +35,7 @@ def test_c_oracle_matches_golden(name):
         _agree(cfg, got, expect[r], 4e-3 if cfg.torch_dtype == 2 else 1e-6)
 
 
-@pytest.mark.parametrize("dtype,world", [(0, 1), (2, 1), (2, 2), (0, 4), (3, 1), (3, 2)])
+@pytest.mark.parametrize("dtype,world", [(0, 1), (2, 1), (2, 2), (0, 4), (3, 1), (3, 2), (1, 1), (1, 2)])
 def test_c_and_numpy_agree_on_fresh_inputs(dtype, world):
     cfg = KleosConfig(sequence_len=128, hidden_size=128, intermediate_size=192, num_experts=8,
                       torch_dtype=dtype)
@@ -44,7 +44,7 @@ def test_c_and_numpy_agree_on_fresh_inputs(dtype, world):
     ref = moe_oracle.moe_forward(cfg, world, views)
     for r in range(world):
         got = c_oracle.moe_forward_rank(cfg, world, r, views)
-        _agree(cfg, got, ref[r], 4e-3 if dtype in (2, 3) else 1e-6)
+        _agree(cfg, got, ref[r], 4e-3 if dtype in (1, 2, 3) else 1e-6)
 
 
 def test_token_subset_equals_full_rows():
@@ -107,3 +107,21 @@ def test_dense_layer_twins_agree_and_match_the_general_path(dtype):
     routed = dict(v, Wg=np.zeros((cfg.PX, cfg.H), dtype=np.float32))
     full = moe_oracle.moe_forward(cfg, 1, [routed])[0]
     assert np.array_equal(full["out"], a)
+
+
+def test_tf32_rounding_is_nearest_even_on_a_ten_bit_mantissa():
+    """torch_dtype 1: fp32 words with the low 13 mantissa bits clear (reference element type
+    cute::tfloat32_t, types.cuh:128-131); both twins and the input generator round alike."""
+    one = np.float32(1.0)
+    ulp = np.float32(2.0 ** -10)
+    x = np.array([one + ulp * np.float32(0.5),      # tie: stays at the even neighbour 1.0
+                  one + ulp * np.float32(1.5),      # tie: goes up to the even neighbour 1 + 2 ulp
+                  one + ulp * np.float32(0.5001),   # above the tie: rounds up
+                  np.float32(-3.14159274), np.float32(np.inf)], dtype=np.float32)
+    want = np.array([1.0, 1.0 + 2 * 2.0 ** -10, 1.0 + 2.0 ** -10, -3.140625, np.inf], dtype=np.float32)
+    assert np.array_equal(moe_oracle.round_elem(x, 1), want)
+    assert np.array_equal(synth.round_to_dtype(x[:4], 1), want[:4])
+    y = x.copy()
+    c_oracle.lib().oracle_round(y.ctypes.data_as(__import__("ctypes").POINTER(__import__("ctypes").c_float)),
+                                __import__("ctypes").c_size_t(y.size), 1)
+    assert np.array_equal(y, want)
