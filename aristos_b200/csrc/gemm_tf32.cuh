@@ -26,11 +26,7 @@ constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int TMEM_COLS = 512;              // two 128x256 fp32 accumulators
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 12288 /*control*/;
 
-// Instruction descriptor of kind::tf32: D fp32 (bits 4-5 = 1), A and B format 2 (tf32) in bits
-// 7-9 and 10-12, both K-major, N >> 3 in bits 17-22, M >> 4 in bits 24-28.
-constexpr uint32_t kInstrDesc = (1u << 4) | (2u << 7) | (2u << 10) |
-                                (static_cast<uint32_t>(BN >> 3) << 17) |
-                                (static_cast<uint32_t>(BM >> 4) << 24);
+constexpr uint32_t kInstrDesc = make_instr_desc_tf32(BM, BN);
 
 struct Control {
     unsigned long long full[STAGES];
@@ -42,16 +38,6 @@ struct Control {
     int le_start[257];
     __align__(16) float bias_s[2][4][256];  // bias of the tile being read back: [accumulator][epilogue warp]
 };
-
-__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
-                                          uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
 
 }  // namespace gemm_tf32
 

@@ -16,6 +16,7 @@
 #include <cstdio>
 #include <cstring>
 #include <string>
+#include <type_traits>
 #include <vector>
 
 #include "config.hpp"
@@ -243,6 +244,10 @@ int ensure_maps(const Sections& s) {
         if ((rc = make_map(&g.map_w1, s.W1, (uint64_t)g.nLx * c.I, c.H, gemm_tf32::BN, bk))) return rc;
         if ((rc = make_map(&g.map_y1, g.y1, cell_rows, c.I, gemm_tf32::BM, bk))) return rc;
         if ((rc = make_map(&g.map_w2, s.W2, (uint64_t)g.nLx * c.H, c.I, gemm_tf32::BN, bk))) return rc;
+        if (c.PX <= 128 && !g.dense) {
+            if ((rc = make_map(&g.map_act, s.A, c.S, c.H, route_tc::BM, bk))) return rc;
+            if ((rc = make_map(&g.map_wg, s.Wg, c.PX, c.H, c.PX, bk))) return rc;
+        }
         g.maps_for_iP = s.A;
         return KLEOS_OK;
     }
@@ -395,8 +400,8 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed, const S
     ra.mcw = g.mcw; ra.refine_list = g.refine_list; ra.refine_count = g.refine_count;
     ra.refine_logits = g.refine_logits; ra.refine_done = g.refine_done;
     ra.S = c.S; ra.H = c.H; ra.E = c.E; ra.K = c.K; ra.PX = c.PX; ra.tie_eps = 1e-4f;
-    if (g.use_tc && c.PX <= 128) {
-        if constexpr (sizeof(T) == 2) {
+    if ((g.use_tc || g.use_tf32_tc) && c.PX <= 128) {
+        if constexpr (!std::is_same<T, float>::value) {
             const int grid = (c.S + route_tc::BM - 1) / route_tc::BM;
             if (c.PX == 64)
                 route_tc_kernel<T, 64><<<grid, 256, route_tc::Shape<64>::SMEM_BYTES, st>>>(
@@ -620,7 +625,8 @@ int ensure_host_pipe() {
         if (g.use_tc && c.PX <= 128) {
             int rc = make_map(&hp.map_act[b], hp.act[b], c.S, c.H, route_tc::BM);
             if (rc) return rc;
-        } else if (g.use_tf32_tc && g.dense) {
+        } else if (g.use_tf32_tc && (g.dense || c.PX <= 128)) {
+            // same box (128 rows x 32 words) serves the tf32 router and the dense layer's GEMM1
             int rc = make_map(&hp.map_act[b], hp.act[b], c.S, c.H, gemm_tf32::BM, gemm_tf32::BK);
             if (rc) return rc;
         }
@@ -809,6 +815,8 @@ int kleos_initialize(const char* config_json_path, int rank, int world, const vo
         KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tf32<0>, dyn, gemm_tf32::SMEM_BYTES));
         KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tf32<1>, dyn, gemm_tf32::SMEM_BYTES));
         KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tf32<2>, dyn, gemm_tf32::SMEM_BYTES));
+        KLEOS_CUDA(cudaFuncSetAttribute(route_tc_kernel<tf32_t, 64>, dyn, route_tc::Shape<64>::SMEM_BYTES));
+        KLEOS_CUDA(cudaFuncSetAttribute(route_tc_kernel<tf32_t, 128>, dyn, route_tc::Shape<128>::SMEM_BYTES));
     }
     if (const char* pr = std::getenv("KLEOS_GEMM_PAIR")) g.use_pair = pr[0] != '0';
     if (const char* fu = std::getenv("KLEOS_FUSED")) g.use_fused = fu[0] != '0';

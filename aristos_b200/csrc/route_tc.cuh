@@ -1,5 +1,7 @@
-// Router on the tensor cores (bf16 layers): gate GEMM with the whole padded expert dimension
-// as one tcgen05 N extent, softmax + top-k in the accumulator read-back.
+// Router on the tensor cores (bf16 / fp16 / tf32 layers): gate GEMM with the whole padded expert
+// dimension as one tcgen05 N extent, softmax + top-k in the accumulator read-back.  A K slice is
+// always 128 bytes wide (64 16-bit or 32 4-byte elements, the swizzle span), four instructions
+// per slice.
 //
 // One block per 128 tokens.  The accumulator is 128 lanes x PX fp32 columns of tensor memory,
 // so every epilogue thread owns one token's full logit row and no cross-block exchange is
@@ -55,8 +57,12 @@ route_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     volatile int* abort_flag = &ctl->abort;
     const int row0 = blockIdx.x * BM;
-    const int KB = a.H / BK;
-    constexpr uint32_t idesc = make_instr_desc_16b(BM, PXT, Pack2<TE>::kMmaFormat);
+    constexpr bool kWide = sizeof(TE) == 4;            // tf32: fp32 words
+    constexpr int BKE = 128 / (int)sizeof(TE);         // elements per K slice
+    const int KB = a.H / BKE;
+    uint32_t idesc;
+    if constexpr (kWide) idesc = make_instr_desc_tf32(BM, PXT);
+    else idesc = make_instr_desc_16b(BM, PXT, Pack2<TE>::kMmaFormat);
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -90,8 +96,8 @@ route_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 }
                 mbar_expect_tx(&ctl->full[s], Sh::STAGE_BYTES);
                 uint8_t* sa = tiles + s * Sh::STAGE_BYTES;
-                tma_load_2d(sa, &map_a, kb * BK, row0, &ctl->full[s]);
-                tma_load_2d(sa + A_STAGE_BYTES, &map_wg, kb * BK, 0, &ctl->full[s]);
+                tma_load_2d(sa, &map_a, kb * BKE, row0, &ctl->full[s]);
+                tma_load_2d(sa + A_STAGE_BYTES, &map_wg, kb * BKE, 0, &ctl->full[s]);
             }
         }
         __syncwarp();
@@ -112,8 +118,10 @@ route_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const uint64_t da = make_smem_desc(sa);
                 const uint64_t db = make_smem_desc(sa + A_STAGE_BYTES);
 #pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k)
-                    umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                for (int k = 0; k < BK / UMMA_K; ++k) {  // four 32-byte steps per slice
+                    if constexpr (kWide) umma_tf32(tmem_base, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    else umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                }
                 umma_commit(&ctl->empty[s]);
             }
             if (ok) umma_commit(&ctl->acc_full);
@@ -166,8 +174,12 @@ route_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const float m = rowmax[rr], inv = rowden[rr];
                 const float p0 = e < a.E ? __expf(Ls[rr * Sh::LDL + e] - m) * inv : 0.f;
                 const float p1 = e + 1 < a.E ? __expf(Ls[rr * Sh::LDL + e + 1] - m) * inv : 0.f;
-                *reinterpret_cast<typename Pack2<TE>::type*>(probs + (size_t)(row0 + rr) * PXT + e) =
-                    Pack2<TE>::from_f2(p0, p1);
+                TE* dst = probs + (size_t)(row0 + rr) * PXT + e;
+                if constexpr (kWide) {
+                    *reinterpret_cast<float2*>(dst) = make_float2(round_tf32(p0), round_tf32(p1));
+                } else {
+                    *reinterpret_cast<typename Pack2<TE>::type*>(dst) = Pack2<TE>::from_f2(p0, p1);
+                }
             }
         }
     }

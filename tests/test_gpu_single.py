@@ -155,7 +155,7 @@ def test_against_committed_golden_fixtures(name):
     hz.check_against_oracle(cfg, ref, probs, out, routing)
 
 
-@pytest.mark.parametrize("dtype,experts", [(2, 8), (0, 8), (2, 1)])
+@pytest.mark.parametrize("dtype,experts", [(2, 8), (0, 8), (2, 1), (1, 8), (1, 1)])
 def test_pipelined_host_path_matches_synchronous_path(dtype, experts):
     """Three queued end-to-end steps with alternating inputs and separate host outputs: each
     must equal what the synchronous host-buffer call returns for the same input."""
