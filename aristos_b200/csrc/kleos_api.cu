@@ -76,6 +76,9 @@ struct State {
         *refine_count = nullptr, *le_start = nullptr, *refine_done = nullptr, *tile_hist = nullptr;
     double* refine_logits = nullptr;
     float *mcw = nullptr, *bias = nullptr;
+    // training mode (is_training = 1): per-router-block probability column sums and the
+    // statistics [mean_prob E][mean_count E][loss] of the last forward
+    float *col_partial = nullptr, *gate_stats = nullptr;
     unsigned *counts = nullptr, *done_dispatch = nullptr, *done_gemm2 = nullptr,
              *cell_counts = nullptr, *cell_done = nullptr;
     PanelEntry* panels = nullptr;
@@ -400,7 +403,10 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed, const S
     ra.mcw = g.mcw; ra.refine_list = g.refine_list; ra.refine_count = g.refine_count;
     ra.refine_logits = g.refine_logits; ra.refine_done = g.refine_done;
     ra.S = c.S; ra.H = c.H; ra.E = c.E; ra.K = c.K; ra.PX = c.PX; ra.tie_eps = 1e-4f;
+    ra.col_partial = g.col_partial;  // null unless is_training
+    int route_blocks = (c.S + 63) / 64;
     if ((g.use_tc || g.use_tf32_tc) && c.PX <= 128) {
+        route_blocks = (c.S + route_tc::BM - 1) / route_tc::BM;
         if constexpr (!std::is_same<T, float>::value) {
             const int grid = (c.S + route_tc::BM - 1) / route_tc::BM;
             if (c.PX == 64)
@@ -425,6 +431,8 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed, const S
     sa.tile_hist = g.tile_hist;
     tile_hist_kernel<<<(c.S + kSlotTile - 1) / kSlotTile, 256, 0, st>>>(sa);
     slot_kernel<<<(c.S + kSlotTile - 1) / kSlotTile, 256, 0, st>>>(sa);
+    if (g.col_partial)
+        gate_stats_kernel<<<1, 256, 0, st>>>(g.col_partial, route_blocks, c.PX, g.counts, c.S, c.E, g.gate_stats);
     KLEOS_CUDA(mark());
 
     const bool fused = g.use_tc && g.use_pair && g.use_fused;
@@ -643,6 +651,7 @@ void release_all() {
     cudaFree(g.refine_list); cudaFree(g.refine_count); cudaFree(g.tile_hist); cudaFree(g.refine_done); cudaFree(g.refine_logits); cudaFree(g.le_start); cudaFree(g.mcw);
     cudaFree(g.bias); cudaFree(g.counts); cudaFree(g.done_dispatch); cudaFree(g.done_gemm2);
     cudaFree(g.cell_counts); cudaFree(g.cell_done); cudaFree(g.panels); cudaFree(g.status); cudaFree(g.gemm_stats);
+    cudaFree(g.col_partial); cudaFree(g.gate_stats);
     for (auto& e : g.ev)
         if (e) cudaEventDestroy(e);
     for (auto& e : g.ev_part)
@@ -797,6 +806,10 @@ int kleos_initialize(const char* config_json_path, int rank, int world, const vo
     if ((rc = dev_alloc(&g.cell_done, (size_t)cfg.E))) return rc;
     if ((rc = dev_alloc(&g.panels, (size_t)cfg.E * cfg.pEC / kTileM))) return rc;
     if ((rc = dev_alloc(&g.status, 1))) return rc;
+    if (cfg.is_training && !dense) {
+        if ((rc = dev_alloc(&g.col_partial, (size_t)((cfg.S + 63) / 64) * cfg.PX))) return rc;
+        if ((rc = dev_alloc(&g.gate_stats, (size_t)2 * cfg.E + 1))) return rc;
+    }
     for (auto& e : g.ev) KLEOS_CUDA(cudaEventCreate(&e));
     KLEOS_CUDA(cudaStreamCreateWithFlags(&g.copy_stream, cudaStreamNonBlocking));
     KLEOS_CUDA(cudaEventCreateWithFlags(&g.ev_slots, cudaEventDisableTiming));
@@ -1020,6 +1033,18 @@ int kleos_debug_routing(int32_t* topk, int32_t* slots, uint32_t* counts, float* 
     if (slots) KLEOS_CUDA(cudaMemcpy(slots, g.slots, sk * 4, cudaMemcpyDeviceToHost));
     if (counts) KLEOS_CUDA(cudaMemcpy(counts, g.counts, (size_t)c.E * 4, cudaMemcpyDeviceToHost));
     if (mcw) KLEOS_CUDA(cudaMemcpy(mcw, g.mcw, (size_t)c.S * 4, cudaMemcpyDeviceToHost));
+    return KLEOS_OK;
+}
+
+int kleos_gate_stats(float* mean_prob, float* mean_count, float* loss) {
+    if (!g.initialised) return fail(KLEOS_E_STATE, "not initialised");
+    if (!g.gate_stats)
+        return fail(KLEOS_E_STATE, "gate statistics are kept only when is_training = 1 (and num_experts > 1)");
+    KLEOS_CUDA(cudaStreamSynchronize(cudaStreamPerThread));
+    const int E = g.cfg.E;
+    if (mean_prob) KLEOS_CUDA(cudaMemcpy(mean_prob, g.gate_stats, sizeof(float) * E, cudaMemcpyDeviceToHost));
+    if (mean_count) KLEOS_CUDA(cudaMemcpy(mean_count, g.gate_stats + E, sizeof(float) * E, cudaMemcpyDeviceToHost));
+    if (loss) KLEOS_CUDA(cudaMemcpy(loss, g.gate_stats + 2 * E, sizeof(float), cudaMemcpyDeviceToHost));
     return KLEOS_OK;
 }
 

@@ -26,6 +26,10 @@ struct RouteArgs {
     int* refine_done;       // [S] per listed token: logits finished (zero between forwards)
     int S, H, E, K, PX;
     float tie_eps;
+    // training mode only, else null: [router blocks][PX] column sums of the fp32 probabilities
+    // of each block's tokens, summed in a fixed order (the reference accumulates the same
+    // per-expert mean with atomicAdd, moe/gate.cuh:607-635)
+    float* col_partial;
 };
 
 // One token's routing decision from its fp32 logits (in shared memory):
@@ -182,12 +186,52 @@ __global__ void __launch_bounds__(256) route_kernel(RouteArgs a) {
     __syncthreads();
     // probabilities, coalesced, padding columns zero (PX == PXT: both are E rounded up to 64)
     T* probs = static_cast<T*>(a.probs);
+    float colsum = 0.f;  // 256 % PXT == 0: a thread always visits the same expert column
     for (int idx = tid; idx < BM * PXT; idx += 256) {
         const int r = idx / PXT, e = idx % PXT;
         if (row0 + r >= a.S) break;
         float p = 0.f;
         if (e < a.E) p = __expf(Ls[r * LDL + e] - rowmax[r]) * rowden[r];
+        colsum += p;
         probs[(size_t)(row0 + r) * PXT + e] = Elem<T>::from_f(p);
+    }
+    if (a.col_partial != nullptr) {
+        __syncthreads();  // everyone is done with the logit tile: reuse it
+        smem[tid] = colsum;
+        __syncthreads();
+        if (tid < PXT) {
+            float sum = 0.f;
+            for (int k = 0; k < 256 / PXT; ++k) sum += smem[tid + k * PXT];
+            a.col_partial[(size_t)blockIdx.x * PXT + tid] = sum;
+        }
+    }
+}
+
+// Training-mode gate statistics of one rank's tokens, as the reference keeps them in its
+// bookkeeping (types.cuh:944-960): mean probability per expert (moe/gate.cuh:607-635), fraction
+// of the tokens that chose each expert (unclamped, :698-705) and the auxiliary loss
+// sum_e mean_prob[e] * mean_count[e] / E (:763-773).  One block; all sums in a fixed order.
+// out = [mean_prob E][mean_count E][loss 1].
+__global__ void __launch_bounds__(256) gate_stats_kernel(const float* col_partial, int blocks,
+                                                         int PX, const unsigned* counts, int S,
+                                                         int E, float* out) {
+    __shared__ float term[256];
+    const int e = threadIdx.x;
+    float t = 0.f;
+    if (e < E) {
+        float sum = 0.f;
+        for (int b = 0; b < blocks; ++b) sum += col_partial[(size_t)b * PX + e];
+        const float mp = sum / (float)S, mc = (float)counts[e] / (float)S;
+        out[e] = mp;
+        out[E + e] = mc;
+        t = mp * mc / (float)E;
+    }
+    term[e] = t;
+    __syncthreads();
+    if (e == 0) {
+        float loss = 0.f;
+        for (int i = 0; i < E; ++i) loss += term[i];
+        out[2 * E] = loss;
     }
 }
 

@@ -167,19 +167,41 @@ route_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         if (ok && !*abort_flag) {
             TE* probs = static_cast<TE*>(a.probs);
             const int et = tid - 128;
-            // two adjacent probabilities per thread, 4-byte stores (PX == PXT)
+            // two adjacent probabilities per thread, 4-byte stores (PX == PXT); 256 % PXT == 0,
+            // so a thread always visits the same two expert columns
+            float cs0 = 0.f, cs1 = 0.f;
             for (int idx = 2 * et; idx < BM * PXT; idx += 256) {
                 const int rr = idx / PXT, e = idx % PXT;
                 if (row0 + rr >= a.S) break;
                 const float m = rowmax[rr], inv = rowden[rr];
                 const float p0 = e < a.E ? __expf(Ls[rr * Sh::LDL + e] - m) * inv : 0.f;
                 const float p1 = e + 1 < a.E ? __expf(Ls[rr * Sh::LDL + e + 1] - m) * inv : 0.f;
+                cs0 += p0;
+                cs1 += p1;
                 TE* dst = probs + (size_t)(row0 + rr) * PXT + e;
                 if constexpr (kWide) {
                     *reinterpret_cast<float2*>(dst) = make_float2(round_tf32(p0), round_tf32(p1));
                 } else {
                     *reinterpret_cast<typename Pack2<TE>::type*>(dst) = Pack2<TE>::from_f2(p0, p1);
                 }
+            }
+            // training mode: stash this thread's two column sums of the fp32 probabilities in
+            // the operand stages (free once the accumulator is full)
+            if (a.col_partial != nullptr) {
+                float* cs = reinterpret_cast<float*>(tiles);
+                cs[2 * et] = cs0;
+                cs[2 * et + 1] = cs1;
+            }
+        }
+        if (a.col_partial != nullptr) {
+            // every epilogue thread takes part in the barrier, also after a failed wait
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const int et = tid - 128;
+            if (ok && !*abort_flag && et < PXT) {
+                const float* cs = reinterpret_cast<const float*>(tiles);
+                float sum = 0.f;
+                for (int k = 0; k < 256 / PXT; ++k) sum += cs[et + k * PXT];  // fixed order
+                a.col_partial[(size_t)blockIdx.x * PXT + et] = sum;
             }
         }
     }

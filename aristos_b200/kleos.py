@@ -27,7 +27,7 @@ EXPORTS = (
     "kleos_forward", "kleos_forward_bench", "kleos_forward_host", "kleos_forward_host_async",
     "kleos_host_sync", "kleos_get_rank",
     "kleos_local_experts", "kleos_get_info", "kleos_last_status", "kleos_clear_status", "kleos_debug_routing",
-    "kleos_phase_times", "kleos_debug_gemm_stats", "kleos_debug_suppress_return_flag", "kleos_route_static", "kleos_finalize", "kleos_error_string",
+    "kleos_phase_times", "kleos_debug_gemm_stats", "kleos_debug_suppress_return_flag", "kleos_gate_stats", "kleos_route_static", "kleos_finalize", "kleos_error_string",
 )
 
 PHASE_NAMES = ("route", "slots", "dispatch", "plan", "gemm1", "gemm2", "combine", "total")
@@ -72,6 +72,7 @@ def load_library() -> ctypes.CDLL:
         lib.kleos_forward_host_async.argtypes = [ctypes.c_void_p] * 4
         lib.kleos_set_gate_bias.argtypes = [ctypes.c_void_p, ctypes.c_int]
         lib.kleos_debug_routing.argtypes = [ctypes.c_void_p] * 4
+        lib.kleos_gate_stats.argtypes = [ctypes.c_void_p] * 3
         lib.kleos_phase_times.argtypes = [ctypes.POINTER(ctypes.c_float), ctypes.c_int]
         lib.kleos_get_unique_id.argtypes = [ctypes.c_void_p]
         _lib = lib
@@ -221,6 +222,18 @@ def debug_routing(info: LayerInfo) -> dict:
                                               counts.ctypes.data, mcw.ctypes.data),
            "kleos_debug_routing")
     return dict(topk=topk, slots=slots, counts=counts, mcw=mcw)
+
+
+def gate_stats(info: LayerInfo) -> dict:
+    """Training-mode gate statistics of the last forward: mean probability and mean (unclamped)
+    selection count per expert, and the auxiliary loss (needs is_training = 1)."""
+    import numpy as np
+    mean_prob = np.empty(info.E, dtype=np.float32)
+    mean_count = np.empty(info.E, dtype=np.float32)
+    loss = np.empty(1, dtype=np.float32)
+    _check(load_library().kleos_gate_stats(mean_prob.ctypes.data, mean_count.ctypes.data,
+                                           loss.ctypes.data), "kleos_gate_stats")
+    return dict(mean_prob=mean_prob, mean_count=mean_count, loss=float(loss[0]))
 
 
 def finalize() -> None:

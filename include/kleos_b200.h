@@ -162,6 +162,17 @@ int kleos_route_static(const void* A, const void* Wg, const float* gate_bias, in
                        int K, int torch_dtype, void* probs, int32_t* topk, float* mcw,
                        void* stream);
 
+/* Training-mode gate statistics of the last forward on this rank (is_training = 1 in the
+ * configuration, num_experts > 1), the three quantities the reference keeps in its device
+ * bookkeeping (types.cuh:944-960) and never copies out:
+ *   mean_prob[e]  = (1/S) sum_t p(t,e), fp32 softmax probabilities      (moe/gate.cuh:607-635)
+ *   mean_count[e] = (tokens of this rank that chose e, before capacity) / S   (:698-705)
+ *   loss          = sum_e mean_prob[e] * mean_count[e] / E              (:763-773)
+ * Host pointers, E floats / E floats / 1 float; any may be NULL.  The reference accumulates
+ * with atomicAdd and never clears between launches; here every forward overwrites the values
+ * and the sums run in a fixed order.  KLEOS_E_STATE when the layer was not set up for training. */
+int kleos_gate_stats(float* mean_prob, float* mean_count, float* loss);
+
 /* Test hook for the failure path: while on, the expert FFN does not raise its "results
  * returned" flags, so the combine's bounded wait runs out, the forward records
  * {KLEOS_E_DEVICE, KLEOS_AT_COMBINE_WAIT} and returns with the context intact.  Nothing is

@@ -23,6 +23,7 @@ Reference lines followed (paths inside the reference project):
   * combine: out[t] += Element(y2 / mCw) * Element(prob[t,e])   processor.cuh:110-168
   * expert -> rank map (contiguous, even)   bootstrap.cuh:36-52
   * single-expert (dense) layer   moe/moe.cuh:174-177, moe/fffn.cuh:31-167
+  * training-mode gate statistics and loss   moe/gate.cuh:607-635,698-705,763-773
 
 Deliberate choices where the reference leaves the outcome open:
   * slot order inside an expert is ascending token index (the reference orders by
@@ -97,8 +98,14 @@ def route(cfg, a: np.ndarray, wg: np.ndarray, gate_bias=None) -> dict:
     routed = np.minimum(counts, cfg.EC).astype(np.uint32)
     probs_pad = np.zeros((S, cfg.PX), dtype=np.float32)
     probs_pad[:, :E] = round_elem(probs, cfg.torch_dtype)
+    # training-mode statistics (moe/gate.cuh:607-635 mean probability per expert, :698-705 mean
+    # unclamped selection count, :763-773 loss = sum_e mean_prob * mean_count / E)
+    mean_prob = probs.astype(np.float64).mean(axis=0)
+    mean_count = counts.astype(np.float64) / S
+    gate_loss = float((mean_prob * mean_count).sum() / E)
     return dict(logits=logits, probs_f32=probs, probs=probs_pad, topk=topk, mcw=mcw,
-                slots=slots, counts=counts, routed=routed, margin=margin)
+                slots=slots, counts=counts, routed=routed, margin=margin,
+                mean_prob=mean_prob, mean_count=mean_count, gate_loss=gate_loss)
 
 
 def expert_ffn(cfg, x: np.ndarray, w1, w2, b1, b2) -> np.ndarray:

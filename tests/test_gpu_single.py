@@ -119,6 +119,50 @@ def test_tf32_layer(monkeypatch, kw, simt):
         hz.check_against_oracle(cfg, ref, probs, out, routing)
 
 
+@pytest.mark.parametrize("dtype,kw", [
+    (2, dict()), (0, dict()), (1, dict()),
+    (2, dict(num_experts=128, sequence_len=512, hidden_size=256, intermediate_size=320)),   # PX = 128
+    (0, dict(num_experts=200, sequence_len=256, hidden_size=128, intermediate_size=128)),   # PX = 256, FFMA router
+])
+def test_training_mode_gate_statistics(dtype, kw):
+    """is_training = 1: mean probability per expert, mean selection count and the auxiliary
+    loss of the last forward against the oracle (reference moe/gate.cuh:607-635,698-705,763-773);
+    the layer output is unaffected."""
+    import torch
+    from aristos_b200 import kleos
+    cfg = _small(dtype, is_training=1, **kw)
+    packed, views = hz.make_inputs(cfg, 1)
+    ref = moe_oracle.moe_forward(cfg, 1, views)[0]
+    raw = synth.encode(packed[0], dtype)
+    info = kleos.initialize(cfg, 0, 1)
+    try:
+        iP = torch.from_numpy(raw.view(np.uint8).copy()).cuda()
+        oP = torch.zeros(info.output_elems * info.elem_bytes, dtype=torch.uint8, device="cuda")
+        for _ in range(2):  # every forward overwrites the statistics
+            kleos.forward_host(iP, oP)
+        assert kleos.last_status().code == 0
+        st = kleos.gate_stats(info)
+        routing = kleos.debug_routing(info)
+    finally:
+        kleos.finalize()
+    assert np.array_equal(routing["counts"], ref["counts"])
+    assert np.array_equal(st["mean_count"], (ref["counts"].astype(np.float32) / np.float32(cfg.S)))
+    assert np.abs(st["mean_prob"] - ref["mean_prob"]).max() <= 2e-6
+    assert abs(st["mean_prob"].sum() - 1.0) <= 1e-5
+    assert abs(st["loss"] - ref["gate_loss"]) <= 1e-6 * max(1.0, abs(ref["gate_loss"]))
+
+
+def test_gate_statistics_need_training_mode():
+    from aristos_b200 import kleos
+    cfg = _small(2)
+    info = kleos.initialize(cfg, 0, 1)
+    try:
+        with pytest.raises(kleos.KleosError):
+            kleos.gate_stats(info)
+    finally:
+        kleos.finalize()
+
+
 def test_zipf_bias_hot_experts_and_drops():
     """Skewed routing: hot experts overflow their capacity, cold experts receive nothing."""
     cfg = _small(2, num_experts=32, sequence_len=1024, hidden_size=256, intermediate_size=256,
