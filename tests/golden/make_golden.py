@@ -29,13 +29,20 @@ CASES = {
                           torch_dtype=2, capacity_factor=1.25), 2, 1.2),
     "fp32_top1": (dict(sequence_len=128, hidden_size=64, intermediate_size=64, num_experts=4,
                        torch_dtype=0, expert_top_k=1), 1, None),
+    # later additions carry a fourth entry: the standard deviation of the FFN biases
+    "tf32_gelu_biased": (dict(sequence_len=128, hidden_size=64, intermediate_size=128, num_experts=8,
+                              torch_dtype=1, hidden_act=1), 1, None, 0.5),
+    "fp16_biased": (dict(sequence_len=128, hidden_size=64, intermediate_size=64, num_experts=16,
+                         torch_dtype=3), 1, None, 0.5),
 }
+STAT_KEYS = ("mean_prob", "mean_count", "gate_loss")  # training-mode gate statistics
 
 
 def build_case(name):
-    kw, world, zipf = CASES[name]
+    kw, world, zipf = CASES[name][:3]
+    bias_scale = CASES[name][3] if len(CASES[name]) > 3 else 0.0
     cfg = KleosConfig(**kw)
-    packed = [synth.packed_input(cfg, r, world) for r in range(world)]
+    packed = [synth.packed_input(cfg, r, world, bias_scale=bias_scale) for r in range(world)]
     views = [synth.split_packed(cfg, p, world) for p in packed]
     bias = synth.zipf_gate_bias(cfg, zipf) * 2.0 if zipf else None
     res = moe_oracle.moe_forward(cfg, world, views, gate_bias=bias)
@@ -46,12 +53,17 @@ def build_case(name):
         out[f"packed_{r}"] = packed[r]
         for k in ("probs", "topk", "slots", "counts", "mcw", "out"):
             out[f"{k}_{r}"] = res[r][k]
+        if bias_scale:  # the newer fixtures also pin the gate statistics
+            for k in STAT_KEYS:
+                out[f"{k}_{r}"] = np.asarray(res[r][k], dtype=np.float64)
     return out
 
 
 def main():
     for name in CASES:
         path = os.path.join(HERE, f"{name}.npz")
+        if os.path.exists(path) and "--all" not in sys.argv:
+            continue  # committed fixtures are only rewritten on request
         np.savez_compressed(path, **build_case(name))
         print(path, os.path.getsize(path) // 1024, "KiB")
 

@@ -25,6 +25,8 @@ def load(name):
     bias = z["bias"] if z["bias"].size else None
     packed = [z[f"packed_{r}"] for r in range(world)]
     views = [synth.split_packed(cfg, p, world) for p in packed]
-    expect = [{k: z[f"{k}_{r}"] for k in ("probs", "topk", "slots", "counts", "mcw", "out")}
+    expect = [{k: z[f"{k}_{r}"] for k in ("probs", "topk", "slots", "counts", "mcw", "out",
+                                          "mean_prob", "mean_count", "gate_loss")
+               if f"{k}_{r}" in z.files}
               for r in range(world)]
     return cfg, world, bias, packed, views, expect

@@ -188,7 +188,7 @@ def test_baseline_config_sampled(name):
     hz.check_against_oracle(cfg, ref, probs, out, routing, rows=rows)
 
 
-@pytest.mark.parametrize("name", ["fp32_w1", "bf16_w1", "fp32_top1"])
+@pytest.mark.parametrize("name", ["fp32_w1", "bf16_w1", "fp32_top1", "tf32_gelu_biased", "fp16_biased"])
 def test_against_committed_golden_fixtures(name):
     from tests import golden_util
     cfg, world, bias, packed, _, expect = golden_util.load(name)
