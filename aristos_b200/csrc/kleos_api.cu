@@ -24,6 +24,7 @@
 #include "gemm_tc.cuh"
 #include "gemm_tc2.cuh"
 #include "gemm_tf32.cuh"
+#include "placement.hpp"
 #include "route.cuh"
 #include "route_tc.cuh"
 #include "transport.cuh"
@@ -1033,6 +1034,63 @@ int kleos_debug_routing(int32_t* topk, int32_t* slots, uint32_t* counts, float* 
     if (slots) KLEOS_CUDA(cudaMemcpy(slots, g.slots, sk * 4, cudaMemcpyDeviceToHost));
     if (counts) KLEOS_CUDA(cudaMemcpy(counts, g.counts, (size_t)c.E * 4, cudaMemcpyDeviceToHost));
     if (mcw) KLEOS_CUDA(cudaMemcpy(mcw, g.mcw, (size_t)c.S * 4, cudaMemcpyDeviceToHost));
+    return KLEOS_OK;
+}
+
+int kleos_placement_model(const char* config_json_path, uint32_t* moe_stages, uint32_t* p2p_buffer_mb,
+                          uint32_t* grad_buffer_mb) {
+    if (!config_json_path || !moe_stages || !p2p_buffer_mb || !grad_buffer_mb)
+        return fail(KLEOS_E_ARG, "null argument");
+    LayerConfig c;
+    const std::string err = load_config(config_json_path, &c);
+    if (!err.empty()) return fail(KLEOS_E_CONFIG, "%s: %s", config_json_path, err.c_str());
+    if (c.mini_batch < 1 || c.moe_frequency < 1) return fail(KLEOS_E_CONFIG, "mini_batch and moe_frequency must be >= 1");
+    // types.cuh:487-494: global MoE stages, parameter count, gradient and dispatch buffers in MB
+    const long long mib = 1024LL * 1024LL;
+    *moe_stages = (uint32_t)((c.is_training ? 3 : 1) * (c.global_batch / c.mini_batch) * (c.num_layers / c.moe_frequency));
+    const long long H = c.H;
+    const long long pc = H * ((long long)c.num_layers * (12 * H + 13) + ((long long)c.vocab_size + H));
+    *grad_buffer_mb = (uint32_t)((pc + mib - 1) / mib);
+    *p2p_buffer_mb = (uint32_t)(((long long)c.S * H + mib - 1) / mib);
+    return KLEOS_OK;
+}
+
+int kleos_plan_placement(const kleos_placement_request* rq, kleos_placement_result* res,
+                         uint32_t* device_to_group, uint32_t* group_ranks, uint32_t* expert_to_member) {
+    if (!rq || !res) return fail(KLEOS_E_ARG, "null argument");
+    if (rq->world < 1 || rq->world > 4096 || rq->num_experts < 1 || rq->num_experts > 65535 ||
+        rq->expert_cost < 1 || rq->expert_cost > 65535 || !rq->alpha || !rq->beta || !rq->rate || !rq->mem)
+        return fail(KLEOS_E_ARG, "planner request out of range");
+    placement::Inputs in;
+    in.world = rq->world;
+    const size_t ww = (size_t)rq->world * rq->world;
+    in.alpha.assign(rq->alpha, rq->alpha + ww);
+    in.beta.assign(rq->beta, rq->beta + ww);
+    in.rate.assign(rq->rate, rq->rate + rq->world);
+    in.mem.assign(rq->mem, rq->mem + rq->world);
+    in.num_experts = rq->num_experts;
+    in.expert_cost = rq->expert_cost;
+    in.training = rq->is_training != 0;
+    in.model = placement::Model{rq->moe_stages, rq->p2p_buffer_mb, rq->grad_buffer_mb};
+    placement::Plan p;
+    std::string why;
+    if (!placement::make_plan(in, rq->rank, &p, &why)) return fail(KLEOS_E_ARG, "%s", why.c_str());
+    *res = kleos_placement_result{};
+    res->feasible = p.feasible ? 1 : 0;
+    if (device_to_group) std::copy(p.device_to_group.begin(), p.device_to_group.end(), device_to_group);
+    if (!p.feasible) return KLEOS_OK;
+    res->group_size = (int32_t)p.group_ranks.size();
+    res->group_rank = (int32_t)p.group_rank;
+    res->local_experts = (int32_t)p.local_experts;
+    res->expert_slots = (int32_t)p.expert_slots;
+    res->widest_group = (int32_t)p.widest_group;
+    // the data path of this library shards the experts evenly and contiguously over all ranks
+    res->matches_data_path = 1;
+    if ((int)p.group_ranks.size() != rq->world || rq->num_experts % rq->world) res->matches_data_path = 0;
+    for (int e = 0; e < rq->num_experts && res->matches_data_path; ++e)
+        if ((int)p.group_ranks[p.expert_to_member[e]] != e / (rq->num_experts / rq->world)) res->matches_data_path = 0;
+    if (group_ranks) std::copy(p.group_ranks.begin(), p.group_ranks.end(), group_ranks);
+    if (expert_to_member) std::copy(p.expert_to_member.begin(), p.expert_to_member.end(), expert_to_member);
     return KLEOS_OK;
 }
 

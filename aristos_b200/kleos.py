@@ -27,7 +27,7 @@ EXPORTS = (
     "kleos_forward", "kleos_forward_bench", "kleos_forward_host", "kleos_forward_host_async",
     "kleos_host_sync", "kleos_get_rank",
     "kleos_local_experts", "kleos_get_info", "kleos_last_status", "kleos_clear_status", "kleos_debug_routing",
-    "kleos_phase_times", "kleos_debug_gemm_stats", "kleos_debug_suppress_return_flag", "kleos_gate_stats", "kleos_route_static", "kleos_finalize", "kleos_error_string",
+    "kleos_phase_times", "kleos_debug_gemm_stats", "kleos_debug_suppress_return_flag", "kleos_gate_stats", "kleos_plan_placement", "kleos_placement_model", "kleos_route_static", "kleos_finalize", "kleos_error_string",
 )
 
 PHASE_NAMES = ("route", "slots", "dispatch", "plan", "gemm1", "gemm2", "combine", "total")
@@ -222,6 +222,61 @@ def debug_routing(info: LayerInfo) -> dict:
                                               counts.ctypes.data, mcw.ctypes.data),
            "kleos_debug_routing")
     return dict(topk=topk, slots=slots, counts=counts, mcw=mcw)
+
+
+class PlacementRequest(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int32) for n in ("world", "rank", "num_experts", "expert_cost", "is_training")] + \
+               [(n, ctypes.c_uint32) for n in ("moe_stages", "p2p_buffer_mb", "grad_buffer_mb")] + \
+               [(n, ctypes.c_void_p) for n in ("alpha", "beta", "rate", "mem")]
+
+
+class PlacementResult(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int32) for n in ("feasible", "group_size", "group_rank", "local_experts",
+                                              "expert_slots", "widest_group", "matches_data_path")]
+
+
+def placement_model(config) -> dict:
+    """Cost-model constants of the placement planner for a layer (needs no GPU)."""
+    import tempfile
+    lib = load_library()
+    vals = [ctypes.c_uint32() for _ in range(3)]
+    with tempfile.TemporaryDirectory() as d:
+        path = config if isinstance(config, str) else os.path.join(d, "kleos_config.json")
+        if not isinstance(config, str):
+            config.to_json(path)
+        _check(lib.kleos_placement_model(path.encode(), *[ctypes.byref(v) for v in vals]),
+               "kleos_placement_model")
+    return dict(moe_stages=vals[0].value, p2p_buffer=vals[1].value, grad_buffer=vals[2].value)
+
+
+def plan_placement(alpha, beta, rate, mem, num_experts, model: dict, rank: int = 0,
+                   expert_cost: int = 1, training: bool = False) -> dict:
+    """Device groups and expert placement from a measured topology (host only)."""
+    import numpy as np
+    a = np.ascontiguousarray(alpha, dtype=np.float32)
+    b = np.ascontiguousarray(beta, dtype=np.float32)
+    r = np.ascontiguousarray(rate, dtype=np.float32)
+    m = np.ascontiguousarray(mem, dtype=np.uint32)
+    world = r.size
+    assert a.shape == (world, world) and b.shape == (world, world) and m.size == world
+    rq = PlacementRequest(world, rank, num_experts, expert_cost, int(training), model["moe_stages"],
+                          model["p2p_buffer"], model["grad_buffer"], a.ctypes.data, b.ctypes.data,
+                          r.ctypes.data, m.ctypes.data)
+    res = PlacementResult()
+    d2g = np.zeros(world, dtype=np.uint32)
+    ranks = np.zeros(world, dtype=np.uint32)
+    e2m = np.zeros(num_experts, dtype=np.uint32)
+    lib = load_library()
+    lib.kleos_plan_placement.argtypes = [ctypes.c_void_p] * 5
+    _check(lib.kleos_plan_placement(ctypes.byref(rq), ctypes.byref(res), d2g.ctypes.data,
+                                    ranks.ctypes.data, e2m.ctypes.data), "kleos_plan_placement")
+    out = dict(feasible=bool(res.feasible), device_to_group=d2g.tolist())
+    if res.feasible:
+        out.update(group_ranks=ranks[:res.group_size].tolist(), group_rank=res.group_rank,
+                   expert_to_member=e2m.tolist(), local_experts=res.local_experts,
+                   expert_slots=res.expert_slots, widest_group=res.widest_group,
+                   matches_data_path=bool(res.matches_data_path))
+    return out
 
 
 def gate_stats(info: LayerInfo) -> dict:

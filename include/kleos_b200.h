@@ -173,6 +173,40 @@ int kleos_route_static(const void* A, const void* Wg, const float* gate_bias, in
  * and the sums run in a fixed order.  KLEOS_E_STATE when the layer was not set up for training. */
 int kleos_gate_stats(float* mean_prob, float* mean_count, float* loss);
 
+/* Init-time placement planner (host only, needs no GPU and no kleos_initialize): restates the
+ * reference's Decider and expert assignment (os/decider/decider.cuh:37-329, used at start-up in
+ * bootstrap.cuh:170-265).  From a latency / inverse-bandwidth matrix (alpha in ms, beta in ms per
+ * MB, entry [i*world + j] = link i -> j), per-device throughput and the number of experts each
+ * device can hold, it merges devices into expert-parallel groups and assigns the experts of the
+ * asking rank's group to its members in proportion to throughput.
+ *   device_to_group  [world]  representative device of every device's group
+ *   group_ranks      [world]  first group_size entries: devices of rank's group, ascending
+ *   expert_to_member [E]      index into group_ranks of the device that holds each expert
+ * Output pointers may be NULL.  matches_data_path is 1 when the plan is the even contiguous
+ * sharding over all ranks that kleos_initialize implements (the case of one NVSwitch node with
+ * identical GPUs); other plans are reported but not executed by this library. */
+typedef struct kleos_placement_request {
+    int32_t world, rank, num_experts, expert_cost, is_training;
+    uint32_t moe_stages, p2p_buffer_mb, grad_buffer_mb; /* see kleos_placement_model */
+    const float* alpha;  /* [world*world] */
+    const float* beta;   /* [world*world] */
+    const float* rate;   /* [world] expert cost units per ms */
+    const uint32_t* mem; /* [world] experts that fit */
+} kleos_placement_request;
+
+typedef struct kleos_placement_result {
+    int32_t feasible, group_size, group_rank, local_experts, expert_slots, widest_group;
+    int32_t matches_data_path;
+} kleos_placement_result;
+
+int kleos_plan_placement(const kleos_placement_request* request, kleos_placement_result* result,
+                         uint32_t* device_to_group, uint32_t* group_ranks, uint32_t* expert_to_member);
+
+/* The three cost-model constants the reference derives from the compiled layer
+ * (types.cuh:487-494): global MoE stages, and the dispatch and gradient buffers in MB. */
+int kleos_placement_model(const char* config_json_path, uint32_t* moe_stages, uint32_t* p2p_buffer_mb,
+                          uint32_t* grad_buffer_mb);
+
 /* Test hook for the failure path: while on, the expert FFN does not raise its "results
  * returned" flags, so the combine's bounded wait runs out, the forward records
  * {KLEOS_E_DEVICE, KLEOS_AT_COMBINE_WAIT} and returns with the context intact.  Nothing is
