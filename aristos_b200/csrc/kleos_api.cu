@@ -19,6 +19,8 @@
 #include <type_traits>
 #include <vector>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "config.hpp"
 #include "gemm_simt.cuh"
 #include "gemm_tc.cuh"
@@ -106,6 +108,43 @@ struct State {
     cudaEvent_t ev[kPhases + 1] = {};
     float phase_ms[kPhases] = {};
     std::string last_error;
+};
+
+// Scoped NVTX range in the domain "Kleos", the domain the reference uses for its ranges around
+// initialisation, forward and finalisation (telemetry.cuh:17-20, bootstrap.cuh:534-536,563-565,
+// moe/moe.cuh:149-151,188-190).  The reference compiles them in with KLEOS_NVTX; here the
+// environment variable KLEOS_NVTX=1 turns them on when the first entry point runs, and nothing
+// of NVTX is touched otherwise.
+class TraceRange {
+public:
+    explicit TraceRange(const char* name) : on_(enabled()) {
+        if (!on_) return;
+        nvtxEventAttributes_t a{};
+        a.version = NVTX_VERSION;
+        a.size = NVTX_EVENT_ATTRIB_STRUCT_SIZE;
+        a.messageType = NVTX_MESSAGE_TYPE_ASCII;
+        a.message.ascii = name;
+        nvtxDomainRangePushEx(domain(), &a);
+    }
+    ~TraceRange() {
+        if (on_) nvtxDomainRangePop(domain());
+    }
+    TraceRange(const TraceRange&) = delete;
+    TraceRange& operator=(const TraceRange&) = delete;
+
+private:
+    static bool enabled() {
+        static const bool on = [] {
+            const char* v = std::getenv("KLEOS_NVTX");
+            return v && v[0] == '1';
+        }();
+        return on;
+    }
+    static nvtxDomainHandle_t domain() {
+        static nvtxDomainHandle_t d = nvtxDomainCreateA("Kleos");
+        return d;
+    }
+    bool on_;
 };
 
 State g;
@@ -736,6 +775,7 @@ int kleos_set_device(int device) {
 }
 
 int kleos_initialize(const char* config_json_path, int rank, int world, const void* nccl_id) {
+    TraceRange trace("kleos_initialize");
     if (g.initialised) return fail(KLEOS_E_STATE, "already initialised");
     if (!config_json_path) return fail(KLEOS_E_ARG, "null config path");
     if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world)
@@ -900,11 +940,13 @@ int kleos_set_gate_bias(const float* host_bias, int n) {
 }
 
 int kleos_forward(const void* iP, void* oP, void* stream) {
+    TraceRange trace("kleos_forward");
     cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : cudaStreamPerThread;
     return forward_any(iP, oP, st, false);
 }
 
 int kleos_forward_bench(const void* iP, void* oP, int skip, int trials, float* ms) {
+    TraceRange trace("kleos_forward_bench");
     if (!ms || trials < 1 || skip < 0) return fail(KLEOS_E_ARG, "bad bench arguments");
     cudaStream_t st = cudaStreamPerThread;
     int rc;
@@ -943,6 +985,7 @@ int kleos_forward_bench(const void* iP, void* oP, int skip, int trials, float* m
 }
 
 int kleos_forward_host(const void* host_activations, void* iP, void* oP, void* host_output) {
+    TraceRange trace("kleos_forward_host");
     if (!g.initialised) return fail(KLEOS_E_STATE, "not initialised");
     if (!host_activations || !iP || !oP || !host_output) return fail(KLEOS_E_ARG, "null buffer");
     const LayerConfig& c = g.cfg;
@@ -958,6 +1001,7 @@ int kleos_forward_host(const void* host_activations, void* iP, void* oP, void* h
 }
 
 int kleos_forward_host_async(const void* host_activations, void* iP, void* oP, void* host_output) {
+    TraceRange trace("kleos_forward_host_async");
     if (!g.initialised) return fail(KLEOS_E_STATE, "not initialised");
     if (!host_activations || !iP || !oP || !host_output) return fail(KLEOS_E_ARG, "null buffer");
     int rc = ensure_host_pipe();
@@ -984,6 +1028,7 @@ int kleos_forward_host_async(const void* host_activations, void* iP, void* oP, v
 }
 
 int kleos_host_sync(void) {
+    TraceRange trace("kleos_host_sync");
     if (!g.initialised) return fail(KLEOS_E_STATE, "not initialised");
     if (g.hp.ready) {
         KLEOS_CUDA(cudaStreamSynchronize(g.hp.in));
@@ -1057,6 +1102,7 @@ int kleos_placement_model(const char* config_json_path, uint32_t* moe_stages, ui
 
 int kleos_plan_placement(const kleos_placement_request* rq, kleos_placement_result* res,
                          uint32_t* device_to_group, uint32_t* group_ranks, uint32_t* expert_to_member) {
+    TraceRange trace("kleos_plan_placement");
     if (!rq || !res) return fail(KLEOS_E_ARG, "null argument");
     if (rq->world < 1 || rq->world > 4096 || rq->num_experts < 1 || rq->num_experts > 65535 ||
         rq->expert_cost < 1 || rq->expert_cost > 65535 || !rq->alpha || !rq->beta || !rq->rate || !rq->mem)
@@ -1129,6 +1175,7 @@ int kleos_phase_times(float* ms, int n) {
 }
 
 int kleos_finalize(void) {
+    TraceRange trace("kleos_finalize");
     if (!g.initialised) return fail(KLEOS_E_STATE, "not initialised");
     cudaDeviceSynchronize();
     if (g.world > 1) {

@@ -135,3 +135,26 @@ def test_bad_requests_are_rejected():
         kleos.plan_placement(a, b, [1.0, 1.0], [4, 4], 0, model)
     with pytest.raises(kleos.KleosError):
         kleos.plan_placement(a, b, [1.0, 1.0], [4, 4], 8, model, rank=5)
+
+
+def test_trace_ranges_are_harmless_without_a_profiler(tmp_path):
+    """KLEOS_NVTX=1 wraps the entry points in NVTX ranges (domain "Kleos", as the reference's
+    telemetry.cuh does); with no tool attached the calls must be no-ops.  Runs in a child process
+    because the switch is read once."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = (
+        "import numpy as np\n"
+        "from aristos_b200 import kleos\n"
+        "a = np.full((2, 2), 1e-3, np.float32); b = np.full((2, 2), 1e-2, np.float32)\n"
+        "m = dict(moe_stages=4, p2p_buffer=1, grad_buffer=1)\n"
+        "for _ in range(3):\n"
+        "    r = kleos.plan_placement(a, b, [1.0, 1.0], [8, 8], 8, m)\n"
+        "assert r['feasible'] and r['expert_to_member'] == [0, 0, 0, 0, 1, 1, 1, 1]\n"
+        "print('ok')\n")
+    env = dict(os.environ, KLEOS_NVTX="1", PYTHONPATH=root)
+    out = subprocess.run([sys.executable, "-c", code], env=env, cwd=root, capture_output=True, text=True,
+                         timeout=120)
+    assert out.returncode == 0 and "ok" in out.stdout, out.stderr
