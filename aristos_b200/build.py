@@ -1,4 +1,5 @@
-"""Builds libkleos_b200.so (CUDA kernels + C ABI) in-tree with nvcc for sm_100a."""
+"""Builds libkleos_b200.so (CUDA kernels + C ABI) and the C++ driver kleos_driver in-tree with
+nvcc for sm_100a."""
 from __future__ import annotations
 
 import os
@@ -8,6 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libkleos_b200.so")
+DRIVER = os.path.join(HERE, "kleos_driver")
 SOURCES = ["kleos_api.cu"]
 
 
@@ -35,5 +37,20 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+def build_driver(force: bool = False) -> str:
+    """The stand-alone C++ driver on include/kleos_b200.hpp (host code only; links the library
+    and finds it next to itself at run time)."""
+    build()
+    if not force and os.path.exists(DRIVER) and os.path.getmtime(DRIVER) >= _newest_source_mtime():
+        return DRIVER
+    subprocess.check_call([
+        "nvcc", "-O2", "-std=c++17", "-Wno-deprecated-gpu-targets", "-ccbin", "g++",
+        os.path.join(CSRC, "host_driver.cpp"),
+        "-o", DRIVER, "-L", HERE, "-lkleos_b200", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN",
+    ])
+    return DRIVER
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build_driver(force="--force" in sys.argv))

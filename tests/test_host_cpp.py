@@ -1,0 +1,86 @@
+"""The C++ host mirror (include/kleos_b200.hpp) and the stand-alone driver built on it
+(aristos_b200/csrc/host_driver.cpp, the counterpart of the reference's csrc/main.cu:12-73)."""
+import os
+import re
+import subprocess
+
+import numpy as np
+import pytest
+
+from aristos_b200 import build as kbuild, synth
+from aristos_b200.config import KleosConfig
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def run_driver(cfg: KleosConfig, workdir, packed=None, timeout=300):
+    """Runs kleos_driver in `workdir` on `cfg`.  With `packed` (fp32 values already rounded to the
+    element type) it performs one forward on that image and returns the packed output decoded
+    to fp32; without it returns the process result of a timed run."""
+    driver = kbuild.build_driver()
+    cfg.to_json(os.path.join(workdir, "kleos_config.json"))
+    env = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "KLEOS_CONFIG")}
+    if packed is None:
+        return subprocess.run([driver], cwd=workdir, env=env, capture_output=True, text=True, timeout=timeout)
+    src, dst = os.path.join(workdir, "in.bin"), os.path.join(workdir, "out.bin")
+    synth.encode(packed, cfg.torch_dtype).tofile(src)
+    res = subprocess.run([driver, "--io", src, dst], cwd=workdir, env=env, capture_output=True, text=True,
+                         timeout=timeout)
+    assert res.returncode == 0, res.stderr
+    raw = np.fromfile(dst, dtype=np.float32 if cfg.elem_bytes == 4 else np.uint16)
+    return synth.decode(raw, cfg.torch_dtype)
+
+
+def test_header_compiles_on_its_own(tmp_path):
+    src = tmp_path / "t.cpp"
+    src.write_text('#include "kleos_b200.hpp"\n'
+                   'int main() { kleos::Launch l = kleos::launchFromEnv(); return l.world > 0 ? 0 : 1; }\n')
+    subprocess.check_call(["g++", "-std=c++17", "-Wall", "-Wextra", "-Werror", "-fsyntax-only",
+                           "-I", os.path.join(ROOT, "include"), str(src)])
+
+
+def test_driver_fails_loudly_without_a_layer_or_a_gpu(tmp_path):
+    driver = kbuild.build_driver()
+    res = subprocess.run([driver], cwd=tmp_path, capture_output=True, text=True, timeout=120)
+    assert res.returncode == 1 and "kleos_config.json" in res.stderr
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("the second half needs a machine without a GPU")
+    res = run_driver(KleosConfig(sequence_len=128, hidden_size=64, intermediate_size=64, num_experts=4),
+                     str(tmp_path))
+    assert res.returncode == 1 and "no CUDA device" in res.stderr
+
+
+def test_driver_rejects_unknown_arguments(tmp_path):
+    driver = kbuild.build_driver()
+    res = subprocess.run([driver, "--what"], cwd=tmp_path, capture_output=True, text=True, timeout=120)
+    assert res.returncode == 2 and "usage" in res.stderr
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [2, 0])
+def test_driver_forward_matches_the_oracle(tmp_path, dtype):
+    """One forward through the C++ mirror (kleos::initialize, moe::forwardHost, kleos::finalize)
+    on a seeded packed input, compared with the oracle like every other parity case."""
+    from oracle import moe_oracle
+    from tests import moe_harness as hz
+    cfg = KleosConfig(sequence_len=256, hidden_size=512, intermediate_size=1024, num_experts=8,
+                      torch_dtype=dtype)
+    packed, views = hz.make_inputs(cfg, 1, bias_scale=0.5)
+    ref = moe_oracle.moe_forward(cfg, 1, views)[0]
+    o = run_driver(cfg, str(tmp_path), packed[0])
+    probs = o[: cfg.S * cfg.PX].reshape(cfg.S, cfg.PX)
+    out = o[cfg.S * cfg.PX:].reshape(cfg.S, cfg.H)
+    assert np.abs(probs - ref["probs"]).max() <= hz.PROB_TOL[dtype]
+    err = np.abs(out - ref["out"]).max() / np.abs(ref["out"]).max()
+    assert err <= hz.TOL[dtype], f"driver output error {err}"
+
+
+@pytest.mark.gpu
+def test_driver_timed_run_prints_the_reference_line(tmp_path):
+    """Timed mode: the line the reference's driver prints (csrc/main.cu:69)."""
+    cfg = KleosConfig(sequence_len=256, hidden_size=512, intermediate_size=1024, num_experts=8)
+    res = run_driver(cfg, str(tmp_path))
+    assert res.returncode == 0, res.stderr
+    m = re.search(r"epRank: 0 took ([0-9.]+)ms", res.stdout)
+    assert m and 0.0 < float(m.group(1)) < 50.0, res.stdout
