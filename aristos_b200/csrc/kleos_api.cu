@@ -62,6 +62,8 @@ struct State {
     bool suppress_return_flag = false;  // test hook: see kleos_debug_suppress_return_flag
     bool use_pair = true;
     bool use_fused = false; // experimental: dispatch + plan inside the GEMM1 kernel (KLEOS_FUSED=1)
+    bool use_overlap = false; // experimental: flagged dispatch on the copy stream beside a GEMM1 that
+                              // plans in its prologue and waits per cell (KLEOS_OVERLAP=1)
     int dispatch_ctas = 16; // blocks of the fused kernel that only move tokens (KLEOS_DISPATCH_CTAS)
     int pipe_parts = 1;     // dispatch / GEMM1 software pipeline over groups of local experts (KLEOS_PIPE)
     cudaStream_t copy_stream = nullptr;
@@ -475,7 +477,8 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed, const S
         gate_stats_kernel<<<1, 256, 0, st>>>(g.col_partial, route_blocks, c.PX, g.counts, c.S, c.E, g.gate_stats);
     KLEOS_CUDA(mark());
 
-    const bool fused = g.use_tc && g.use_pair && g.use_fused;
+    const bool overlap = g.use_tc && g.use_pair && g.use_overlap;
+    const bool fused = (g.use_tc && g.use_pair && g.use_fused) || overlap;
     // Dispatch and GEMM1 are software-pipelined over `parts` groups of local experts: the copy
     // stream moves the rows of group p+1 to their owners while this stream plans and multiplies
     // group p.  Every plan launch waits (on the device, bounded) for the count flags of its
@@ -511,6 +514,16 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed, const S
         plan_kernel<<<1, 1024, 0, st>>>(pa);
         KLEOS_CUDA(mark());
     } else {
+        if (overlap) {
+            // the whole exchange goes to the copy stream; this stream does not wait for it: the
+            // GEMM's loader waits (bounded) for each cell's flag
+            KLEOS_CUDA(cudaEventRecord(g.ev_slots, st));
+            KLEOS_CUDA(cudaStreamWaitEvent(g.copy_stream, g.ev_slots, 0));
+            da.le_begin = 0;
+            da.le_end = g.nLx;
+            dispatch_flow_kernel<<<g.sm_count, 256, 0, g.copy_stream>>>(da, g.cell_done);
+            KLEOS_CUDA(cudaEventRecord(g.ev_part[0], g.copy_stream));
+        }
         KLEOS_CUDA(mark());
         KLEOS_CUDA(mark());
     }
@@ -553,7 +566,7 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed, const S
                 fa.tokens = s.A; fa.cell_tokens = g.cell_tokens; fa.counts = g.counts;
                 fa.cell_done = g.cell_done; fa.panels_out = g.panels; fa.le_start_out = g.le_start;
                 fa.arena = g.arena; fa.E = c.E; fa.EC = c.EC; fa.world = g.world; fa.H = c.H;
-                fa.dispatch_ctas = fused ? g.dispatch_ctas : 0;
+                fa.dispatch_ctas = (fused && !overlap) ? g.dispatch_ctas : 0;
                 if (fused) {
                     const int thr = gemm_tc2::kFusedThreads;
                     if (c.hidden_act == 0)
@@ -571,6 +584,8 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed, const S
                         launch_tc2<T, 1, false>(deep, grid, 256, st, g.map_x, g.map_w1h, g1, fa);
                 }
                 KLEOS_CUDA(mark());
+                // the dispatch kernel has ended by now in practice; make it a stream dependency
+                if (overlap) KLEOS_CUDA(cudaStreamWaitEvent(st, g.ev_part[0], 0));
                 launch_tc2<T, 2, false>(deep, grid, 256, st, g.map_y1, g.map_w2h, g2, fa);
                 KLEOS_CUDA(mark());
             } else {
@@ -874,11 +889,14 @@ int kleos_initialize(const char* config_json_path, int rank, int world, const vo
     }
     if (const char* pr = std::getenv("KLEOS_GEMM_PAIR")) g.use_pair = pr[0] != '0';
     if (const char* fu = std::getenv("KLEOS_FUSED")) g.use_fused = fu[0] != '0';
+    if (const char* ov = std::getenv("KLEOS_OVERLAP")) g.use_overlap = ov[0] != '0';
     if (const char* dc = std::getenv("KLEOS_DISPATCH_CTAS")) g.dispatch_ctas = std::max(2, std::atoi(dc) & ~1);
     // the fused kernel keeps its panel list and per-cell tables in shared memory
     if ((size_t)cfg.E * cfg.pEC / kTileM > (size_t)gemm_tc2::kMaxFusedPanels || cfg.E > 256 || g.nLx > 255 ||
-        cfg.H * 2 > gemm_tc2::kRowBufBytes)
+        cfg.H * 2 > gemm_tc2::kRowBufBytes) {
         g.use_fused = false;
+        g.use_overlap = false;
+    }
 
     for (int r = 0; r < kMaxWorld; ++r) g.peers.arena[r] = nullptr;
     g.peers.arena[rank] = g.arena;

@@ -18,12 +18,12 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _run_world(tmp_path, cfg, world, bias=None, forwards=2, port=29611):
+def _run_world(tmp_path, cfg, world, bias=None, forwards=2, port=29611, extra_env=None):
     spec = dict(cfg=asdict(cfg), forwards=forwards, seed=0,
                 bias=None if bias is None else [float(b) for b in bias])
     sp = tmp_path / "spec.json"
     sp.write_text(json.dumps(spec))
-    env = dict(os.environ, KLEOS_WAIT_MS="2000", NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, KLEOS_WAIT_MS="2000", NCCL_NVLS_ENABLE="0", **(extra_env or {}))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
            f"--nproc-per-node={world}", "--master-addr", "127.0.0.1", "--master-port", str(port),
            os.path.join(ROOT, "tests", "multirank_worker.py"), str(sp), str(tmp_path)]
@@ -60,5 +60,28 @@ def test_expert_parallel_skewed_routing(tmp_path, gpu_count):
     got = _run_world(tmp_path, cfg, world, bias=bias, forwards=3, port=29631)
     for r in range(world):
         assert got[r]["status"][0] == 0
+        routing = {k: got[r][k] for k in ("topk", "slots", "counts", "mcw")}
+        hz.check_against_oracle(cfg, ref[r], got[r]["probs"], got[r]["out"], routing)
+
+
+EXPERIMENTAL = pytest.mark.skipif(os.environ.get("KLEOS_TEST_EXPERIMENTAL") != "1",
+                                  reason="opt-in code paths: set KLEOS_TEST_EXPERIMENTAL=1")
+
+
+@EXPERIMENTAL
+@pytest.mark.parametrize("world", [2, 8])
+def test_overlapped_dispatch_mode(tmp_path, gpu_count, world):
+    """KLEOS_OVERLAP=1: per-cell flagged dispatch on the copy stream beside a GEMM1 that plans in
+    its prologue and waits per cell.  Same results as the default path are required."""
+    if gpu_count < world:
+        pytest.skip(f"needs {world} GPUs")
+    cfg = KleosConfig(sequence_len=512, hidden_size=512, intermediate_size=1024, num_experts=16,
+                      torch_dtype=2)
+    views = [synth.split_packed(cfg, synth.packed_input(cfg, r, world), world) for r in range(world)]
+    ref = moe_oracle.moe_forward(cfg, world, views)
+    got = _run_world(tmp_path, cfg, world, forwards=3, port=29651 + world,
+                     extra_env=dict(KLEOS_OVERLAP="1"))
+    for r in range(world):
+        assert got[r]["status"][0] == 0, f"rank {r} device status {got[r]['status']}"
         routing = {k: got[r][k] for k in ("topk", "slots", "counts", "mcw")}
         hz.check_against_oracle(cfg, ref[r], got[r]["probs"], got[r]["out"], routing)

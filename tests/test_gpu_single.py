@@ -294,3 +294,16 @@ def test_large_baseline_layers_single_gpu_sampled(name):
     ref = c_oracle.moe_forward_rank(cfg, 1, 0, views, gate_bias=bias, tokens=rows)
     probs, out, routing = hz.run_layer_single_gpu(cfg, packed[0], gate_bias=bias)
     hz.check_against_oracle(cfg, ref, probs, out, routing, rows=rows)
+
+
+@pytest.mark.skipif(__import__("os").environ.get("KLEOS_TEST_EXPERIMENTAL") != "1",
+                    reason="opt-in code paths: set KLEOS_TEST_EXPERIMENTAL=1")
+@pytest.mark.parametrize("mode", ["KLEOS_OVERLAP", "KLEOS_FUSED"])
+def test_experimental_dispatch_modes_one_gpu(monkeypatch, mode):
+    """The opt-in dispatch / GEMM1 arrangements must give the default path's results."""
+    monkeypatch.setenv(mode, "1")
+    cfg = _small(2, sequence_len=512, num_experts=16)
+    packed, views = hz.make_inputs(cfg, 1)
+    ref = moe_oracle.moe_forward(cfg, 1, views)[0]
+    probs, out, routing = hz.run_layer_single_gpu(cfg, packed[0], forwards=3)
+    hz.check_against_oracle(cfg, ref, probs, out, routing)
