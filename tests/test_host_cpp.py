@@ -39,6 +39,34 @@ def test_header_compiles_on_its_own(tmp_path):
                            "-I", os.path.join(ROOT, "include"), str(src)])
 
 
+def test_c_abi_header_is_plain_c_and_links(tmp_path):
+    """Foreign-function callers (cgo, JNI, ctypes generators) need the header to be C: compile it
+    as C11 with warnings as errors, then link a C program against the library and call entry
+    points that need no GPU."""
+    src = tmp_path / "t.c"
+    src.write_text(
+        '#include <stdio.h>\n#include <string.h>\n#include "kleos_b200.h"\n'
+        'int main(int argc, char** argv) {\n'
+        '    kleos_layer_info info;\n'
+        '    if (argc != 2) return 2;\n'
+        '    if (kleos_config_probe(argv[1], 8, &info) != KLEOS_OK) return 3;\n'
+        '    if (kleos_get_rank() != KLEOS_E_STATE) return 4;   /* not initialised */\n'
+        '    printf("%d %d %d %lld\\n", info.S, info.EC, info.local_experts, (long long)info.input_elems);\n'
+        '    return strlen(kleos_error_string(KLEOS_E_CONFIG)) > 0 ? 0 : 5;\n'
+        '}\n')
+    exe = tmp_path / "t"
+    libdir = os.path.dirname(kbuild.build())
+    subprocess.check_call(["gcc", "-std=c11", "-Wall", "-Wextra", "-Werror", "-pedantic",
+                           "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe),
+                           "-L", libdir, "-lkleos_b200", f"-Wl,-rpath,{libdir}"])
+    cfg = KleosConfig()   # the reference's shipped layer shape
+    cfg.to_json(str(tmp_path / "kleos_config.json"))
+    out = subprocess.run([str(exe), str(tmp_path / "kleos_config.json")], capture_output=True, text=True,
+                         timeout=120)
+    assert out.returncode == 0, out.stderr
+    assert out.stdout.split() == ["8192", "256", "8", str(cfg.input_elems(8))]
+
+
 def test_driver_fails_loudly_without_a_layer_or_a_gpu(tmp_path):
     driver = kbuild.build_driver()
     res = subprocess.run([driver], cwd=tmp_path, capture_output=True, text=True, timeout=120)
