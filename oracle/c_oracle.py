@@ -57,6 +57,27 @@ def use_all_cores() -> int:
     return num_threads()
 
 
+def gate_stats(cfg, inp, counts, gate_bias=None):
+    """Training-mode gate statistics of one rank; twin of the keys mean_prob / mean_count /
+    gate_loss that moe_oracle.route returns."""
+    L = lib()
+    c = _cfg(cfg, 1)
+    A = np.ascontiguousarray(inp["A"], dtype=np.float32)
+    Wg = np.ascontiguousarray(inp["Wg"], dtype=np.float32)
+    bias = None if gate_bias is None else np.ascontiguousarray(gate_bias, dtype=np.float32)
+    cnt = np.ascontiguousarray(counts, dtype=np.uint32)
+    mp = np.zeros(cfg.E, dtype=np.float64)
+    mc = np.zeros(cfg.E, dtype=np.float64)
+    loss = ctypes.c_double(0)
+    dp = ctypes.POINTER(ctypes.c_double)
+    rc = L.oracle_gate_stats(ctypes.byref(c), _fp(A), _fp(Wg), None if bias is None else _fp(bias),
+                             cnt.ctypes.data_as(ctypes.POINTER(ctypes.c_uint32)),
+                             mp.ctypes.data_as(dp), mc.ctypes.data_as(dp), ctypes.byref(loss))
+    if rc:
+        raise RuntimeError(f"oracle_gate_stats failed: {rc}")
+    return dict(mean_prob=mp, mean_count=mc, gate_loss=loss.value)
+
+
 def dense_ffn(cfg, inp, tokens=None, accum64=True):
     """Single-expert layer (plain FFN) for one rank's tokens; twin of moe_oracle.dense_ffn."""
     L = lib()

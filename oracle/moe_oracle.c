@@ -198,6 +198,41 @@ int oracle_route(const oracle_cfg* c, const float* A, const float* Wg, const flo
     return 0;
 }
 
+/*
+ * Training-mode gate statistics of one source rank (reference moe/gate.cuh:607-635 mean
+ * probability per expert, :698-705 mean unclamped selection count, :763-773 loss):
+ *   mean_prob[e] = (1/S) sum_t p(t,e) over the fp32 softmax probabilities (before rounding),
+ *   mean_count[e] = count[e] / S,   loss = sum_e mean_prob[e] * mean_count[e] / E.
+ * Sums are carried in double; counts come from oracle_route.
+ */
+int oracle_gate_stats(const oracle_cfg* c, const float* A, const float* Wg, const float* bias,
+                      const uint32_t* counts, double* mean_prob, double* mean_count, double* loss) {
+    const int S = c->S, H = c->H, E = c->E;
+    double* logits = (double*)malloc(sizeof(double) * (size_t)S * E);
+    if (!logits) return -1;
+    gemm_nt(S, E, H, A, Wg, NULL, logits, 1);
+    for (int e = 0; e < E; ++e) mean_prob[e] = 0.0;
+    for (int t = 0; t < S; ++t) {
+        double* l = logits + (size_t)t * E;
+        float m = -INFINITY, d = 0.f;
+        for (int e = 0; e < E; ++e) {
+            if (bias) l[e] += (double)bias[e];
+            m = fmaxf(m, (float)l[e]);
+        }
+        for (int e = 0; e < E; ++e) d += expf((float)l[e] - m);
+        for (int e = 0; e < E; ++e) mean_prob[e] += (double)(expf((float)l[e] - m) / d);
+    }
+    double sum = 0.0;
+    for (int e = 0; e < E; ++e) {
+        mean_prob[e] /= (double)S;
+        mean_count[e] = (double)counts[e] / (double)S;
+        sum += mean_prob[e] * mean_count[e];
+    }
+    *loss = sum / (double)E;
+    free(logits);
+    return 0;
+}
+
 static inline double act_fn(double z, int hidden_act) {
     if (hidden_act == 0) return z > 0 ? z : 0;
     return 0.5 * z * (1.0 + erf(z / sqrt(2.0)));

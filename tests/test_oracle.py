@@ -129,3 +129,17 @@ def test_tf32_rounding_is_nearest_even_on_a_ten_bit_mantissa():
     c_oracle.lib().oracle_round(y.ctypes.data_as(__import__("ctypes").POINTER(__import__("ctypes").c_float)),
                                 __import__("ctypes").c_size_t(y.size), 1)
     assert np.array_equal(y, want)
+
+
+@pytest.mark.parametrize("dtype", [0, 2])
+def test_gate_statistics_twins_agree(dtype):
+    cfg = KleosConfig(sequence_len=256, hidden_size=128, intermediate_size=128, num_experts=16,
+                      torch_dtype=dtype, is_training=1)
+    v = synth.split_packed(cfg, synth.packed_input(cfg, 0, 1, seed=9), 1)
+    bias = synth.zipf_gate_bias(cfg, 1.2)
+    a = moe_oracle.route(cfg, v["A"], v["Wg"], bias)
+    b = c_oracle.gate_stats(cfg, v, a["counts"], gate_bias=bias)
+    assert np.abs(a["mean_prob"] - b["mean_prob"]).max() <= 1e-7
+    assert np.array_equal(a["mean_count"], b["mean_count"])
+    assert abs(a["gate_loss"] - b["gate_loss"]) <= 1e-9
+    assert abs(a["mean_prob"].sum() - 1.0) <= 1e-6 and abs(a["mean_count"].sum() - cfg.K) <= 1e-12
