@@ -893,7 +893,7 @@ int kleos_initialize(const char* config_json_path, int rank, int world, const vo
     if (const char* dc = std::getenv("KLEOS_DISPATCH_CTAS")) g.dispatch_ctas = std::max(2, std::atoi(dc) & ~1);
     // the fused kernel keeps its panel list and per-cell tables in shared memory
     if ((size_t)cfg.E * cfg.pEC / kTileM > (size_t)gemm_tc2::kMaxFusedPanels || cfg.E > 256 || g.nLx > 255 ||
-        cfg.H * 2 > gemm_tc2::kRowBufBytes) {
+        cfg.H * 2 > gemm_tc2::kRowBufBytes || cfg.pEC > 65535) {  // 16-bit row counts in shared memory
         g.use_fused = false;
         g.use_overlap = false;
     }
