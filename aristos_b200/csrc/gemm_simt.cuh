@@ -12,7 +12,7 @@ namespace kleos {
 
 template <typename T>
 __global__ void __launch_bounds__(256) ffn_gemm_simt(GemmArgs g) {
-    constexpr int BM = 128, BN = 128, BK = 16, LD = 132;
+    constexpr int BN = 128, BK = 16, LD = 132;  // 128-row panels x 128 columns x 16-deep K steps
     __shared__ __align__(16) float As[BK][LD];
     __shared__ __align__(16) float Bs[BK][LD];
     __shared__ int le_start_s[257];

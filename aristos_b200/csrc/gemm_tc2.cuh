@@ -385,7 +385,6 @@ ffn_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     } else if (warp >= 4 && warp < 8) {
         // ------------------------------------------------------------ epilogue (both blocks)
         const int q = warp - 4;
-        const int row = q * 32 + lane;
         const TE* bias = static_cast<const TE*>(g.bias);
         uint32_t tile_n = 0;
         long long w_accfull = 0, w_tmem = 0;
