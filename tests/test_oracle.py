@@ -143,3 +143,64 @@ def test_gate_statistics_twins_agree(dtype):
     assert np.array_equal(a["mean_count"], b["mean_count"])
     assert abs(a["gate_loss"] - b["gate_loss"]) <= 1e-9
     assert abs(a["mean_prob"].sum() - 1.0) <= 1e-6 and abs(a["mean_count"].sum() - cfg.K) <= 1e-12
+
+
+def _views(cfg, seed=0, world=1, bias_scale=0.0):
+    return [synth.split_packed(cfg, synth.packed_input(cfg, r, world, seed, bias_scale), world)
+            for r in range(world)]
+
+
+@pytest.mark.parametrize("dtype", [0, 2])
+def test_identical_experts_make_the_layer_a_plain_ffn(dtype):
+    """If every expert has the same weights, out[t] = FFN(x[t]) * sum_e p~(t,e) / sum_e p(t,e):
+    with top-k = E and nothing dropped the factor is 1 up to the rounding of the probabilities,
+    so the routed layer must reproduce the dense FFN (a size-independent check of routing,
+    capacity and combine together)."""
+    cfg = KleosConfig(sequence_len=128, hidden_size=64, intermediate_size=128, num_experts=4,
+                      expert_top_k=4, torch_dtype=dtype, drop_tokens=0)
+    v = _views(cfg, seed=2, bias_scale=0.25)[0]
+    for k in ("W1", "W2", "b1", "b2"):
+        v[k] = np.repeat(v[k][:1], cfg.E, axis=0)
+    got = moe_oracle.moe_forward(cfg, 1, [v])[0]
+    assert (got["slots"] >= 0).all()
+    dense = moe_oracle.expert_ffn(cfg, v["A"], v["W1"][0], v["W2"][0], v["b1"][0], v["b2"][0])
+    tol = 1e-5 if dtype == 0 else 3e-2
+    assert np.abs(got["out"] - dense).max() <= tol * np.abs(dense).max()
+    c = c_oracle.moe_forward_rank(cfg, 1, 0, [v])
+    assert np.abs(c["out"] - dense).max() <= tol * np.abs(dense).max()
+
+
+def test_token_order_only_matters_through_capacity():
+    """Without drops the layer is a per-token function: permuting the tokens permutes the rows."""
+    cfg = KleosConfig(sequence_len=128, hidden_size=64, intermediate_size=64, num_experts=8,
+                      torch_dtype=0, drop_tokens=0)
+    v = _views(cfg, seed=4)[0]
+    base = moe_oracle.moe_forward(cfg, 1, [v])[0]
+    perm = np.random.default_rng(0).permutation(cfg.S)
+    pv = dict(v, A=v["A"][perm])
+    moved = moe_oracle.moe_forward(cfg, 1, [pv])[0]
+    assert np.array_equal(np.sort(moved["topk"], axis=1), np.sort(base["topk"][perm], axis=1))
+    assert np.array_equal(moved["counts"], base["counts"])
+    assert np.abs(moved["out"] - base["out"][perm]).max() <= 1e-6 * np.abs(base["out"]).max()
+
+
+@pytest.mark.parametrize("cf", [1, 1.25, 2])
+def test_capacity_bookkeeping_is_consistent(cf):
+    """Per expert: kept rows = min(count, EC), kept slots are 0..kept-1 in ascending token order,
+    and a token's dropped choices still count in the normaliser."""
+    cfg = KleosConfig(sequence_len=256, hidden_size=64, intermediate_size=64, num_experts=8,
+                      torch_dtype=2, capacity_factor=cf)
+    v = _views(cfg, seed=6)[0]
+    bias = synth.zipf_gate_bias(cfg, 1.2) * 2.0
+    for r in (moe_oracle.route(cfg, v["A"], v["Wg"], bias),
+              c_oracle.moe_forward_rank(cfg, 1, 0, [v], gate_bias=bias, tokens=[0])):
+        assert r["counts"].sum() == cfg.S * cfg.K
+        for e in range(cfg.E):
+            hit = r["topk"] == e
+            slots = r["slots"][hit]                      # token-major order
+            kept = slots[slots >= 0]
+            assert len(kept) == min(int(r["counts"][e]), cfg.EC)
+            assert np.array_equal(kept, np.arange(len(kept)))
+            assert (slots[len(kept):] == moe_oracle.DROPPED).all()
+        assert np.array_equal(r["routed"], np.minimum(r["counts"], cfg.EC))
+        assert (r["mcw"] > 0).all() and (r["mcw"] <= 1.0 + 1e-6).all()
