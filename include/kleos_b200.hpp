@@ -85,39 +85,43 @@ inline Launch launchFromEnv() {
     return l;
 }
 
+// Rank 0 creates the 128-byte NCCL id and publishes it in l.id_file (written under another name,
+// then renamed, so that a reader never sees half of it); every other rank polls for the file.
+inline void exchangeId(const Launch& l, unsigned char (&id)[128]) {
+    if (l.rank == 0) {
+        detail::check(kleos_get_unique_id(id), "kleos_get_unique_id");
+        const std::string tmp = l.id_file + ".part";
+        {
+            std::ofstream f(tmp, std::ios::binary | std::ios::trunc);
+            f.write(reinterpret_cast<const char*>(id), sizeof(id));
+        }
+        if (std::rename(tmp.c_str(), l.id_file.c_str()) != 0) {
+            std::fprintf(stderr, "Error: cannot publish the NCCL id at %s\n", l.id_file.c_str());
+            std::exit(1);
+        }
+        detail::id_path() = l.id_file;
+        return;
+    }
+    const auto deadline = std::chrono::steady_clock::now() + std::chrono::seconds(l.id_timeout_s);
+    for (;;) {
+        std::ifstream f(l.id_file, std::ios::binary);
+        if (f && f.read(reinterpret_cast<char*>(id), sizeof(id)) && f.gcount() == (std::streamsize)sizeof(id)) return;
+        if (std::chrono::steady_clock::now() > deadline) {
+            std::fprintf(stderr, "Error: rank %d waited %d s for the NCCL id at %s\n", l.rank,
+                         l.id_timeout_s, l.id_file.c_str());
+            std::exit(1);
+        }
+        std::this_thread::sleep_for(std::chrono::milliseconds(20));
+    }
+}
+
 inline void initialize(const Launch& l) {
     if (detail::initialised()) {
         std::fprintf(stderr, "Error: Already Initialized\n");
         std::quick_exit(EXIT_FAILURE);
     }
     unsigned char id[128] = {};
-    if (l.world > 1) {
-        if (l.rank == 0) {
-            detail::check(kleos_get_unique_id(id), "kleos_get_unique_id");
-            const std::string tmp = l.id_file + ".part";
-            {
-                std::ofstream f(tmp, std::ios::binary | std::ios::trunc);
-                f.write(reinterpret_cast<const char*>(id), sizeof(id));
-            }
-            if (std::rename(tmp.c_str(), l.id_file.c_str()) != 0) {
-                std::fprintf(stderr, "Error: cannot publish the NCCL id at %s\n", l.id_file.c_str());
-                std::exit(1);
-            }
-            detail::id_path() = l.id_file;
-        } else {
-            const auto deadline = std::chrono::steady_clock::now() + std::chrono::seconds(l.id_timeout_s);
-            for (;;) {
-                std::ifstream f(l.id_file, std::ios::binary);
-                if (f && f.read(reinterpret_cast<char*>(id), sizeof(id)) && f.gcount() == (std::streamsize)sizeof(id)) break;
-                if (std::chrono::steady_clock::now() > deadline) {
-                    std::fprintf(stderr, "Error: rank %d waited %d s for the NCCL id at %s\n", l.rank,
-                                 l.id_timeout_s, l.id_file.c_str());
-                    std::exit(1);
-                }
-                std::this_thread::sleep_for(std::chrono::milliseconds(20));
-            }
-        }
-    }
+    if (l.world > 1) exchangeId(l, id);
     detail::check(kleos_initialize(l.config.c_str(), l.rank, l.world, l.world > 1 ? id : nullptr),
                   "kleos_initialize");
     detail::initialised() = true;

@@ -112,3 +112,40 @@ def test_driver_timed_run_prints_the_reference_line(tmp_path):
     assert res.returncode == 0, res.stderr
     m = re.search(r"epRank: 0 took ([0-9.]+)ms", res.stdout)
     assert m and 0.0 < float(m.group(1)) < 50.0, res.stdout
+
+
+def test_id_rendezvous_between_two_ranks(tmp_path):
+    """The C++ mirror hands rank 0's NCCL id to the other ranks through a file.  Two processes
+    (no GPU needed: creating the id only loads NCCL) must end up with the same 128 bytes, and a
+    rank whose rank 0 never shows up must give up with a message."""
+    src = tmp_path / "rv.cpp"
+    src.write_text(
+        '#include <cstdio>\n#include "kleos_b200.hpp"\n'
+        'int main() {\n'
+        '    kleos::Launch l = kleos::launchFromEnv();\n'
+        '    l.id_timeout_s = 3;\n'
+        '    unsigned char id[128] = {};\n'
+        '    kleos::exchangeId(l, id);\n'
+        '    for (unsigned char c : id) std::printf("%02x", c);\n'
+        '    std::printf("\\n");\n'
+        '    return 0;\n'
+        '}\n')
+    exe = tmp_path / "rv"
+    libdir = os.path.dirname(kbuild.build())
+    subprocess.check_call(["g++", "-std=c++17", "-Wall", "-Wextra", "-Werror", "-I", os.path.join(ROOT, "include"),
+                           str(src), "-o", str(exe), "-L", libdir, "-lkleos_b200", f"-Wl,-rpath,{libdir}",
+                           "-pthread"])
+    idf = str(tmp_path / "id")
+    base = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE")}
+    procs = [subprocess.Popen([str(exe)], env=dict(base, RANK=str(r), WORLD_SIZE="2", KLEOS_ID_FILE=idf),
+                              stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+             for r in (1, 0)]   # the reader starts first and has to wait
+    outs = [p.communicate(timeout=120) for p in procs]
+    assert all(p.returncode == 0 for p in procs), [o[1] for o in outs]
+    ids = [o[0].strip() for o in outs]
+    assert len(ids[0]) == 256 and ids[0] == ids[1] and set(ids[0]) != {"0"}
+    # nobody publishes: rank 1 gives up after its timeout
+    lonely = subprocess.run([str(exe)], env=dict(base, RANK="1", WORLD_SIZE="2",
+                                                 KLEOS_ID_FILE=str(tmp_path / "never")),
+                            capture_output=True, text=True, timeout=120)
+    assert lonely.returncode == 1 and "waited 3 s for the NCCL id" in lonely.stderr
