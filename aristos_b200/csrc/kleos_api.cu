@@ -108,6 +108,7 @@ struct State {
 
     ncclComm_t comm = nullptr;
     cudaEvent_t ev[kPhases + 1] = {};
+    cudaEvent_t ev_last = nullptr;  // recorded behind every forward on the caller's stream
     float phase_ms[kPhases] = {};
     std::string last_error;
 };
@@ -210,13 +211,16 @@ int dev_alloc(T** p, size_t count) {
 
 // All-gather `bytes` bytes per rank through a temporary device buffer.
 int all_gather_bytes(const void* mine, void* all, size_t bytes) {
-    char* d = nullptr;
-    KLEOS_CUDA(cudaMalloc(&d, bytes * (g.world + 1)));
-    KLEOS_CUDA(cudaMemcpy(d, mine, bytes, cudaMemcpyHostToDevice));
-    KLEOS_NCCL(nccl.AllGather(d, d + bytes, bytes, ncclChar, g.comm, cudaStreamPerThread));
+    if (!g.comm || !nccl.AllGather) return fail(KLEOS_E_STATE, "ranks are not connected");
+    struct Temp {  // freed on every way out
+        char* p = nullptr;
+        ~Temp() { cudaFree(p); }
+    } d;
+    KLEOS_CUDA(cudaMalloc(&d.p, bytes * (g.world + 1)));
+    KLEOS_CUDA(cudaMemcpy(d.p, mine, bytes, cudaMemcpyHostToDevice));
+    KLEOS_NCCL(nccl.AllGather(d.p, d.p + bytes, bytes, ncclChar, g.comm, cudaStreamPerThread));
     KLEOS_CUDA(cudaStreamSynchronize(cudaStreamPerThread));
-    KLEOS_CUDA(cudaMemcpy(all, d + bytes, bytes * g.world, cudaMemcpyDeviceToHost));
-    KLEOS_CUDA(cudaFree(d));
+    KLEOS_CUDA(cudaMemcpy(all, d.p + bytes, bytes * g.world, cudaMemcpyDeviceToHost));
     return KLEOS_OK;
 }
 
@@ -645,10 +649,23 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed, const S
 int forward_any(const void* iP, void* oP, cudaStream_t st, bool timed, const Staging* stg = nullptr) {
     if (!g.initialised) return fail(KLEOS_E_STATE, "kleos_forward before kleos_initialize");
     if (!iP || !oP) return fail(KLEOS_E_ARG, "null buffer");
-    if (g.cfg.torch_dtype == 0) return forward_typed<float>(iP, oP, st, timed, stg);
-    if (g.cfg.torch_dtype == 1) return forward_typed<tf32_t>(iP, oP, st, timed, stg);
-    if (g.cfg.torch_dtype == 3) return forward_typed<__half>(iP, oP, st, timed, stg);
-    return forward_typed<__nv_bfloat16>(iP, oP, st, timed, stg);
+    int rc;
+    if (g.cfg.torch_dtype == 0) rc = forward_typed<float>(iP, oP, st, timed, stg);
+    else if (g.cfg.torch_dtype == 1) rc = forward_typed<tf32_t>(iP, oP, st, timed, stg);
+    else if (g.cfg.torch_dtype == 3) rc = forward_typed<__half>(iP, oP, st, timed, stg);
+    else rc = forward_typed<__nv_bfloat16>(iP, oP, st, timed, stg);
+    if (rc) return rc;
+    // the status and debug accessors wait for this event: the caller's stream need not be the
+    // per-thread default stream and may be non-blocking
+    KLEOS_CUDA(cudaEventRecord(g.ev_last, st));
+    return KLEOS_OK;
+}
+
+// Waits until the most recent forward has finished, whatever stream it was queued on.
+int sync_last_forward() {
+    KLEOS_CUDA(cudaEventSynchronize(g.ev_last));
+    KLEOS_CUDA(cudaStreamSynchronize(cudaStreamPerThread));
+    return KLEOS_OK;
 }
 
 template <typename TE>
@@ -719,6 +736,7 @@ void release_all() {
         cudaStreamDestroy(g.hp.in); cudaStreamDestroy(g.hp.out);
     }
     if (g.ev_slots) cudaEventDestroy(g.ev_slots);
+    if (g.ev_last) cudaEventDestroy(g.ev_last);
     if (g.copy_stream) cudaStreamDestroy(g.copy_stream);
     if (g.comm && nccl.CommDestroy) nccl.CommDestroy(g.comm);
     g = State();
@@ -789,9 +807,23 @@ int kleos_set_device(int device) {
     return KLEOS_OK;
 }
 
+static int initialize_impl(const char* config_json_path, int rank, int world, const void* nccl_id);
+
 int kleos_initialize(const char* config_json_path, int rank, int world, const void* nccl_id) {
     TraceRange trace("kleos_initialize");
     if (g.initialised) return fail(KLEOS_E_STATE, "already initialised");
+    const int rc = initialize_impl(config_json_path, rank, world, nccl_id);
+    if (rc != KLEOS_OK) {
+        // a failed set-up leaves nothing behind: device buffers, events, streams, peer mappings
+        // and the communicator created so far are released, so the caller may try again
+        const std::string why = g.last_error;
+        release_all();
+        g.last_error = why;
+    }
+    return rc;
+}
+
+static int initialize_impl(const char* config_json_path, int rank, int world, const void* nccl_id) {
     if (!config_json_path) return fail(KLEOS_E_ARG, "null config path");
     if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world)
         return fail(KLEOS_E_ARG, "rank %d / world %d out of range (max world %d)", rank, world, kMaxWorld);
@@ -867,6 +899,7 @@ int kleos_initialize(const char* config_json_path, int rank, int world, const vo
         if ((rc = dev_alloc(&g.gate_stats, (size_t)2 * cfg.E + 1))) return rc;
     }
     for (auto& e : g.ev) KLEOS_CUDA(cudaEventCreate(&e));
+    KLEOS_CUDA(cudaEventCreateWithFlags(&g.ev_last, cudaEventDisableTiming));
     KLEOS_CUDA(cudaStreamCreateWithFlags(&g.copy_stream, cudaStreamNonBlocking));
     KLEOS_CUDA(cudaEventCreateWithFlags(&g.ev_slots, cudaEventDisableTiming));
     for (auto& e : g.ev_part) KLEOS_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
@@ -1073,7 +1106,7 @@ int kleos_get_info(kleos_layer_info* out) {
 int kleos_last_status(kleos_status* out) {
     if (!g.initialised) return fail(KLEOS_E_STATE, "not initialised");
     if (!out) return fail(KLEOS_E_ARG, "null status");
-    KLEOS_CUDA(cudaStreamSynchronize(cudaStreamPerThread));
+    { const int src = sync_last_forward(); if (src) return src; }
     DeviceStatus d;
     KLEOS_CUDA(cudaMemcpy(&d, g.status, sizeof(d), cudaMemcpyDeviceToHost));
     out->code = d.code; out->where = d.where; out->detail = d.detail; out->epoch = d.epoch;
@@ -1082,7 +1115,7 @@ int kleos_last_status(kleos_status* out) {
 
 int kleos_clear_status(void) {
     if (!g.initialised) return fail(KLEOS_E_STATE, "not initialised");
-    KLEOS_CUDA(cudaStreamSynchronize(cudaStreamPerThread));
+    { const int src = sync_last_forward(); if (src) return src; }
     KLEOS_CUDA(cudaMemset(g.status, 0, sizeof(DeviceStatus)));
     return KLEOS_OK;
 }
@@ -1091,7 +1124,7 @@ int kleos_debug_routing(int32_t* topk, int32_t* slots, uint32_t* counts, float* 
     if (!g.initialised) return fail(KLEOS_E_STATE, "not initialised");
     if (g.dense) return fail(KLEOS_E_UNSUPPORTED, "a single-expert layer does no routing");
     const LayerConfig& c = g.cfg;
-    KLEOS_CUDA(cudaStreamSynchronize(cudaStreamPerThread));
+    { const int src = sync_last_forward(); if (src) return src; }
     const size_t sk = (size_t)c.S * c.K;
     if (topk) KLEOS_CUDA(cudaMemcpy(topk, g.topk, sk * 4, cudaMemcpyDeviceToHost));
     if (slots) KLEOS_CUDA(cudaMemcpy(slots, g.slots, sk * 4, cudaMemcpyDeviceToHost));
@@ -1162,7 +1195,7 @@ int kleos_gate_stats(float* mean_prob, float* mean_count, float* loss) {
     if (!g.initialised) return fail(KLEOS_E_STATE, "not initialised");
     if (!g.gate_stats)
         return fail(KLEOS_E_STATE, "gate statistics are kept only when is_training = 1 (and num_experts > 1)");
-    KLEOS_CUDA(cudaStreamSynchronize(cudaStreamPerThread));
+    { const int src = sync_last_forward(); if (src) return src; }
     const int E = g.cfg.E;
     if (mean_prob) KLEOS_CUDA(cudaMemcpy(mean_prob, g.gate_stats, sizeof(float) * E, cudaMemcpyDeviceToHost));
     if (mean_count) KLEOS_CUDA(cudaMemcpy(mean_count, g.gate_stats + E, sizeof(float) * E, cudaMemcpyDeviceToHost));
@@ -1175,7 +1208,7 @@ int kleos_debug_gemm_stats(long long* out, int max_values) {
     if (!g.gemm_stats) return fail(KLEOS_E_STATE, "set KLEOS_GEMM_STATS=1 before kleos_initialize");
     const int n = 2 * g.sm_count * kStatSlots;
     if (!out || max_values < n) return fail(KLEOS_E_ARG, "need room for %d values", n);
-    KLEOS_CUDA(cudaStreamSynchronize(cudaStreamPerThread));
+    { const int src = sync_last_forward(); if (src) return src; }
     KLEOS_CUDA(cudaMemcpy(out, g.gemm_stats, sizeof(long long) * n, cudaMemcpyDeviceToHost));
     return n;
 }
@@ -1196,8 +1229,9 @@ int kleos_finalize(void) {
     TraceRange trace("kleos_finalize");
     if (!g.initialised) return fail(KLEOS_E_STATE, "not initialised");
     cudaDeviceSynchronize();
-    if (g.world > 1) {
-        // nobody unmaps while a peer may still be storing into its cells
+    if (g.world > 1 && g.comm) {
+        // nobody unmaps while a peer may still be storing into its cells (ranks of a dense
+        // layer were never connected: they exchange nothing and have nothing to wait for)
         int token = g.rank, tokens[kMaxWorld];
         all_gather_bytes(&token, tokens, sizeof(int));
     }

@@ -33,7 +33,8 @@ constexpr size_t kOffZeroBias = kOffList + sizeof(int) * kStaticMaxTokens;     /
 constexpr size_t kClearBytes = kOffZeroBias + 256;                             // cleared every call
 constexpr size_t kOffLogits = kClearBytes;                                     // double[S*E]
 constexpr size_t kScratchBytes =
-    kOffLogits + sizeof(double) * kStaticMaxTokens * kStaticMaxExperts;        // 2,130,176 bytes
+    kOffLogits + sizeof(double) * kStaticMaxTokens * kStaticMaxExperts;
+static_assert(kScratchBytes == 2130432, "the size quoted in kleos_b200.h and in the documentation");
 
 // In host code this name is only a handle for cudaGetSymbolAddress, never a device address.
 static __device__ __align__(256) unsigned char g_route_scratch[kScratchBytes];
@@ -52,6 +53,9 @@ extern "C" int kleos_route_static(const void* A, const void* Wg, const float* ga
                                   int32_t* topk, float* mcw, void* stream) {
     using namespace kleos;
     if (!A || !Wg || !probs || !topk || !mcw) return complain(KLEOS_E_ARG, "null device pointer");
+    // the near-tie re-evaluation reads rows of A and Wg sixteen bytes at a time
+    if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(Wg)) & 15)
+        return complain(KLEOS_E_ARG, "A and Wg must be 16-byte aligned");
     if (S < 1 || S > kStaticMaxTokens)
         return complain(KLEOS_E_ARG, "S exceeds the 4096-token limit of the fixed scratch array");
     if (E < 1 || E > kStaticMaxExperts)

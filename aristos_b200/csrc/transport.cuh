@@ -226,7 +226,7 @@ struct PlanArgs {
 // lists the panels grouped by local expert so that tiles sharing a weight tile run together.
 __global__ void __launch_bounds__(1024) plan_kernel(PlanArgs a) {
     __shared__ int failed;
-    __shared__ unsigned short cnt_s[2048];  // world * nLx <= 8 * 256
+    __shared__ int cnt_s[2048];  // world * nLx <= 8 * 256; a count can reach pEC, which has no 16-bit limit
     const int cells = a.world * a.nLx;
     if (threadIdx.x == 0) failed = 0;
     __syncthreads();
@@ -244,7 +244,7 @@ __global__ void __launch_bounds__(1024) plan_kernel(PlanArgs a) {
         } else {
             const unsigned n = min((unsigned)(v & 0xffffffffu), (unsigned)a.pEC);
             a.cell_counts[c] = n;
-            cnt_s[c] = (unsigned short)n;
+            cnt_s[c] = (int)n;
         }
     }
     __syncthreads();

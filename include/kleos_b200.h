@@ -147,11 +147,12 @@ int kleos_debug_gemm_stats(long long* out, int max_values);
 /* Router only, for callers that cannot allocate device memory when they call (inside another
  * runtime's allocator callback, in a serving loop with a frozen memory budget, ...).  It has no
  * counterpart in the reference, which always routes inside its fused kernel.  It needs no
- * kleos_initialize: the scratch it uses (near-tie list, fp64 logits, counters; 2,130,176 bytes)
+ * kleos_initialize: the scratch it uses (near-tie list, fp64 logits, counters; 2,130,432 bytes)
  * is a fixed array inside the library that every GPU loading it keeps until the process ends,
  * and the call performs no cudaMalloc / cudaFree.
  *   A [S,H], Wg [64,H] (row e = expert e, rows >= E zero), gate_bias [E] floats or NULL,
- *   probs [S,64] (element type), topk [S,K], mcw [S]: all DEVICE pointers owned by the caller.
+ *   probs [S,64] (element type), topk [S,K], mcw [S]: all DEVICE pointers owned by the caller;
+ *   A and Wg must be 16-byte aligned (KLEOS_E_ARG otherwise).
  *   Limits: S <= 4096, E <= 64, K <= min(E, 8), H a multiple of 64, torch_dtype 0 or 2; anything
  *   larger is refused with KLEOS_E_ARG and a message on stderr.
  * The first call on each device looks up the array's device address; make that call before any

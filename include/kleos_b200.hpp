@@ -19,17 +19,20 @@
 // nvshmem_init() (bootstrap.cuh:295).  Here rank and world size are read from the launcher's
 // environment (RANK / WORLD_SIZE, OMPI_COMM_WORLD_*, PMI_*, SLURM_*), and the 128-byte NCCL
 // id that rank 0 creates reaches the other ranks of the node through a file (KLEOS_ID_FILE, or
-// a name derived from the launcher's process id in the temporary directory).
+// a name derived from the launcher's port or job id and its process id in the temporary
+// directory).
 #pragma once
 
 #include <chrono>
 #include <cstdio>
 #include <cstdlib>
+#include <ctime>
 #include <fstream>
 #include <initializer_list>
 #include <string>
 #include <thread>
 
+#include <sys/stat.h>
 #include <unistd.h>
 
 #include "kleos_b200.h"
@@ -76,19 +79,30 @@ inline Launch launchFromEnv() {
     if (const char* f = std::getenv("KLEOS_ID_FILE")) {
         l.id_file = f;
     } else {
+        // the launcher's process id is part of the name, so the file a crashed earlier launch
+        // left behind (same port, same job) is never mistaken for this launch's
         const char* tmp = std::getenv("TMPDIR");
         const char* tag = std::getenv("MASTER_PORT");
         if (!tag) tag = std::getenv("SLURM_JOB_ID");
-        l.id_file = std::string(tmp ? tmp : "/tmp") + "/kleos_id_" +
-                    (tag ? std::string(tag) : std::to_string(static_cast<long>(getppid())));
+        l.id_file = std::string(tmp ? tmp : "/tmp") + "/kleos_id_" + (tag ? std::string(tag) + "_" : std::string()) +
+                    std::to_string(static_cast<long>(getppid()));
     }
     return l;
 }
+
+namespace detail {
+// Seconds since the epoch of the file's last modification, or -1 when it does not exist.
+inline long long mtime_of(const std::string& path) {
+    struct stat st;
+    return ::stat(path.c_str(), &st) == 0 ? static_cast<long long>(st.st_mtime) : -1;
+}
+}  // namespace detail
 
 // Rank 0 creates the 128-byte NCCL id and publishes it in l.id_file (written under another name,
 // then renamed, so that a reader never sees half of it); every other rank polls for the file.
 inline void exchangeId(const Launch& l, unsigned char (&id)[128]) {
     if (l.rank == 0) {
+        std::remove(l.id_file.c_str());  // whatever an earlier launch left under this name
         detail::check(kleos_get_unique_id(id), "kleos_get_unique_id");
         const std::string tmp = l.id_file + ".part";
         {
@@ -102,10 +116,16 @@ inline void exchangeId(const Launch& l, unsigned char (&id)[128]) {
         detail::id_path() = l.id_file;
         return;
     }
+    // A file last written well before this process started belongs to an earlier launch (one
+    // that crashed before finalize() removed it): ranks of one launch start within the waiting
+    // time of one another, so anything older than that is ignored until rank 0 replaces it.
+    const long long oldest = static_cast<long long>(std::time(nullptr)) - l.id_timeout_s;
     const auto deadline = std::chrono::steady_clock::now() + std::chrono::seconds(l.id_timeout_s);
     for (;;) {
         std::ifstream f(l.id_file, std::ios::binary);
-        if (f && f.read(reinterpret_cast<char*>(id), sizeof(id)) && f.gcount() == (std::streamsize)sizeof(id)) return;
+        if (f && detail::mtime_of(l.id_file) >= oldest && f.read(reinterpret_cast<char*>(id), sizeof(id)) &&
+            f.gcount() == (std::streamsize)sizeof(id))
+            return;
         if (std::chrono::steady_clock::now() > deadline) {
             std::fprintf(stderr, "Error: rank %d waited %d s for the NCCL id at %s\n", l.rank,
                          l.id_timeout_s, l.id_file.c_str());

@@ -136,3 +136,60 @@ def moe_forward_rank(cfg, world, rank, inputs, gate_bias=None, tokens=None, accu
     return dict(probs=probs, topk=topk, mcw=mcw, slots=slots, counts=counts,
                 routed=np.minimum(counts, cfg.EC).astype(np.uint32), margin=margin.value,
                 out=out)
+
+
+def route_rank(cfg, A, Wg, gate_bias=None):
+    """Routing of one source rank alone (probs, topk, mcw, slots, counts, margin)."""
+    L = lib()
+    c = _cfg(cfg, 1)
+    A = np.ascontiguousarray(A, dtype=np.float32)
+    Wg = np.ascontiguousarray(Wg, dtype=np.float32)
+    bias = None if gate_bias is None else np.ascontiguousarray(gate_bias, dtype=np.float32)
+    probs = np.zeros((cfg.S, cfg.PX), dtype=np.float32)
+    topk = np.zeros((cfg.S, cfg.K), dtype=np.int32)
+    mcw = np.zeros(cfg.S, dtype=np.float32)
+    slots = np.zeros((cfg.S, cfg.K), dtype=np.int32)
+    counts = np.zeros(cfg.E, dtype=np.uint32)
+    margin = ctypes.c_double(0)
+    rc = L.oracle_route(ctypes.byref(c), _fp(A), _fp(Wg), None if bias is None else _fp(bias),
+                        _fp(probs), topk.ctypes.data_as(ctypes.POINTER(ctypes.c_int)), _fp(mcw),
+                        slots.ctypes.data_as(ctypes.POINTER(ctypes.c_int)),
+                        counts.ctypes.data_as(ctypes.POINTER(ctypes.c_uint32)), ctypes.byref(margin))
+    if rc:
+        raise RuntimeError(f"oracle_route failed: {rc}")
+    return dict(probs=probs, topk=topk, mcw=mcw, slots=slots, counts=counts,
+                routed=np.minimum(counts, cfg.EC).astype(np.uint32), margin=margin.value)
+
+
+def moe_forward_rank_lazy(cfg, A, Wg, get_expert, gate_bias=None, tokens=None, accum64=True):
+    """moe_forward_rank for callers that do not hold every expert's weights: routing first, then
+    ``get_expert(e) -> (W1 [I,H], W2 [H,I], b1 [I], b2 [H])`` is asked only for the experts that
+    the listed tokens were routed to (and kept by)."""
+    L = lib()
+    c = _cfg(cfg, 1)
+    rt = route_rank(cfg, A, Wg, gate_bias)
+    tok = np.arange(cfg.S, dtype=np.int32) if tokens is None else np.ascontiguousarray(tokens, dtype=np.int32)
+    used = rt["topk"][tok][rt["slots"][tok] != -1]
+    keep = []
+    arrs = [(ctypes.POINTER(ctypes.c_float) * cfg.E)() for _ in range(4)]
+    for e in sorted(set(int(x) for x in used)):
+        parts = [np.ascontiguousarray(x, dtype=np.float32) for x in get_expert(e)]
+        keep.append(parts)
+        for arr, part in zip(arrs, parts):
+            arr[e] = _fp(part)
+    A = np.ascontiguousarray(A, dtype=np.float32)
+    Wg = np.ascontiguousarray(Wg, dtype=np.float32)
+    bias = None if gate_bias is None else np.ascontiguousarray(gate_bias, dtype=np.float32)
+    out = np.zeros((len(tok), cfg.H), dtype=np.float32)
+    margin = ctypes.c_double(0)
+    rc = L.oracle_moe_forward_rank(
+        ctypes.byref(c), _fp(A), _fp(Wg), *arrs, None if bias is None else _fp(bias),
+        tok.ctypes.data_as(ctypes.POINTER(ctypes.c_int)), ctypes.c_int(len(tok)),
+        ctypes.c_int(1 if accum64 else 0), _fp(rt["probs"]),
+        rt["topk"].ctypes.data_as(ctypes.POINTER(ctypes.c_int)), _fp(rt["mcw"]),
+        rt["slots"].ctypes.data_as(ctypes.POINTER(ctypes.c_int)),
+        rt["counts"].ctypes.data_as(ctypes.POINTER(ctypes.c_uint32)), ctypes.byref(margin), _fp(out))
+    if rc:
+        raise RuntimeError(f"oracle_moe_forward_rank failed: {rc}")
+    rt["out"] = out
+    return rt

@@ -32,13 +32,20 @@ def run_layer_single_gpu(cfg: KleosConfig, packed: np.ndarray, gate_bias=None, f
         oP = torch.zeros(info.output_elems * eb, dtype=torch.uint8, device="cuda")
         if gate_bias is not None:
             kleos.set_gate_bias(gate_bias)
+        # all forwards but the last run on OTHER tokens, so that state left behind by an earlier
+        # forward (cells, result rows, counts, flags) cannot reproduce the expected answer
+        n_act = cfg.S * cfg.H
+        act = np.ascontiguousarray(raw[:n_act])
+        others = [synth.encode(synth.round_to_dtype(synth.activations(cfg, 0, 4242 + i).ravel(),
+                                                    cfg.torch_dtype), cfg.torch_dtype)
+                  for i in range(forwards - 1)]
         if via_host:
-            act = np.ascontiguousarray(raw[: cfg.S * cfg.H])
-            host_out = np.zeros(cfg.S * cfg.H, dtype=raw.dtype)
-            for _ in range(forwards):
-                kleos.forward_from_host(act, iP, oP, host_out)
+            host_out = np.zeros(n_act, dtype=raw.dtype)
+            for a in others + [act]:
+                kleos.forward_from_host(np.ascontiguousarray(a), iP, oP, host_out)
         else:
-            for _ in range(forwards):
+            for a in others + [act]:
+                iP[: n_act * eb].copy_(torch.from_numpy(a.view(np.uint8).copy()))
                 kleos.forward_host(iP, oP)
         st = kleos.last_status()
         assert st.code == 0, f"device status code={st.code} where={st.where} detail={st.detail}"

@@ -1,5 +1,10 @@
 """Expert-parallel parity on 2+ GPUs: every rank's routing and layer output against the CPU
-oracle evaluated on the global problem.  Skipped on boxes with fewer GPUs."""
+oracle evaluated on the global problem.  Skipped on boxes with fewer GPUs.
+
+Every case runs several forwards with DIFFERENT activations per forward (same weights) and
+checks the last one, so a kernel that consumed a dispatched cell, a returned row, a count or a
+flag left over from the forward before cannot pass; one case also lets a rank sleep on the host
+between forwards so that the ranks enter their forwards skewed in time."""
 import json
 import os
 import subprocess
@@ -10,26 +15,50 @@ import numpy as np
 import pytest
 
 from aristos_b200 import synth
-from aristos_b200.config import KleosConfig
-from oracle import moe_oracle
+from aristos_b200.config import KleosConfig, baseline_config
+from oracle import c_oracle, moe_oracle
 from tests import moe_harness as hz
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ACT_SEEDS = [3000, 1000, 2000]  # one per forward; the last one is checked
 
 
-def _run_world(tmp_path, cfg, world, bias=None, forwards=2, port=29611, extra_env=None):
-    spec = dict(cfg=asdict(cfg), forwards=forwards, seed=0,
+def _run_world(tmp_path, cfg, world, bias=None, act_seeds=ACT_SEEDS, port=29611, extra_env=None,
+               rows=None, sleep=None, mode="device", timeout=900):
+    spec = dict(cfg=asdict(cfg), seed=0, act_seeds=list(act_seeds), mode=mode, sleep=sleep,
+                rows=None if rows is None else [int(r) for r in rows],
                 bias=None if bias is None else [float(b) for b in bias])
     sp = tmp_path / "spec.json"
     sp.write_text(json.dumps(spec))
-    env = dict(os.environ, KLEOS_WAIT_MS="2000", NCCL_NVLS_ENABLE="0", **(extra_env or {}))
+    env = dict(os.environ, KLEOS_WAIT_MS="3000", NCCL_NVLS_ENABLE="0", **(extra_env or {}))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
            f"--nproc-per-node={world}", "--master-addr", "127.0.0.1", "--master-port", str(port),
            os.path.join(ROOT, "tests", "multirank_worker.py"), str(sp), str(tmp_path)]
-    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     return [np.load(tmp_path / f"rank{r}.npz") for r in range(world)]
+
+
+def _views(cfg, world, act_seed):
+    """Every rank's packed sections with the weights of seed 0 and the activations of act_seed."""
+    views = []
+    for r in range(world):
+        v = synth.split_packed(cfg, synth.packed_input(cfg, r, world), world)
+        v["A"] = synth.round_to_dtype(synth.activations(cfg, r, act_seed), cfg.torch_dtype)
+        views.append(v)
+    return views
+
+
+def _check_rank(cfg, ref, got, r, rows=None):
+    assert got["status"][0] == 0, f"rank {r} device status {got['status']}"
+    routing = {k: got[k] for k in ("topk", "slots", "counts", "mcw")}
+    out = got["out"]
+    if rows is not None:  # the worker saved only the sampled rows: put them where the checker looks
+        full = np.zeros((cfg.S, cfg.H), dtype=np.float32)
+        full[rows] = out
+        out = full
+    return hz.check_against_oracle(cfg, ref, got["probs"], out, routing, rows=rows)
 
 
 @pytest.mark.parametrize("dtype,world", [(2, 2), (0, 2), (2, 4), (2, 8)])
@@ -38,13 +67,10 @@ def test_expert_parallel_parity(tmp_path, gpu_count, dtype, world):
         pytest.skip(f"needs {world} GPUs")
     cfg = KleosConfig(sequence_len=256, hidden_size=512, intermediate_size=1024, num_experts=8,
                       torch_dtype=dtype)
-    views = [synth.split_packed(cfg, synth.packed_input(cfg, r, world), world) for r in range(world)]
-    ref = moe_oracle.moe_forward(cfg, world, views)
+    ref = moe_oracle.moe_forward(cfg, world, _views(cfg, world, ACT_SEEDS[-1]))
     got = _run_world(tmp_path, cfg, world, port=29611 + world + dtype)
     for r in range(world):
-        assert got[r]["status"][0] == 0, f"rank {r} device status {got[r]['status']}"
-        routing = {k: got[r][k] for k in ("topk", "slots", "counts", "mcw")}
-        hz.check_against_oracle(cfg, ref[r], got[r]["probs"], got[r]["out"], routing)
+        _check_rank(cfg, ref[r], got[r], r)
 
 
 def test_expert_parallel_skewed_routing(tmp_path, gpu_count):
@@ -55,33 +81,51 @@ def test_expert_parallel_skewed_routing(tmp_path, gpu_count):
     cfg = KleosConfig(sequence_len=512, hidden_size=256, intermediate_size=256, num_experts=16,
                       torch_dtype=2, capacity_factor=1.25)
     bias = synth.zipf_gate_bias(cfg, 1.2) * 2.0
-    views = [synth.split_packed(cfg, synth.packed_input(cfg, r, world), world) for r in range(world)]
-    ref = moe_oracle.moe_forward(cfg, world, views, gate_bias=bias)
-    got = _run_world(tmp_path, cfg, world, bias=bias, forwards=3, port=29631)
+    ref = moe_oracle.moe_forward(cfg, world, _views(cfg, world, ACT_SEEDS[-1]), gate_bias=bias)
+    got = _run_world(tmp_path, cfg, world, bias=bias, port=29631)
     for r in range(world):
-        assert got[r]["status"][0] == 0
-        routing = {k: got[r][k] for k in ("topk", "slots", "counts", "mcw")}
-        hz.check_against_oracle(cfg, ref[r], got[r]["probs"], got[r]["out"], routing)
+        _check_rank(cfg, ref[r], got[r], r)
 
 
-EXPERIMENTAL = pytest.mark.skipif(os.environ.get("KLEOS_TEST_EXPERIMENTAL") != "1",
-                                  reason="opt-in code paths: set KLEOS_TEST_EXPERIMENTAL=1")
+@pytest.mark.parametrize("mode", ["device", "host"])
+def test_ranks_skewed_in_time_with_new_tokens_every_forward(tmp_path, gpu_count, mode):
+    """Six forwards, new tokens each time, rank 1 sleeping 5 ms on the host before each of its
+    forwards: rank 0 finishes dispatching forward n+1 while rank 1 has not yet entered it."""
+    world = 2
+    if gpu_count < world:
+        pytest.skip("needs 2 GPUs")
+    cfg = KleosConfig(sequence_len=1024, hidden_size=512, intermediate_size=512, num_experts=16,
+                      torch_dtype=2)
+    seeds = [100, 200, 300, 400, 500, 600]
+    ref = moe_oracle.moe_forward(cfg, world, _views(cfg, world, seeds[-1]))
+    got = _run_world(tmp_path, cfg, world, act_seeds=seeds, port=29641 + (mode == "host"),
+                     sleep=dict(rank=1, ms=5), mode=mode)
+    for r in range(world):
+        _check_rank(cfg, ref[r], got[r], r)
 
 
-@EXPERIMENTAL
-@pytest.mark.parametrize("world", [2, 8])
-def test_overlapped_dispatch_mode(tmp_path, gpu_count, world):
-    """KLEOS_OVERLAP=1: per-cell flagged dispatch on the copy stream beside a GEMM1 that plans in
-    its prologue and waits per cell.  Same results as the default path are required."""
+BASELINE_CASES = [("C3", 2), ("C5", 2), ("C3", 4), ("C5", 4), ("C3", 8), ("C4", 8), ("C5", 8)]
+
+
+@pytest.mark.parametrize("name,world", BASELINE_CASES, ids=[f"{n}-w{w}" for n, w in BASELINE_CASES])
+def test_benchmark_layers_expert_parallel(tmp_path, gpu_count, name, world):
+    """The benchmark layers at the world sizes they are quoted on: routing of every token of
+    every rank bit-exact, layer output of a seeded sample of 64 tokens per rank within the bf16
+    tolerance (the oracle's FFN is evaluated only for the sampled tokens)."""
     if gpu_count < world:
         pytest.skip(f"needs {world} GPUs")
-    cfg = KleosConfig(sequence_len=512, hidden_size=512, intermediate_size=1024, num_experts=16,
-                      torch_dtype=2)
-    views = [synth.split_packed(cfg, synth.packed_input(cfg, r, world), world) for r in range(world)]
-    ref = moe_oracle.moe_forward(cfg, world, views)
-    got = _run_world(tmp_path, cfg, world, forwards=3, port=29651 + world,
-                     extra_env=dict(KLEOS_OVERLAP="1"))
+    cfg, extra = baseline_config(name)
+    bias = synth.zipf_gate_bias(cfg, extra["zipf"]) if extra["zipf"] else None
+    rng = np.random.default_rng(7)
+    rows = np.sort(rng.choice(cfg.S, size=64, replace=False)).astype(np.int32)
+    seeds = ACT_SEEDS[1:]  # two forwards with different tokens
+    got = _run_world(tmp_path, cfg, world, bias=bias, act_seeds=seeds, rows=rows,
+                     port=29700 + 10 * world + int(name[1]), timeout=1500)
+    views = _views(cfg, world, seeds[-1])
+    c_oracle.use_all_cores()
+    worst = 0.0
     for r in range(world):
-        assert got[r]["status"][0] == 0, f"rank {r} device status {got[r]['status']}"
-        routing = {k: got[r][k] for k in ("topk", "slots", "counts", "mcw")}
-        hz.check_against_oracle(cfg, ref[r], got[r]["probs"], got[r]["out"], routing)
+        ref = c_oracle.moe_forward_rank(cfg, world, r, views, gate_bias=bias, tokens=rows)
+        worst = max(worst, _check_rank(cfg, ref, got[r], r, rows=rows))
+    print(f"{name} on {world} GPUs: routing bit-exact on {world * cfg.S} tokens, "
+          f"worst sampled output error {worst:.3e}")

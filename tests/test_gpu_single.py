@@ -307,3 +307,44 @@ def test_experimental_dispatch_modes_one_gpu(monkeypatch, mode):
     ref = moe_oracle.moe_forward(cfg, 1, views)[0]
     probs, out, routing = hz.run_layer_single_gpu(cfg, packed[0], forwards=3)
     hz.check_against_oracle(cfg, ref, probs, out, routing)
+
+
+def test_dense_layer_in_a_multi_rank_launch_needs_no_connection():
+    """num_experts == 1 with world > 1: every rank runs the same FFN on its own tokens, the ranks
+    are never connected (no id is passed), and initialise / forward / finalise work on each of
+    them alone."""
+    import torch
+    from aristos_b200 import kleos
+    cfg = _small(2, num_experts=1, expert_top_k=1, sequence_len=256, hidden_size=128,
+                 intermediate_size=256)
+    packed, views = hz.make_inputs(cfg, 1, bias_scale=0.5)
+    ref = c_oracle.dense_ffn(cfg, views[0])
+    raw = synth.encode(packed[0], 2)
+    for rank in (0, 1):
+        kleos.set_device(0)
+        info = kleos.initialize(cfg, rank, 2, None)
+        try:
+            assert info.world == 2 and info.local_experts == 1
+            iP = torch.from_numpy(raw.view(np.uint8).copy()).cuda()
+            oP = torch.zeros(info.output_elems * 2, dtype=torch.uint8, device="cuda")
+            kleos.forward_host(iP, oP)
+            assert kleos.last_status().code == 0
+            out = synth.decode(oP.cpu().numpy().view(np.uint16), 2).reshape(cfg.S, cfg.H)
+        finally:
+            kleos.finalize()
+        assert np.abs(out - ref).max() / np.abs(ref).max() <= hz.TOL[2]
+
+
+def test_expert_cell_with_more_than_65535_rows():
+    """Two experts, top-1, 131072 tokens: the capacity is 65536 rows per expert and the busier
+    expert fills it, which a 16-bit row count would wrap to zero."""
+    cfg = _small(2, num_experts=2, expert_top_k=1, sequence_len=131072, hidden_size=64,
+                 intermediate_size=64)
+    assert cfg.EC == 65536
+    packed, views = hz.make_inputs(cfg, 1)
+    rng = np.random.default_rng(3)
+    rows = np.sort(rng.choice(cfg.S, size=256, replace=False)).astype(np.int32)
+    ref = c_oracle.moe_forward_rank(cfg, 1, 0, views, tokens=rows)
+    assert ref["routed"].max() == 65536
+    probs, out, routing = hz.run_layer_single_gpu(cfg, packed[0])
+    hz.check_against_oracle(cfg, ref, probs, out, routing, rows=rows)

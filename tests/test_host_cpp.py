@@ -144,6 +144,23 @@ def test_id_rendezvous_between_two_ranks(tmp_path):
     assert all(p.returncode == 0 for p in procs), [o[1] for o in outs]
     ids = [o[0].strip() for o in outs]
     assert len(ids[0]) == 256 and ids[0] == ids[1] and set(ids[0]) != {"0"}
+    # a file that an earlier launch left behind (crashed before finalize) is not this launch's id:
+    # the reader ignores it until rank 0 has replaced it
+    stale = tmp_path / "stale"
+    stale.write_bytes(b"\x55" * 128)
+    old = os.path.getmtime(stale) - 3600
+    os.utime(stale, (old, old))
+    procs = [subprocess.Popen([str(exe)], env=dict(base, RANK=str(r), WORLD_SIZE="2", KLEOS_ID_FILE=str(stale)),
+                              stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+             for r in (1, 0)]
+    outs = [p.communicate(timeout=120) for p in procs]
+    assert all(p.returncode == 0 for p in procs), [o[1] for o in outs]
+    ids = [o[0].strip() for o in outs]
+    assert ids[0] == ids[1] and ids[0] != "55" * 128
+    os.utime(stale, (old, old))   # rank 0 never shows up again: the old file must not satisfy rank 1
+    alone = subprocess.run([str(exe)], env=dict(base, RANK="1", WORLD_SIZE="2", KLEOS_ID_FILE=str(stale)),
+                           capture_output=True, text=True, timeout=120)
+    assert alone.returncode == 1 and "waited 3 s for the NCCL id" in alone.stderr
     # nobody publishes: rank 1 gives up after its timeout
     lonely = subprocess.run([str(exe)], env=dict(base, RANK="1", WORLD_SIZE="2",
                                                  KLEOS_ID_FILE=str(tmp_path / "never")),
