@@ -16,24 +16,10 @@
 //   warp 2      tensor-memory allocation / release (both blocks, cta_group::2 forms)
 //   warps 4..7  epilogue of the block's own 128 accumulator rows; arrives on the LEADER's
 //               `acc_empty`
-// Work and epilogue semantics are those of gemm_tc.cuh (reference
-// os/processor/processor.cuh:350-489,706-741).  Every wait is bounded.
-//
-// kFused (GEMM1 only) folds the token dispatch and the tile plan into the same kernel, which is
-// the reference's arrangement (dispatch blocks, subscriber and processors all live in one
-// launch, moe/moe.cuh:134-143) without its central scheduler:
-//   * every block reads the routed counts that all source ranks have already published
-//     (count flags, raised by the slot kernel) and builds the same panel list in shared memory;
-//   * the last `dispatch_ctas` blocks of the grid do no GEMM work: their "mover" lanes stream
-//     this rank's routed rows into the owner ranks' cells with bulk async copies (global -> a
-//     shared-memory row buffer -> the peer's cell over NVLink), local expert by local expert,
-//     and the mover that completes a cell raises that cell's data flag on the owner.  Movers
-//     placed inside the GEMM blocks were tried first and ran at a third of this speed: their
-//     copies queue behind the operand loads on the same SM's copy engine.  This variant is
-//     slower than the separate dispatch kernel at every world size measured so far and is
-//     therefore opt-in;
-//   * the TMA producer waits (bounded) for the data flag of a panel's cell before its first
-//     load of that cell, so expert GEMMs start while later cells are still in flight on NVLink.
+// Work and epilogue semantics follow the reference's tile worker (os/processor/processor.cuh:
+// 350-489,706-741).  Every wait is bounded.  This kernel runs one GEMM over a finished panel
+// list (the dense single-expert layer, and the routed layer when its phases are launched one
+// by one); the persistent kernel in moe_flow.cuh reuses its tile shapes and pipeline.
 #pragma once
 
 #include <cuda.h>
@@ -51,12 +37,6 @@ constexpr int B_STAGE_BYTES = (BN / 2) * BK * 2;  // 16 KiB: one K slice of this
 constexpr int SLICE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int TMEM_COLS = 512;  // two accumulators of 256 fp32 columns
 constexpr int SMEM_BYTES = kSlices * SLICE_BYTES + 1024 + 28672;
-constexpr int kMaxFusedPanels = 384;
-constexpr int kFusedThreads = 256;
-constexpr int kDispatchUnit = 4;    // consecutive rows of one cell a mover lane copies between two publications
-constexpr int kRowBufBytes = kSlices * SLICE_BYTES;  // a dispatcher block's row buffers: the stage area
-constexpr int kMaxMovers = 48;      // mover lanes per dispatcher block, one row buffer each
-
 
 struct Control {
     unsigned long long full[kSlices];   // used on the leader (one per pipeline stage)
@@ -68,30 +48,9 @@ struct Control {
     int le_start[257];
     __align__(16) float bias_s[4][256];      // bias of the tile being read back, per epilogue warp
     __align__(16) uint4 stage_s[4][32 * 8];  // per epilogue warp: 32 rows x 128 bytes, swizzled
-    // fused GEMM1 only
-    uint2 panel_s[kMaxFusedPanels];          // {row_base, rows | le << 8 | src << 16}
-    unsigned short cnt_s[256];               // routed count per (source, local expert) cell
-    unsigned char ready_s[256];              // producer's memo: data flag of the cell seen
-    unsigned prefix_s[257];                  // dispatch order: prefix of 8-row units over this rank's experts
-    unsigned short own_s[256];               // routed count of this rank's tokens per expert, dispatch order
-    unsigned long long mover_bar[kMaxMovers];  // one per dispatch row buffer
-    unsigned short poff_s[257];              // first panel of each cell, cells in plan order
 };
 
 static_assert(sizeof(Control) <= 28672, "control block must fit the shared memory set aside for it");
-
-// Extra arguments of the fused GEMM1 (dispatch + plan inside the kernel).
-struct FusedArgs {
-    const void* tokens;          // [S,H] this rank's activations
-    const int* cell_tokens;      // [E,pEC] token held by each slot (from the slot kernel)
-    const unsigned* counts;      // [E] unclamped counts of this rank's tokens per expert
-    unsigned* cell_done;         // [E] rows stored so far per expert (zero between forwards)
-    PanelEntry* panels_out;      // panel list for the following GEMM2 launch
-    int* le_start_out;           // [nLx+1]
-    const char* arena;           // this rank's arena (count and data flags arrive here)
-    int E, EC, world, H;
-    int dispatch_ctas;           // blocks at the end of the grid that only dispatch (even number)
-};
 
 struct PairTile {
     int panel0, n_panels_left, nt, le;
@@ -131,10 +90,10 @@ __device__ __forceinline__ int total_pair_tiles(const int* le_start, int le_begi
 // kSub = 64-wide K slices per pipeline stage: 1 gives six shallow stages (best when the weights
 // stream from HBM), 2 gives three deep stages and half the barrier round trips (best when the
 // operands come from L2 and the tensor pipe is the limit).
-template <typename TE, int kEpi, bool kFused, int kSub>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFused ? gemm_tc2::kFusedThreads : 256, 1)
+template <typename TE, int kEpi, int kSub>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(256, 1)
 ffn_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-             GemmArgs g, gemm_tc2::FusedArgs f) {
+             GemmArgs g) {
     using namespace tc;
     using namespace gemm_tc2;
     constexpr int SUB = kSub, STAGES = kSlices / kSub, STAGE_BYTES = kSub * SLICE_BYTES;
@@ -153,15 +112,12 @@ ffn_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     const bool leader = cta_rank == 0;
     volatile int* abort_flag = &ctl->abort;
 
-    if constexpr (!kFused) {
-        for (int i = tid; i <= g.nLx; i += blockDim.x) ctl->le_start[i] = g.le_start[i];
-    }
+    for (int i = tid; i <= g.nLx; i += blockDim.x) ctl->le_start[i] = g.le_start[i];
     if (tid == 0) {
         for (int s = 0; s < NST; ++s) {
             mbar_init(&ctl->full[s], 1);
             mbar_init(&ctl->empty[s], 1);
         }
-        for (int m = 0; m < kMaxMovers; ++m) mbar_init(&ctl->mover_bar[m], 1);
         for (int b = 0; b < 2; ++b) {
             mbar_init(&ctl->acc_full[b], 1);
             mbar_init(&ctl->acc_empty[b], 8);
@@ -169,81 +125,11 @@ ffn_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
         ctl->abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    // fused kernel: the last dispatch_ctas blocks (whole clusters) move tokens, the rest multiply
-    const int n_disp = kFused ? f.dispatch_ctas : 0;
-    const bool dispatcher = kFused && (int)blockIdx.x >= (int)gridDim.x - n_disp;
-    if (warp == 2 && !dispatcher) {
+    if (warp == 2) {
         asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
                      ::"r"(smem_u32(&ctl->tmem_base)), "r"(TMEM_COLS)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-    }
-    if constexpr (kFused) {
-        // plan: routed counts of every (source, local expert) cell, published by the sources'
-        // slot kernels; then the panel list, local expert by local expert, sources in the
-        // order their rows are sent (the source just below this rank first, this rank last)
-        const int cells = f.world * g.nLx;
-        const unsigned long long* cflag =
-            reinterpret_cast<const unsigned long long*>(f.arena + g.lay.cflag);
-        for (int c = tid; c < 256; c += blockDim.x) ctl->ready_s[c] = 0;
-        for (int c = tid; c < cells; c += blockDim.x) {
-            unsigned long long v = 0;
-            if (!wait_flag(cflag + c, g.epoch, g.wait_cycles, &v)) {
-                report_error(g.status, KLEOS_AT_PLAN_WAIT, c, (int)g.epoch);
-                ctl->abort = 1;
-                v = 0;
-            }
-            ctl->cnt_s[c] = (unsigned short)min((unsigned)(v & 0xffffffffu), (unsigned)g.pEC);
-        }
-        // dispatch order of this rank's experts: local expert index first, owners rotated so
-        // that every owner receives the cells of its local expert 0 first
-        for (int i = tid; i < f.E; i += blockDim.x) {
-            const int le = i / f.world, owner = (g.rank + 1 + i % f.world) % f.world;
-            ctl->own_s[i] = (unsigned short)min(f.counts[owner * g.nLx + le], (unsigned)f.EC);
-        }
-        __syncthreads();
-        // two short scans by two different warps, then every cell writes its own panels
-        if (tid == 0) {
-            unsigned run = 0;
-            for (int i = 0; i < f.E; ++i) {
-                ctl->prefix_s[i] = run;
-                run += (ctl->own_s[i] + kDispatchUnit - 1) / kDispatchUnit;
-            }
-            ctl->prefix_s[f.E] = run;
-        } else if (tid == 32) {
-            int n = 0;
-            for (int o = 0; o < cells; ++o) {  // plan order: o = le * world + j
-                const int le = o / f.world, j = o - le * f.world;
-                const int src = (g.rank - 1 - j + 2 * f.world) % f.world;
-                if (j == 0) ctl->le_start[le] = n;
-                ctl->poff_s[o] = (unsigned short)n;
-                n = min(n + (ctl->cnt_s[src * g.nLx + le] + kTileM - 1) / kTileM, kMaxFusedPanels);
-            }
-            ctl->poff_s[cells] = (unsigned short)n;
-            ctl->le_start[g.nLx] = n;
-        }
-        __syncthreads();
-        for (int o = tid; o < cells; o += blockDim.x) {
-            const int le = o / f.world, j = o - le * f.world;
-            const int src = (g.rank - 1 - j + 2 * f.world) % f.world;
-            const int c = src * g.nLx + le;
-            const int cnt = ctl->cnt_s[c];
-            int n = ctl->poff_s[o];
-            for (int r = 0; r < cnt && n < kMaxFusedPanels; r += kTileM)
-                ctl->panel_s[n++] = make_uint2(
-                    (unsigned)(c * g.pEC + r),
-                    (unsigned)min(kTileM, cnt - r) | ((unsigned)le << 8) | ((unsigned)src << 16));
-        }
-        __syncthreads();
-        if (blockIdx.x == 0) {
-            // the following GEMM2 launch reads the same plan from global memory
-            for (int i = tid; i <= g.nLx; i += blockDim.x) f.le_start_out[i] = ctl->le_start[i];
-            for (int i = tid; i < ctl->le_start[g.nLx]; i += blockDim.x) {
-                const uint2 e = ctl->panel_s[i];
-                f.panels_out[i] = PanelEntry{(int)e.x, (int)(e.y & 0xff), (int)((e.y >> 8) & 0xff),
-                                             (int)(e.y >> 16)};
-            }
-        }
     }
     tc_fence_before();
     __syncthreads();
@@ -251,30 +137,20 @@ ffn_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     tc_fence_after();
     const uint32_t tmem_base = ctl->tmem_base;
     if (g.stats && tid == 0) g.stats[blockIdx.x * kStatSlots + 8] = clock64() - t_kernel;
-    // panel lookup: shared memory in the fused kernel, the plan kernel's list otherwise
-    auto panel_at = [&](int i) -> PanelEntry {
-        if constexpr (kFused) {
-            const uint2 e = ctl->panel_s[i];
-            return PanelEntry{(int)e.x, (int)(e.y & 0xff), (int)((e.y >> 8) & 0xff), (int)(e.y >> 16)};
-        } else {
-            return g.panels[i];
-        }
-    };
+    auto panel_at = [&](int i) -> PanelEntry { return g.panels[i]; };
 
     const int NT = (g.N + BN - 1) / BN;
     const int total = total_pair_tiles(ctl->le_start, g.le_begin, g.le_end, NT);
     const int KS = g.Kd / BK;                 // 64-wide K slices
     const int KB = (KS + SUB - 1) / SUB;      // pipeline stages per tile
-    const int n_clusters = ((int)gridDim.x - n_disp) >> 1, cluster_id = blockIdx.x >> 1;
+    const int n_clusters = (int)gridDim.x >> 1, cluster_id = blockIdx.x >> 1;
 
-    if (dispatcher) {
-        // handled below
-    } else if (warp == 0) {
+    if (warp == 0) {
         // ------------------------------------------------------------ TMA producer (both blocks)
         if (lane == 0) {
             asm volatile("fence.proxy.async;" ::: "memory");
             uint32_t it = 0;
-            long long w_empty = 0, w_cell = 0;
+            long long w_empty = 0;
             const long long t_begin = clock64();
             for (int t = cluster_id; t < total && !*abort_flag; t += n_clusters) {
                 PairTile pt;
@@ -283,24 +159,6 @@ ffn_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
                 const int my_panel = pt.panel0 + ((int)cta_rank < pt.n_panels_left ? (int)cta_rank : 0);
                 const PanelEntry p = panel_at(my_panel);
                 const int brow = pt.le * g.N + pt.nt * BN + (int)cta_rank * (BN / 2);
-                if constexpr (kFused) {
-                    // rows of this panel's cell may still be on their way from the source rank
-                    const int cell = p.src * g.nLx + p.le;
-                    if (!ctl->ready_s[cell]) {
-                        const long long tc0 = clock64();
-                        unsigned long long v;
-                        const unsigned long long* xf =
-                            reinterpret_cast<const unsigned long long*>(f.arena + g.lay.xflag) + cell;
-                        if (!wait_flag(xf, g.epoch, g.wait_cycles, &v)) {
-                            report_error(g.status, KLEOS_AT_PLAN_WAIT, 1000 + cell, (int)g.epoch);
-                            *abort_flag = 1;
-                            break;
-                        }
-                        ctl->ready_s[cell] = 1;
-                        w_cell += clock64() - tc0;
-                        asm volatile("fence.proxy.async;" ::: "memory");
-                    }
-                }
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const int s = it % NST;
                     const uint32_t ph = (it / NST) & 1;
@@ -325,7 +183,6 @@ ffn_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
             if (g.stats) {
                 g.stats[blockIdx.x * kStatSlots + 0] = w_empty;
                 g.stats[blockIdx.x * kStatSlots + 1] = clock64() - t_begin;
-                g.stats[blockIdx.x * kStatSlots + 9] = w_cell;
             }
         }
         __syncwarp();
@@ -501,94 +358,12 @@ ffn_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
         }
     }
 
-    if constexpr (kFused) {
-        const int row_bytes = f.H * 2;
-        const int movers = min(kMaxMovers, kRowBufBytes / row_bytes);
-        if (dispatcher && tid < movers && !*abort_flag) {
-            // -------------------------------------------------------- dispatch (dispatcher blocks)
-            // Every mover lane runs its own loop with its own row buffer (in the otherwise unused
-            // stage area) and mbarrier: bulk load of a token row, bulk store into the owner's
-            // cell (reference os/packet.cuh:147-166: unscaled rows, row i of a cell = the token
-            // that owns slot i).  Work comes in units of up to 4 consecutive rows of one cell,
-            // handed out round-robin in sending order, so all movers work on the same local
-            // expert at a time.  A unit is published (system fence + counter) after the NEXT
-            // unit's stores have been issued: its own stores have completed by then, so the
-            // NVLink round trip is not waited for.  The mover that completes a cell raises the
-            // cell's data flag on the owner.
-            uint8_t* buf = tiles + (size_t)tid * row_bytes;
-            unsigned long long* bar = &ctl->mover_bar[tid];
-            uint32_t phase = 0;
-            const int dblock = (int)blockIdx.x - ((int)gridDim.x - n_disp);
-            const unsigned stride = n_disp * movers;
-            const unsigned total_units = ctl->prefix_s[f.E];
-            int pend_e = -1, pend_rows = 0, pend_routed = 0, pend_owner = 0, pend_le = 0;
-            auto publish = [&]() {
-                __threadfence_system();
-                const unsigned prev = atomicAdd(f.cell_done + pend_e, (unsigned)pend_rows);
-                if ((int)prev + pend_rows == pend_routed) {
-                    __threadfence_system();
-                    f.cell_done[pend_e] = 0u;
-                    unsigned long long* xf = reinterpret_cast<unsigned long long*>(
-                        g.peers.arena[pend_owner] + g.lay.xflag) + ((size_t)g.rank * g.nLx + pend_le);
-                    st_release_sys(xf, make_flag(g.epoch, (unsigned)pend_routed));
-                }
-            };
-            bool alive = true;
-            for (unsigned u = dblock * movers + tid; u < total_units && alive; u += stride) {
-                int lo = 0, hi = f.E;
-                while (hi - lo > 1) {
-                    const int mid = (lo + hi) >> 1;
-                    if (ctl->prefix_s[mid] <= u) lo = mid; else hi = mid;
-                }
-                const int le = lo / f.world, owner = (g.rank + 1 + lo % f.world) % f.world;
-                const int e = owner * g.nLx + le;
-                const int routed = ctl->own_s[lo];
-                const int slot0 = (int)(u - ctl->prefix_s[lo]) * kDispatchUnit;
-                const int nrows = min(kDispatchUnit, routed - slot0);
-                int toks[kDispatchUnit];
-#pragma unroll
-                for (int r = 0; r < kDispatchUnit; ++r)
-                    toks[r] = r < nrows ? f.cell_tokens[(size_t)e * g.pEC + slot0 + r] : 0;
-                char* cell = g.peers.arena[owner] + g.lay.xcell +
-                             (((size_t)g.rank * g.nLx + le) * g.pEC + slot0) * row_bytes;
-#pragma unroll
-                for (int r = 0; r < kDispatchUnit; ++r) {
-                    if (r < nrows) {
-                        bulk_store_wait_read();  // the buffer's previous row has left shared memory
-                        mbar_expect_tx(bar, row_bytes);
-                        bulk_load(buf, static_cast<const char*>(f.tokens) + (size_t)toks[r] * row_bytes,
-                                  row_bytes, bar);
-                        if (!mbar_wait(bar, phase, g.wait_cycles, abort_flag)) {
-                            report_error(g.status, KLEOS_AT_GEMM_PRODUCER, 2000 + e, (int)g.epoch);
-                            *abort_flag = 1;
-                            alive = false;
-                            break;
-                        }
-                        phase ^= 1;
-                        bulk_store(cell + (size_t)r * row_bytes, buf, row_bytes);
-                    } else {
-                        bulk_commit_empty();  // four groups per unit, always
-                    }
-                }
-                if (!alive) break;
-                if (pend_e >= 0) {
-                    bulk_store_wait_pending<kDispatchUnit>();  // everything but this unit's stores
-                    publish();
-                }
-                pend_e = e; pend_rows = nrows; pend_routed = routed; pend_owner = owner; pend_le = le;
-            }
-            bulk_store_wait_all();  // nothing in flight when the block leaves
-            if (alive && pend_e >= 0) publish();
-            if (g.stats && tid == 0) g.stats[blockIdx.x * kStatSlots + 10] = clock64() - t_kernel;
-        }
-    }
-
     // teardown: neither block may leave while its partner can still touch its shared memory,
     // barriers or tensor memory
     tc_fence_before();
     __syncthreads();
     cluster_sync_all();
-    if (warp == 2 && !dispatcher) {
+    if (warp == 2) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                      "r"(TMEM_COLS)

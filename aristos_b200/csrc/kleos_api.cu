@@ -23,9 +23,9 @@
 
 #include "config.hpp"
 #include "gemm_simt.cuh"
-#include "gemm_tc.cuh"
 #include "gemm_tc2.cuh"
 #include "gemm_tf32.cuh"
+#include "moe_flow.cuh"
 #include "placement.hpp"
 #include "route.cuh"
 #include "route_tc.cuh"
@@ -60,14 +60,14 @@ struct State {
     // buffers carry no gate weight and no probabilities (moe/fffn.cuh:47-53)
     bool dense = false;
     bool suppress_return_flag = false;  // test hook: see kleos_debug_suppress_return_flag
-    bool use_pair = true;
-    bool use_fused = false; // experimental: dispatch + plan inside the GEMM1 kernel (KLEOS_FUSED=1)
-    bool use_overlap = false; // experimental: flagged dispatch on the copy stream beside a GEMM1 that
-                              // plans in its prologue and waits per cell (KLEOS_OVERLAP=1)
-    int dispatch_ctas = 16; // blocks of the fused kernel that only move tokens (KLEOS_DISPATCH_CTAS)
-    int pipe_parts = 1;     // dispatch / GEMM1 software pipeline over groups of local experts (KLEOS_PIPE)
-    cudaStream_t copy_stream = nullptr;
-    cudaEvent_t ev_slots = nullptr, ev_part[8] = {};  // cta_group::2 GEMM (two blocks per 256x256 tile)
+    // 16-bit routed layers: dispatch, plan, both expert GEMMs and the combine run as ONE persistent
+    // kernel (moe_flow.cuh).  KLEOS_PHASES=1, or a layer beyond the kernel's shared-memory tables,
+    // selects the same work as separate launches (dispatch, plan, GEMM1, GEMM2, combine).
+    bool use_flow = false;
+    int flow_grid = 0;                       // blocks of the persistent kernel (co-resident pairs x 2)
+    flow::Counters* flow_ctr = nullptr;      // [2] scheduler state, see moe_flow.cuh
+    long long* flow_stamps = nullptr;        // [flow_grid][kStampSlots] timeline of a timed forward
+    float flow_ms[flow::kStampSlots] = {};   // last kleos_forward_bench: milestones after kernel start
 
     // symmetric arena
     ArenaLayout lay{};
@@ -85,14 +85,16 @@ struct State {
     // statistics [mean_prob E][mean_count E][loss] of the last forward
     float *col_partial = nullptr, *gate_stats = nullptr;
     unsigned *counts = nullptr, *done_dispatch = nullptr, *done_gemm2 = nullptr,
-             *cell_counts = nullptr, *cell_done = nullptr;
+             *cell_counts = nullptr;
     PanelEntry* panels = nullptr;
     DeviceStatus* status = nullptr;
     long long* gemm_stats = nullptr;  // [2][grid][8] when KLEOS_GEMM_STATS=1
 
     // tensor maps (rebuilt when the caller's weight pointer changes)
     const void* maps_for_iP = nullptr;
-    CUtensorMap map_x{}, map_w1{}, map_y1{}, map_w2{}, map_act{}, map_wg{}, map_w1h{}, map_w2h{};
+    // map_w1 / map_w2: whole 256-row weight tiles (TF32 GEMM); map_w1h / map_w2h: the half tile
+    // each block of a pair loads (16-bit GEMMs)
+    CUtensorMap map_x{}, map_w1{}, map_y1{}, map_w2{}, map_act{}, map_wg{}, map_w1h{}, map_w2h{}, map_wgh{};
 
     // pipelined host-buffer path (kleos_forward_host_async): double-buffered staging of the
     // activations and of the layer output, one stream per direction
@@ -300,16 +302,17 @@ int ensure_maps(const Sections& s) {
         g.maps_for_iP = s.A;
         return KLEOS_OK;
     }
-    if ((rc = make_map(&g.map_x, g.dense ? s.A : g.arena + g.lay.xcell, cell_rows, c.H, gemm_tc::BM))) return rc;
-    if ((rc = make_map(&g.map_w1, s.W1, (uint64_t)g.nLx * c.I, c.H, gemm_tc::BN))) return rc;
-    if ((rc = make_map(&g.map_y1, g.y1, cell_rows, c.I, gemm_tc::BM))) return rc;
-    if ((rc = make_map(&g.map_w2, s.W2, (uint64_t)g.nLx * c.H, c.I, gemm_tc::BN))) return rc;
+    if ((rc = make_map(&g.map_x, g.dense ? s.A : g.arena + g.lay.xcell, cell_rows, c.H, gemm_tc2::BM))) return rc;
+    if ((rc = make_map(&g.map_y1, g.y1, cell_rows, c.I, gemm_tc2::BM))) return rc;
     const int promo = 3;  // 256-byte L2 promotion; 0/64/128 bytes measured the same on the C3 layer
     if ((rc = make_map(&g.map_w1h, s.W1, (uint64_t)g.nLx * c.I, c.H, gemm_tc2::BN / 2, 64, true, promo))) return rc;
     if ((rc = make_map(&g.map_w2h, s.W2, (uint64_t)g.nLx * c.H, c.I, gemm_tc2::BN / 2, 64, true, promo))) return rc;
     if (c.PX <= 128 && !g.dense) {
         if ((rc = make_map(&g.map_act, s.A, c.S, c.H, route_tc::BM))) return rc;
         if ((rc = make_map(&g.map_wg, s.Wg, c.PX, c.H, c.PX))) return rc;
+        // the half of the gate weight each block of a pair loads when the router runs inside the
+        // persistent kernel
+        if ((rc = make_map(&g.map_wgh, s.Wg, c.PX, c.H, c.PX / 2))) return rc;
     }
     g.maps_for_iP = s.A;
     return KLEOS_OK;
@@ -340,13 +343,23 @@ int launch_route(const RouteArgs& ra, cudaStream_t st) {
 
 // The paired GEMM comes in two pipeline shapes (see gemm_tc2.cuh): deep = three 128-wide stages,
 // otherwise six 64-wide stages.
-template <typename TE, int kEpi, bool kFused>
-void launch_tc2(bool deep, int grid, int threads, cudaStream_t st, const CUtensorMap& map_a,
-                const CUtensorMap& map_b, const GemmArgs& ga, const gemm_tc2::FusedArgs& fa) {
+template <typename TE, int kEpi>
+void launch_tc2(bool deep, int grid, cudaStream_t st, const CUtensorMap& map_a, const CUtensorMap& map_b,
+                const GemmArgs& ga) {
     if (deep)
-        ffn_gemm_tc2<TE, kEpi, kFused, 2><<<grid, threads, gemm_tc2::SMEM_BYTES, st>>>(map_a, map_b, ga, fa);
+        ffn_gemm_tc2<TE, kEpi, 2><<<grid, 256, gemm_tc2::SMEM_BYTES, st>>>(map_a, map_b, ga);
     else
-        ffn_gemm_tc2<TE, kEpi, kFused, 1><<<grid, threads, gemm_tc2::SMEM_BYTES, st>>>(map_a, map_b, ga, fa);
+        ffn_gemm_tc2<TE, kEpi, 1><<<grid, 256, gemm_tc2::SMEM_BYTES, st>>>(map_a, map_b, ga);
+}
+
+// The persistent kernel, instantiated per activation and per compile-time top-k of the combine.
+template <typename TE>
+void launch_flow(int act, int K, cudaStream_t st, const flow::Args& fa, const CUtensorMap* fa_act) {
+    const int grid = g.flow_grid, smem = flow::SMEM_BYTES, thr = flow::kThreads;
+    if (act == 0 && K == 2) moe_flow_kernel<TE, 0, 2><<<grid, thr, smem, st>>>(g.map_x, g.map_w1h, g.map_y1, g.map_w2h, *fa_act, g.map_wgh, fa);
+    else if (act == 0) moe_flow_kernel<TE, 0, 0><<<grid, thr, smem, st>>>(g.map_x, g.map_w1h, g.map_y1, g.map_w2h, *fa_act, g.map_wgh, fa);
+    else if (K == 2) moe_flow_kernel<TE, 1, 2><<<grid, thr, smem, st>>>(g.map_x, g.map_w1h, g.map_y1, g.map_w2h, *fa_act, g.map_wgh, fa);
+    else moe_flow_kernel<TE, 1, 0><<<grid, thr, smem, st>>>(g.map_x, g.map_w1h, g.map_y1, g.map_w2h, *fa_act, g.map_wgh, fa);
 }
 
 // TF32 layers: one launch of the kind::tf32 GEMM with the epilogue chosen at compile time.
@@ -390,24 +403,14 @@ int forward_dense(const Sections& s, const CUtensorMap* map_a, cudaStream_t st, 
     g2.hidden_act = 2;  // identity
     if (g.use_tc) {
         if constexpr (sizeof(T) == 2) {
-            if (g.use_pair) {
-                const int grid = g.sm_count & ~1;
-                const bool deep = c.S >= 512;
-                const gemm_tc2::FusedArgs fa{};
-                if (c.hidden_act == 0)
-                    launch_tc2<T, 0, false>(deep, grid, 256, st, *map_a, g.map_w1h, g1, fa);
-                else
-                    launch_tc2<T, 1, false>(deep, grid, 256, st, *map_a, g.map_w1h, g1, fa);
-                KLEOS_CUDA(mark());
-                launch_tc2<T, 2, false>(deep, grid, 256, st, g.map_y1, g.map_w2h, g2, fa);
-            } else {
-                if (c.hidden_act == 0)
-                    ffn_gemm_tc<T, 0><<<g.sm_count, 256, gemm_tc::SMEM_BYTES, st>>>(*map_a, g.map_w1, g1);
-                else
-                    ffn_gemm_tc<T, 1><<<g.sm_count, 256, gemm_tc::SMEM_BYTES, st>>>(*map_a, g.map_w1, g1);
-                KLEOS_CUDA(mark());
-                ffn_gemm_tc<T, 2><<<g.sm_count, 256, gemm_tc::SMEM_BYTES, st>>>(g.map_y1, g.map_w2, g2);
-            }
+            const int grid = g.sm_count & ~1;
+            const bool deep = c.S >= 512;
+            if (c.hidden_act == 0)
+                launch_tc2<T, 0>(deep, grid, st, *map_a, g.map_w1h, g1);
+            else
+                launch_tc2<T, 1>(deep, grid, st, *map_a, g.map_w1h, g1);
+            KLEOS_CUDA(mark());
+            launch_tc2<T, 2>(deep, grid, st, g.map_y1, g.map_w2h, g2);
         }
     } else if (g.use_tf32_tc) {
         launch_tf32(c.hidden_act, st, *map_a, g.map_w1, g1);
@@ -481,56 +484,47 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed, const S
         gate_stats_kernel<<<1, 256, 0, st>>>(g.col_partial, route_blocks, c.PX, g.counts, c.S, c.E, g.gate_stats);
     KLEOS_CUDA(mark());
 
-    const bool overlap = g.use_tc && g.use_pair && g.use_overlap;
-    const bool fused = (g.use_tc && g.use_pair && g.use_fused) || overlap;
-    // Dispatch and GEMM1 are software-pipelined over `parts` groups of local experts: the copy
-    // stream moves the rows of group p+1 to their owners while this stream plans and multiplies
-    // group p.  Every plan launch waits (on the device, bounded) for the count flags of its
-    // group from all source ranks, so there is still no host-side collective.
-    const int parts = fused ? 1 : std::max(1, std::min(std::min(g.pipe_parts, 8), g.nLx));
+    if (g.use_flow) {
+        if constexpr (sizeof(T) == 2) {
+            // 3.-7. one persistent kernel: dispatch, plan, GEMM1, GEMM2, combine
+            flow::Args fa{};
+            fa.tokens = s.A; fa.b1 = s.b1; fa.b2 = s.b2; fa.y1 = g.y1; fa.out = s.out; fa.probs = s.probs;
+            fa.topk = g.topk; fa.slots = g.slots; fa.mcw = g.mcw; fa.cell_tokens = g.cell_tokens;
+            fa.counts = g.counts; fa.peers = g.peers; fa.lay = g.lay; fa.ctr = g.flow_ctr;
+            fa.status = g.status; fa.stamps = timed ? g.flow_stamps : nullptr;
+            fa.wait_cycles = g.wait_cycles; fa.S = c.S; fa.H = c.H; fa.I = c.I; fa.E = c.E; fa.K = c.K;
+            fa.PX = c.PX; fa.EC = c.EC; fa.pEC = c.pEC; fa.nLx = g.nLx; fa.rank = g.rank;
+            fa.world = g.world; fa.epoch = g.epoch; fa.suppress = g.suppress_return_flag ? 1 : 0;
+            // deep stages when an expert sees enough rows for the tensor pipe, not the weight
+            // stream from HBM, to be the limit (about 260 FLOP per weight byte on this part)
+            fa.sub = (long long)g.world * c.EC >= 512 ? 2 : 1;
+            if (timed)
+                KLEOS_CUDA(cudaMemsetAsync(g.flow_stamps, 0,
+                                           sizeof(long long) * g.flow_grid * flow::kStampSlots, st));
+            for (int i = 0; i < 4; ++i) KLEOS_CUDA(mark());  // dispatch .. GEMM2: inside the kernel
+            launch_flow<T>(c.hidden_act, c.K, st, fa, act_map);
+        }
+        KLEOS_CUDA(mark());
+        KLEOS_CUDA(cudaGetLastError());
+        return KLEOS_OK;
+    }
+
+    // 3. dispatch
     DispatchArgs da{};
     da.A = s.A; da.cell_tokens = g.cell_tokens; da.counts = g.counts; da.peers = g.peers;
     da.lay = g.lay; da.done_counter = g.done_dispatch; da.H = c.H; da.E = c.E; da.EC = c.EC;
     da.pEC = c.pEC; da.nLx = g.nLx; da.rank = g.rank; da.world = g.world; da.epoch = g.epoch;
-    da.elem_bytes = c.elem_bytes;
+    da.elem_bytes = c.elem_bytes; da.le_begin = 0; da.le_end = g.nLx;
+    dispatch_kernel<<<g.sm_count * 4, 256, 0, st>>>(da);
+    KLEOS_CUDA(mark());
+    // 4. plan: wait for every source's rows, list the panels
     PlanArgs pa{};
     pa.arena = g.arena; pa.lay = g.lay; pa.panels = g.panels; pa.le_start = g.le_start;
     pa.cell_counts = g.cell_counts; pa.status = g.status; pa.world = g.world; pa.nLx = g.nLx;
     pa.pEC = c.pEC; pa.epoch = g.epoch; pa.wait_cycles = g.wait_cycles; pa.rank = g.rank;
-    if (!fused) {
-        // 3. dispatch, all parts queued on the copy stream behind the slot kernel
-        cudaStream_t cs = parts > 1 ? g.copy_stream : st;
-        if (parts > 1) {
-            KLEOS_CUDA(cudaEventRecord(g.ev_slots, st));
-            KLEOS_CUDA(cudaStreamWaitEvent(cs, g.ev_slots, 0));
-        }
-        for (int p = 0; p < parts; ++p) {
-            da.le_begin = p * g.nLx / parts;
-            da.le_end = (p + 1) * g.nLx / parts;
-            dispatch_kernel<<<g.sm_count * 4, 256, 0, cs>>>(da);
-            if (parts > 1) KLEOS_CUDA(cudaEventRecord(g.ev_part[p], cs));
-        }
-        if (parts > 1) KLEOS_CUDA(cudaStreamWaitEvent(st, g.ev_part[0], 0));
-        KLEOS_CUDA(mark());
-        // 4. plan of the first part: wait for every source's counts, list the panels
-        pa.le_begin = 0;
-        pa.le_end = g.nLx / parts;
-        plan_kernel<<<1, 1024, 0, st>>>(pa);
-        KLEOS_CUDA(mark());
-    } else {
-        if (overlap) {
-            // the whole exchange goes to the copy stream; this stream does not wait for it: the
-            // GEMM's loader waits (bounded) for each cell's flag
-            KLEOS_CUDA(cudaEventRecord(g.ev_slots, st));
-            KLEOS_CUDA(cudaStreamWaitEvent(g.copy_stream, g.ev_slots, 0));
-            da.le_begin = 0;
-            da.le_end = g.nLx;
-            dispatch_flow_kernel<<<g.sm_count, 256, 0, g.copy_stream>>>(da, g.cell_done);
-            KLEOS_CUDA(cudaEventRecord(g.ev_part[0], g.copy_stream));
-        }
-        KLEOS_CUDA(mark());
-        KLEOS_CUDA(mark());
-    }
+    pa.le_begin = 0; pa.le_end = g.nLx;
+    plan_kernel<<<1, 1024, 0, st>>>(pa);
+    KLEOS_CUDA(mark());
 
     // 5./6. expert FFN
     GemmArgs ga{};
@@ -541,89 +535,33 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed, const S
     ga.ret.peers = g.peers; ga.ret.lay = g.lay; ga.ret.done_counter = g.done_gemm2;
     ga.ret.rank = g.rank; ga.ret.world = g.world; ga.ret.epoch = g.epoch;
     ga.ret.suppress = g.suppress_return_flag ? 1 : 0;
-
     GemmArgs g1 = ga;
     g1.A = g.arena + g.lay.xcell; g1.B = s.W1; g1.bias = s.b1; g1.N = c.I; g1.Kd = c.H; g1.mode = 0;
     GemmArgs g2 = ga;
     g2.A = g.y1; g2.B = s.W2; g2.bias = s.b2; g2.N = c.H; g2.Kd = c.I; g2.mode = 1;
-    // before GEMM1 of part p > 0: wait for that part's rows and extend the plan
-    auto next_part = [&](int p) -> int {
-        if (p == 0 || fused) return KLEOS_OK;
-        KLEOS_CUDA(cudaStreamWaitEvent(st, g.ev_part[p], 0));
-        pa.le_begin = p * g.nLx / parts;
-        pa.le_end = (p + 1) * g.nLx / parts;
-        plan_kernel<<<1, 1024, 0, st>>>(pa);
-        return KLEOS_OK;
-    };
     if (g.gemm_stats) {
         g1.stats = g.gemm_stats;
         g2.stats = g.gemm_stats + (size_t)g.sm_count * kStatSlots;
     }
     if (g.use_tc) {
         if constexpr (sizeof(T) == 2) {
-            if (g.use_pair) {
-                const int grid = g.sm_count & ~1;
-                // deep stages when an expert sees enough rows for the tensor pipe, not the weight
-                // stream from HBM, to be the limit (about 260 FLOP per weight byte on this part)
-                const bool deep = (long long)g.world * c.EC >= 512;
-                gemm_tc2::FusedArgs fa{};
-                fa.tokens = s.A; fa.cell_tokens = g.cell_tokens; fa.counts = g.counts;
-                fa.cell_done = g.cell_done; fa.panels_out = g.panels; fa.le_start_out = g.le_start;
-                fa.arena = g.arena; fa.E = c.E; fa.EC = c.EC; fa.world = g.world; fa.H = c.H;
-                fa.dispatch_ctas = (fused && !overlap) ? g.dispatch_ctas : 0;
-                if (fused) {
-                    const int thr = gemm_tc2::kFusedThreads;
-                    if (c.hidden_act == 0)
-                        launch_tc2<T, 0, true>(deep, grid, thr, st, g.map_x, g.map_w1h, g1, fa);
-                    else
-                        launch_tc2<T, 1, true>(deep, grid, thr, st, g.map_x, g.map_w1h, g1, fa);
-                }
-                for (int p = 0; p < parts && !fused; ++p) {
-                    if ((rc = next_part(p))) return rc;
-                    g1.le_begin = p * g.nLx / parts;
-                    g1.le_end = (p + 1) * g.nLx / parts;
-                    if (c.hidden_act == 0)
-                        launch_tc2<T, 0, false>(deep, grid, 256, st, g.map_x, g.map_w1h, g1, fa);
-                    else
-                        launch_tc2<T, 1, false>(deep, grid, 256, st, g.map_x, g.map_w1h, g1, fa);
-                }
-                KLEOS_CUDA(mark());
-                // the dispatch kernel has ended by now in practice; make it a stream dependency
-                if (overlap) KLEOS_CUDA(cudaStreamWaitEvent(st, g.ev_part[0], 0));
-                launch_tc2<T, 2, false>(deep, grid, 256, st, g.map_y1, g.map_w2h, g2, fa);
-                KLEOS_CUDA(mark());
-            } else {
-                for (int p = 0; p < parts; ++p) {
-                    if ((rc = next_part(p))) return rc;
-                    g1.le_begin = p * g.nLx / parts;
-                    g1.le_end = (p + 1) * g.nLx / parts;
-                    if (c.hidden_act == 0)
-                        ffn_gemm_tc<T, 0><<<g.sm_count, 256, gemm_tc::SMEM_BYTES, st>>>(g.map_x, g.map_w1, g1);
-                    else
-                        ffn_gemm_tc<T, 1><<<g.sm_count, 256, gemm_tc::SMEM_BYTES, st>>>(g.map_x, g.map_w1, g1);
-                }
-                KLEOS_CUDA(mark());
-                ffn_gemm_tc<T, 2><<<g.sm_count, 256, gemm_tc::SMEM_BYTES, st>>>(g.map_y1, g.map_w2, g2);
-                KLEOS_CUDA(mark());
-            }
+            const int grid = g.sm_count & ~1;
+            const bool deep = (long long)g.world * c.EC >= 512;
+            if (c.hidden_act == 0)
+                launch_tc2<T, 0>(deep, grid, st, g.map_x, g.map_w1h, g1);
+            else
+                launch_tc2<T, 1>(deep, grid, st, g.map_x, g.map_w1h, g1);
+            KLEOS_CUDA(mark());
+            launch_tc2<T, 2>(deep, grid, st, g.map_y1, g.map_w2h, g2);
+            KLEOS_CUDA(mark());
         }
     } else if (g.use_tf32_tc) {
-        for (int p = 0; p < parts; ++p) {
-            if ((rc = next_part(p))) return rc;
-            g1.le_begin = p * g.nLx / parts;
-            g1.le_end = (p + 1) * g.nLx / parts;
-            launch_tf32(c.hidden_act, st, g.map_x, g.map_w1, g1);
-        }
+        launch_tf32(c.hidden_act, st, g.map_x, g.map_w1, g1);
         KLEOS_CUDA(mark());
         launch_tf32(2, st, g.map_y1, g.map_w2, g2);
         KLEOS_CUDA(mark());
     } else {
-        for (int p = 0; p < parts; ++p) {
-            if ((rc = next_part(p))) return rc;
-            g1.le_begin = p * g.nLx / parts;
-            g1.le_end = (p + 1) * g.nLx / parts;
-            ffn_gemm_simt<T><<<g.sm_count * 2, 256, 0, st>>>(g1);
-        }
+        ffn_gemm_simt<T><<<g.sm_count * 2, 256, 0, st>>>(g1);
         KLEOS_CUDA(mark());
         ffn_gemm_simt<T><<<g.sm_count * 2, 256, 0, st>>>(g2);
         KLEOS_CUDA(mark());
@@ -673,19 +611,32 @@ int set_tc_attributes() {
     const auto dyn = cudaFuncAttributeMaxDynamicSharedMemorySize;
     KLEOS_CUDA(cudaFuncSetAttribute(route_tc_kernel<TE, 64>, dyn, route_tc::Shape<64>::SMEM_BYTES));
     KLEOS_CUDA(cudaFuncSetAttribute(route_tc_kernel<TE, 128>, dyn, route_tc::Shape<128>::SMEM_BYTES));
-    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<TE, 0, false, 1>, dyn, gemm_tc2::SMEM_BYTES));
-    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<TE, 0, false, 2>, dyn, gemm_tc2::SMEM_BYTES));
-    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<TE, 1, false, 1>, dyn, gemm_tc2::SMEM_BYTES));
-    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<TE, 1, false, 2>, dyn, gemm_tc2::SMEM_BYTES));
-    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<TE, 2, false, 1>, dyn, gemm_tc2::SMEM_BYTES));
-    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<TE, 2, false, 2>, dyn, gemm_tc2::SMEM_BYTES));
-    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<TE, 0, true, 1>, dyn, gemm_tc2::SMEM_BYTES));
-    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<TE, 0, true, 2>, dyn, gemm_tc2::SMEM_BYTES));
-    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<TE, 1, true, 1>, dyn, gemm_tc2::SMEM_BYTES));
-    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<TE, 1, true, 2>, dyn, gemm_tc2::SMEM_BYTES));
-    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc<TE, 0>, dyn, gemm_tc::SMEM_BYTES));
-    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc<TE, 1>, dyn, gemm_tc::SMEM_BYTES));
-    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc<TE, 2>, dyn, gemm_tc::SMEM_BYTES));
+    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<TE, 0, 1>, dyn, gemm_tc2::SMEM_BYTES));
+    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<TE, 0, 2>, dyn, gemm_tc2::SMEM_BYTES));
+    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<TE, 1, 1>, dyn, gemm_tc2::SMEM_BYTES));
+    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<TE, 1, 2>, dyn, gemm_tc2::SMEM_BYTES));
+    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<TE, 2, 1>, dyn, gemm_tc2::SMEM_BYTES));
+    KLEOS_CUDA(cudaFuncSetAttribute(ffn_gemm_tc2<TE, 2, 2>, dyn, gemm_tc2::SMEM_BYTES));
+    KLEOS_CUDA(cudaFuncSetAttribute(moe_flow_kernel<TE, 0, 2>, dyn, flow::SMEM_BYTES));
+    KLEOS_CUDA(cudaFuncSetAttribute(moe_flow_kernel<TE, 0, 0>, dyn, flow::SMEM_BYTES));
+    KLEOS_CUDA(cudaFuncSetAttribute(moe_flow_kernel<TE, 1, 2>, dyn, flow::SMEM_BYTES));
+    KLEOS_CUDA(cudaFuncSetAttribute(moe_flow_kernel<TE, 1, 0>, dyn, flow::SMEM_BYTES));
+    // how many block pairs of the persistent kernel the device holds at once: its blocks wait on
+    // one another, so the grid must not exceed that
+    cudaLaunchConfig_t lc{};
+    lc.gridDim = dim3((unsigned)(g.sm_count & ~1));
+    lc.blockDim = dim3(flow::kThreads);
+    lc.dynamicSmemBytes = flow::SMEM_BYTES;
+    cudaLaunchAttribute at{};
+    at.id = cudaLaunchAttributeClusterDimension;
+    at.val.clusterDim.x = 2;
+    at.val.clusterDim.y = 1;
+    at.val.clusterDim.z = 1;
+    lc.attrs = &at;
+    lc.numAttrs = 1;
+    int pairs = 0;
+    KLEOS_CUDA(cudaOccupancyMaxActiveClusters(&pairs, moe_flow_kernel<TE, 0, 2>, &lc));
+    g.flow_grid = 2 * std::min(pairs, g.sm_count / 2);
     return KLEOS_OK;
 }
 
@@ -722,11 +673,9 @@ void release_all() {
     cudaFree(g.y1); cudaFree(g.topk); cudaFree(g.slots); cudaFree(g.cell_tokens);
     cudaFree(g.refine_list); cudaFree(g.refine_count); cudaFree(g.tile_hist); cudaFree(g.refine_done); cudaFree(g.refine_logits); cudaFree(g.le_start); cudaFree(g.mcw);
     cudaFree(g.bias); cudaFree(g.counts); cudaFree(g.done_dispatch); cudaFree(g.done_gemm2);
-    cudaFree(g.cell_counts); cudaFree(g.cell_done); cudaFree(g.panels); cudaFree(g.status); cudaFree(g.gemm_stats);
+    cudaFree(g.cell_counts); cudaFree(g.flow_ctr); cudaFree(g.flow_stamps); cudaFree(g.panels); cudaFree(g.status); cudaFree(g.gemm_stats);
     cudaFree(g.col_partial); cudaFree(g.gate_stats);
     for (auto& e : g.ev)
-        if (e) cudaEventDestroy(e);
-    for (auto& e : g.ev_part)
         if (e) cudaEventDestroy(e);
     if (g.hp.ready) {
         for (int b = 0; b < 2; ++b) {
@@ -735,9 +684,7 @@ void release_all() {
         }
         cudaStreamDestroy(g.hp.in); cudaStreamDestroy(g.hp.out);
     }
-    if (g.ev_slots) cudaEventDestroy(g.ev_slots);
     if (g.ev_last) cudaEventDestroy(g.ev_last);
-    if (g.copy_stream) cudaStreamDestroy(g.copy_stream);
     if (g.comm && nccl.CommDestroy) nccl.CommDestroy(g.comm);
     g = State();
 }
@@ -869,7 +816,8 @@ static int initialize_impl(const char* config_json_path, int rank, int world, co
     g.lay.xflag = align_up(g.lay.ycell + cell_bytes, 1024);
     g.lay.cflag = align_up(g.lay.xflag + (size_t)cfg.E * 8, 1024);
     g.lay.yflag = align_up(g.lay.cflag + (size_t)cfg.E * 8, 1024);
-    g.lay.bytes = align_up(g.lay.yflag + (size_t)kMaxWorld * 8, 1024);
+    g.lay.ypflag = align_up(g.lay.yflag + (size_t)kMaxWorld * 8, 1024);
+    g.lay.bytes = align_up(g.lay.ypflag + (size_t)cfg.E * (cfg.pEC / kTileM) * 8, 1024);
 
     int rc;
     if ((rc = dev_alloc(&g.arena, g.lay.bytes))) return rc;
@@ -891,7 +839,6 @@ static int initialize_impl(const char* config_json_path, int rank, int world, co
     if ((rc = dev_alloc(&g.done_dispatch, 1))) return rc;
     if ((rc = dev_alloc(&g.done_gemm2, 1))) return rc;
     if ((rc = dev_alloc(&g.cell_counts, (size_t)cfg.E))) return rc;
-    if ((rc = dev_alloc(&g.cell_done, (size_t)cfg.E))) return rc;
     if ((rc = dev_alloc(&g.panels, (size_t)cfg.E * cfg.pEC / kTileM))) return rc;
     if ((rc = dev_alloc(&g.status, 1))) return rc;
     if (cfg.is_training && !dense) {
@@ -900,10 +847,6 @@ static int initialize_impl(const char* config_json_path, int rank, int world, co
     }
     for (auto& e : g.ev) KLEOS_CUDA(cudaEventCreate(&e));
     KLEOS_CUDA(cudaEventCreateWithFlags(&g.ev_last, cudaEventDisableTiming));
-    KLEOS_CUDA(cudaStreamCreateWithFlags(&g.copy_stream, cudaStreamNonBlocking));
-    KLEOS_CUDA(cudaEventCreateWithFlags(&g.ev_slots, cudaEventDisableTiming));
-    for (auto& e : g.ev_part) KLEOS_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
-    if (const char* pp = std::getenv("KLEOS_PIPE")) g.pipe_parts = std::max(1, std::atoi(pp));
     if (const char* gs = std::getenv("KLEOS_GEMM_STATS"))
         if (gs[0] == '1' && (rc = dev_alloc(&g.gemm_stats, (size_t)2 * g.sm_count * kStatSlots))) return rc;
 
@@ -920,15 +863,17 @@ static int initialize_impl(const char* config_json_path, int rank, int world, co
         KLEOS_CUDA(cudaFuncSetAttribute(route_tc_kernel<tf32_t, 64>, dyn, route_tc::Shape<64>::SMEM_BYTES));
         KLEOS_CUDA(cudaFuncSetAttribute(route_tc_kernel<tf32_t, 128>, dyn, route_tc::Shape<128>::SMEM_BYTES));
     }
-    if (const char* pr = std::getenv("KLEOS_GEMM_PAIR")) g.use_pair = pr[0] != '0';
-    if (const char* fu = std::getenv("KLEOS_FUSED")) g.use_fused = fu[0] != '0';
-    if (const char* ov = std::getenv("KLEOS_OVERLAP")) g.use_overlap = ov[0] != '0';
-    if (const char* dc = std::getenv("KLEOS_DISPATCH_CTAS")) g.dispatch_ctas = std::max(2, std::atoi(dc) & ~1);
-    // the fused kernel keeps its panel list and per-cell tables in shared memory
-    if ((size_t)cfg.E * cfg.pEC / kTileM > (size_t)gemm_tc2::kMaxFusedPanels || cfg.E > 256 || g.nLx > 255 ||
-        cfg.H * 2 > gemm_tc2::kRowBufBytes || cfg.pEC > 65535) {  // 16-bit row counts in shared memory
-        g.use_fused = false;
-        g.use_overlap = false;
+    // the persistent kernel keeps its panel list and per-cell tables in shared memory; layers
+    // beyond those tables (and KLEOS_PHASES=1, for comparisons) run as separate launches
+    const char* phases = std::getenv("KLEOS_PHASES");
+    g.use_flow = g.use_tc && !dense && !(phases && phases[0] == '1') && g.flow_grid >= 2 &&
+                 (size_t)cfg.E * cfg.pEC / kTileM <= (size_t)flow::kMaxPanels && cfg.E <= flow::kMaxCells &&
+                 g.nLx <= flow::kMaxLocal;
+    if (g.use_flow) {
+        flow::Counters* ctr = nullptr;
+        if ((rc = dev_alloc(&ctr, 2))) return rc;
+        g.flow_ctr = ctr;
+        if ((rc = dev_alloc(&g.flow_stamps, (size_t)g.flow_grid * flow::kStampSlots))) return rc;
     }
 
     for (int r = 0; r < kMaxWorld; ++r) g.peers.arena[r] = nullptr;
@@ -1005,6 +950,8 @@ int kleos_forward_bench(const void* iP, void* oP, int skip, int trials, float* m
         if ((rc = forward_any(iP, oP, st, false))) return rc;
     KLEOS_CUDA(cudaStreamSynchronize(st));
     float acc[kPhases] = {};
+    double macc[flow::kStampSlots] = {};
+    std::vector<long long> stamps;
     // timed trials record per-phase events; the total is first event to last event
     for (int i = 0; i < trials; ++i) {
         if ((rc = forward_any(iP, oP, st, true))) return rc;
@@ -1017,8 +964,36 @@ int kleos_forward_bench(const void* iP, void* oP, int skip, int trials, float* m
         float v = 0;
         KLEOS_CUDA(cudaEventElapsedTime(&v, g.ev[0], g.ev[kPhases - 1]));
         acc[kPhases - 1] += v;
+        if (g.use_flow && !g.dense) {
+            // milestones of the persistent kernel from the blocks' global-timer stamps: the latest
+            // block for each, counted from the earliest block's start (first tile: the earliest)
+            stamps.resize((size_t)g.flow_grid * flow::kStampSlots);
+            KLEOS_CUDA(cudaMemcpy(stamps.data(), g.flow_stamps, stamps.size() * sizeof(long long),
+                                  cudaMemcpyDeviceToHost));
+            long long t0 = 0, hi[flow::kStampSlots] = {}, first_tile = 0;
+            for (int b = 0; b < g.flow_grid; ++b) {
+                const long long* sb = &stamps[(size_t)b * flow::kStampSlots];
+                if (sb[flow::kStart] && (!t0 || sb[flow::kStart] < t0)) t0 = sb[flow::kStart];
+                if (sb[flow::kFirstTile] && (!first_tile || sb[flow::kFirstTile] < first_tile)) first_tile = sb[flow::kFirstTile];
+                for (int k = 0; k < flow::kStampSlots; ++k) hi[k] = std::max(hi[k], sb[k]);
+            }
+            hi[flow::kFirstTile] = first_tile;
+            for (int k = 0; k < flow::kStampSlots; ++k) macc[k] += hi[k] > t0 ? (double)(hi[k] - t0) * 1e-6 : 0.0;
+        }
     }
     for (int p = 0; p < kPhases; ++p) g.phase_ms[p] = acc[p] / trials;
+    if (g.use_flow && !g.dense) {
+        float* m = g.flow_ms;
+        for (int k = 0; k < flow::kStampSlots; ++k) m[k] = (float)(macc[k] / trials);
+        // the per-phase slots, as far as phases still exist inside one kernel: when the last row was
+        // dispatched and the plan was known (both from kernel start), the GEMM1 and GEMM2 spans of the
+        // tile stream, and the tail between the last tile and the end (combine of the last tokens)
+        g.phase_ms[2] = m[flow::kDispatched];
+        g.phase_ms[3] = m[flow::kPlanned];
+        g.phase_ms[4] = m[flow::kLastGemm1] - m[flow::kFirstTile];
+        g.phase_ms[5] = m[flow::kLastTile] - m[flow::kLastGemm1];
+        g.phase_ms[6] = m[flow::kEnd] - m[flow::kLastTile];
+    }
     // back-to-back launches between one pair of events, as the reference times it
     cudaEvent_t a = g.ev[0], b = g.ev[kPhases];
     KLEOS_CUDA(cudaEventRecord(a, st));
@@ -1222,6 +1197,13 @@ int kleos_debug_suppress_return_flag(int on) {
 int kleos_phase_times(float* ms, int n) {
     if (!ms || n < kPhases) return fail(KLEOS_E_ARG, "need room for %d floats", kPhases);
     for (int p = 0; p < kPhases; ++p) ms[p] = g.phase_ms[p];
+    return KLEOS_OK;
+}
+
+int kleos_flow_timeline(float* ms, int n) {
+    if (!ms || n < flow::kStampSlots) return fail(KLEOS_E_ARG, "need room for %d floats", flow::kStampSlots);
+    if (!g.initialised || !g.use_flow) return fail(KLEOS_E_STATE, "this layer does not run the persistent kernel");
+    for (int k = 0; k < flow::kStampSlots; ++k) ms[k] = g.flow_ms[k];
     return KLEOS_OK;
 }
 

@@ -21,6 +21,7 @@ struct ArenaLayout {
     size_t xflag;  // [world*nLx] u64: (epoch<<32)|routed count, raised when the cell's rows are stored
     size_t cflag;  // [world*nLx] u64: (epoch<<32)|routed count, raised as soon as the count is known
     size_t yflag;  // [world] u64: (epoch<<32)|1 when that expert rank has returned everything
+    size_t ypflag; // [E][pEC/128] u64: (epoch<<32)|1 when that 128-row panel of results has arrived
     size_t bytes;
 };
 
@@ -110,93 +111,6 @@ __global__ void __launch_bounds__(256) dispatch_kernel(DispatchArgs a) {
             st_release_sys(f, make_flag(a.epoch, min(a.counts[e], (unsigned)a.EC)));
         }
         if (tid == 0) *a.done_counter = 0u;
-    }
-}
-
-// Dispatch for running BESIDE the first expert GEMM (experimental, KLEOS_OVERLAP=1): same rows,
-// same sending order as dispatch_kernel, but every cell's data flag is raised as soon as that
-// cell's last row has been stored, so the GEMM (whose loader waits per cell) follows the
-// dispatch front local expert by local expert instead of waiting for the whole exchange.
-// Launched with one 256-thread block per SM so that all of it is resident next to the GEMM's
-// blocks (72 registers per thread here plus the GEMM block's 256 x 152 fit one SM's register
-// file; a second block per SM, or 512 threads, would not, and blocks that are not resident would
-// leave their share of the rows for later and stall the GEMM behind them); work
-// comes in units of kFlowUnit consecutive rows of one cell, one unit per warp at a time, and a
-// unit is published with one system fence and one counter update.
-constexpr int kFlowUnit = 4;
-
-__global__ void __launch_bounds__(256) dispatch_flow_kernel(DispatchArgs a, unsigned* cell_done) {
-    __shared__ unsigned prefix[257];        // units before order position i (E <= 256)
-    __shared__ unsigned short rows_s[256];  // routed rows of order position i
-    const int tid = threadIdx.x, lane = tid & 31;
-    for (int i = tid; i < a.E; i += blockDim.x) {
-        const int le = i / a.world, owner = (a.rank + 1 + i % a.world) % a.world;
-        rows_s[i] = (unsigned short)min(a.counts[owner * a.nLx + le], (unsigned)a.EC);
-    }
-    __syncthreads();
-    if (tid == 0) {
-        unsigned run = 0;
-        for (int i = 0; i < a.E; ++i) {
-            prefix[i] = run;
-            run += (rows_s[i] + kFlowUnit - 1) / kFlowUnit;
-        }
-        prefix[a.E] = run;
-    }
-    __syncthreads();
-    // cells without rows: nothing will complete them, so their flags go out first
-    if (blockIdx.x == 0)
-        for (int i = tid; i < a.E; i += blockDim.x)
-            if (rows_s[i] == 0) {
-                const int le = i / a.world, owner = (a.rank + 1 + i % a.world) % a.world;
-                st_release_sys(reinterpret_cast<unsigned long long*>(a.peers.arena[owner] + a.lay.xflag) +
-                                   ((size_t)a.rank * a.nLx + le),
-                               make_flag(a.epoch, 0u));
-            }
-    const unsigned total = prefix[a.E];
-    const unsigned warps = gridDim.x * (blockDim.x >> 5);
-    const unsigned row_chunks = (unsigned)((size_t)a.H * a.elem_bytes / 16);
-    for (unsigned g = blockIdx.x * (blockDim.x >> 5) + (tid >> 5); g < total; g += warps) {
-        int lo = 0, hi = a.E;  // last order position with prefix[] <= g
-        while (hi - lo > 1) {
-            const int mid = (lo + hi) >> 1;
-            if (prefix[mid] <= g) lo = mid; else hi = mid;
-        }
-        const int le = lo / a.world, owner = (a.rank + 1 + lo % a.world) % a.world;
-        const int e = owner * a.nLx + le;
-        const int routed = rows_s[lo];
-        const int slot0 = (int)(g - prefix[lo]) * kFlowUnit;
-        const int nrows = min(kFlowUnit, routed - slot0);
-        for (int r = 0; r < nrows; ++r) {
-            const int tok = a.cell_tokens[(size_t)e * a.pEC + slot0 + r];
-            const uint4* src = reinterpret_cast<const uint4*>(
-                static_cast<const char*>(a.A) + (size_t)tok * a.H * a.elem_bytes);
-            uint4* dst = reinterpret_cast<uint4*>(
-                a.peers.arena[owner] + a.lay.xcell +
-                (((size_t)a.rank * a.nLx + le) * a.pEC + slot0 + r) * a.H * a.elem_bytes);
-            for (unsigned c0 = lane; c0 < row_chunks; c0 += 256) {
-                uint4 v[8];
-#pragma unroll
-                for (int q = 0; q < 8; ++q)
-                    if (c0 + 32 * q < row_chunks) v[q] = __ldg(src + c0 + 32 * q);
-#pragma unroll
-                for (int q = 0; q < 8; ++q)
-                    if (c0 + 32 * q < row_chunks) dst[c0 + 32 * q] = v[q];
-            }
-        }
-        // publish the unit: every lane orders its own stores, lane 0 counts; whoever brings the
-        // cell's count to its total raises the flag on the owner
-        __threadfence_system();
-        __syncwarp();
-        if (lane == 0) {
-            const unsigned prev = atomicAdd(cell_done + e, (unsigned)nrows);
-            if ((int)prev + nrows == routed) {
-                __threadfence_system();
-                cell_done[e] = 0u;  // ready for the next forward
-                st_release_sys(reinterpret_cast<unsigned long long*>(a.peers.arena[owner] + a.lay.xflag) +
-                                   ((size_t)a.rank * a.nLx + le),
-                               make_flag(a.epoch, (unsigned)routed));
-            }
-        }
     }
 }
 

@@ -39,7 +39,8 @@ enum {
     KLEOS_AT_GEMM_PRODUCER = 3, /* TMA producer waiting for a free pipeline stage   */
     KLEOS_AT_GEMM_MMA = 4,      /* MMA issuer waiting for operands or accumulator   */
     KLEOS_AT_GEMM_EPILOGUE = 5, /* epilogue waiting for an accumulator              */
-    KLEOS_AT_BOUNDS = 6         /* an index outside its table                       */
+    KLEOS_AT_BOUNDS = 6,        /* an index outside its table                       */
+    KLEOS_AT_GRID_BARRIER = 7   /* blocks of the persistent kernel waiting for one another */
 };
 
 typedef struct kleos_status {
@@ -135,6 +136,18 @@ int kleos_debug_routing(int32_t* topk, int32_t* slots, uint32_t* counts, float* 
  * its trials: [0] route, [1] slots, [2] dispatch, [3] plan(wait), [4] GEMM1, [5] GEMM2,
  * [6] combine, [7] whole forward.  n = number of floats the caller provides (>= 8). */
 int kleos_phase_times(float* ms, int n);
+
+/* 16-bit routed layers run dispatch, plan, both expert GEMMs and the combine as ONE persistent
+ * kernel (the reference's arrangement, moe/moe.cuh:77-144), so phases [2]..[6] above are then
+ * read from the blocks' global-timer stamps: [2] last row dispatched and [3] tile plan known, both
+ * counted from the kernel's start; [4] span of the GEMM1 tiles; [5] from the last GEMM1 tile to
+ * the last tile; [6] from the last tile to the kernel's end.  This call returns the raw
+ * milestones of the most recent kleos_forward_bench, milliseconds after the earliest block's
+ * start, latest block each: [0] 0, [1] plan known, [2] first tile begins (earliest block),
+ * [3] last GEMM1 tile done, [4] last tile done, [5] last row dispatched, [6] last token combined,
+ * [7] last block ends.  n >= 8.  KLEOS_E_STATE when the layer runs as separate launches
+ * (float and TF32 layers, the dense layer, KLEOS_PHASES=1). */
+int kleos_flow_timeline(float* ms, int n);
 
 /* Stall counters of the last GEMM1 and GEMM2 launches, only when the environment variable
  * KLEOS_GEMM_STATS=1 was set at initialise time: [2][blocks][12] clock cycles per block

@@ -296,17 +296,47 @@ def test_large_baseline_layers_single_gpu_sampled(name):
     hz.check_against_oracle(cfg, ref, probs, out, routing, rows=rows)
 
 
-@pytest.mark.skipif(__import__("os").environ.get("KLEOS_TEST_EXPERIMENTAL") != "1",
-                    reason="opt-in code paths: set KLEOS_TEST_EXPERIMENTAL=1")
-@pytest.mark.parametrize("mode", ["KLEOS_OVERLAP", "KLEOS_FUSED"])
-def test_experimental_dispatch_modes_one_gpu(monkeypatch, mode):
-    """The opt-in dispatch / GEMM1 arrangements must give the default path's results."""
-    monkeypatch.setenv(mode, "1")
-    cfg = _small(2, sequence_len=512, num_experts=16)
-    packed, views = hz.make_inputs(cfg, 1)
+@pytest.mark.parametrize("kw", [
+    dict(sequence_len=512, num_experts=16),
+    dict(num_experts=128, sequence_len=512, hidden_size=256, intermediate_size=320, capacity_factor=1.25,
+         hidden_act=1),
+    dict(num_experts=8, sequence_len=256, hidden_size=256, intermediate_size=512, expert_top_k=4),
+], ids=["e16", "e128-gelu-tail", "top4"])
+def test_separate_launches_give_the_persistent_kernels_results(monkeypatch, kw):
+    """KLEOS_PHASES=1 runs dispatch, plan, GEMM1, GEMM2 and combine as separate launches (the path
+    that layers beyond the persistent kernel's tables take); both arrangements must match the
+    oracle, and each other bit for bit."""
+    cfg = _small(2, **kw)
+    packed, views = hz.make_inputs(cfg, 1, bias_scale=0.5)
     ref = moe_oracle.moe_forward(cfg, 1, views)[0]
-    probs, out, routing = hz.run_layer_single_gpu(cfg, packed[0], forwards=3)
-    hz.check_against_oracle(cfg, ref, probs, out, routing)
+    outs = []
+    for phases in ("0", "1"):
+        monkeypatch.setenv("KLEOS_PHASES", phases)
+        probs, out, routing = hz.run_layer_single_gpu(cfg, packed[0], forwards=3)
+        hz.check_against_oracle(cfg, ref, probs, out, routing)
+        outs.append(out)
+    assert np.array_equal(outs[0], outs[1])
+
+
+def test_persistent_kernel_reports_its_timeline():
+    """kleos_forward_bench on a 16-bit routed layer: the milestones of the one kernel are ordered
+    (plan, first tile, last GEMM1 tile, last tile, end) and lie inside the forward's duration."""
+    import torch
+    from aristos_b200 import kleos
+    cfg = _small(2, sequence_len=1024, num_experts=16)
+    raw = synth.encode(synth.packed_input(cfg, 0, 1), 2)
+    info = kleos.initialize(cfg, 0, 1)
+    try:
+        iP = torch.from_numpy(raw.view(np.uint8).copy()).cuda()
+        oP = torch.zeros(info.output_elems * 2, dtype=torch.uint8, device="cuda")
+        kleos.forward_host_bench(iP, oP, skip=2, trials=4)
+        tl = kleos.flow_timeline()
+        ph = kleos.phase_times()
+    finally:
+        kleos.finalize()
+    assert 0 < tl["planned"] <= tl["last_gemm1_tile"] <= tl["last_tile"] <= tl["end"]
+    assert tl["first_tile"] <= tl["last_tile"] and tl["dispatched"] <= tl["end"] and tl["combined"] <= tl["end"]
+    assert tl["end"] <= ph["total"] * 1.05 + 0.01
 
 
 def test_dense_layer_in_a_multi_rank_launch_needs_no_connection():
