@@ -64,6 +64,7 @@ struct State {
     // kernel (moe_flow.cuh).  KLEOS_PHASES=1, or a layer beyond the kernel's shared-memory tables,
     // selects the same work as separate launches (dispatch, plan, GEMM1, GEMM2, combine).
     bool use_flow = false;
+    bool fuse_route = false;                 // ... and the router runs inside it too (KLEOS_FUSE_ROUTE=0: separate launches)
     int flow_grid = 0;                       // blocks of the persistent kernel (co-resident pairs x 2)
     flow::Counters* flow_ctr = nullptr;      // [2] scheduler state, see moe_flow.cuh
     long long* flow_stamps = nullptr;        // [flow_grid][kStampSlots] timeline of a timed forward
@@ -111,6 +112,7 @@ struct State {
     ncclComm_t comm = nullptr;
     cudaEvent_t ev[kPhases + 1] = {};
     cudaEvent_t ev_last = nullptr;  // recorded behind every forward on the caller's stream
+    unsigned long long launches = 0;  // kernels launched by the forward paths since initialise
     float phase_ms[kPhases] = {};
     std::string last_error;
 };
@@ -322,9 +324,9 @@ template <typename T>
 int launch_route(const RouteArgs& ra, cudaStream_t st) {
     const int grid = (ra.S + 63) / 64;
     if (ra.PX == 64) {
-        route_kernel<T, 64><<<grid, 256, route_smem_bytes<64>(), st>>>(ra);
+        { ++g.launches; route_kernel<T, 64><<<grid, 256, route_smem_bytes<64>(), st>>>(ra); }
     } else if (ra.PX == 128) {
-        route_kernel<T, 128><<<grid, 256, route_smem_bytes<128>(), st>>>(ra);
+        { ++g.launches; route_kernel<T, 128><<<grid, 256, route_smem_bytes<128>(), st>>>(ra); }
     } else if (ra.PX == 256) {
         static bool attr_set = false;
         if (!attr_set) {
@@ -333,11 +335,11 @@ int launch_route(const RouteArgs& ra, cudaStream_t st) {
                                             (int)route_smem_bytes<256>()));
             attr_set = true;
         }
-        route_kernel<T, 256><<<grid, 256, route_smem_bytes<256>(), st>>>(ra);
+        { ++g.launches; route_kernel<T, 256><<<grid, 256, route_smem_bytes<256>(), st>>>(ra); }
     } else {
         return fail(KLEOS_E_UNSUPPORTED, "more than 256 experts are not supported by the router");
     }
-    refine_kernel<T><<<148, 256, 0, st>>>(ra);
+    { ++g.launches; refine_kernel<T><<<148, 256, 0, st>>>(ra); }
     return KLEOS_OK;
 }
 
@@ -347,28 +349,28 @@ template <typename TE, int kEpi>
 void launch_tc2(bool deep, int grid, cudaStream_t st, const CUtensorMap& map_a, const CUtensorMap& map_b,
                 const GemmArgs& ga) {
     if (deep)
-        ffn_gemm_tc2<TE, kEpi, 2><<<grid, 256, gemm_tc2::SMEM_BYTES, st>>>(map_a, map_b, ga);
+        { ++g.launches; ffn_gemm_tc2<TE, kEpi, 2><<<grid, 256, gemm_tc2::SMEM_BYTES, st>>>(map_a, map_b, ga); }
     else
-        ffn_gemm_tc2<TE, kEpi, 1><<<grid, 256, gemm_tc2::SMEM_BYTES, st>>>(map_a, map_b, ga);
+        { ++g.launches; ffn_gemm_tc2<TE, kEpi, 1><<<grid, 256, gemm_tc2::SMEM_BYTES, st>>>(map_a, map_b, ga); }
 }
 
 // The persistent kernel, instantiated per activation and per compile-time top-k of the combine.
 template <typename TE>
 void launch_flow(int act, int K, cudaStream_t st, const flow::Args& fa, const CUtensorMap* fa_act) {
     const int grid = g.flow_grid, smem = flow::SMEM_BYTES, thr = flow::kThreads;
-    if (act == 0 && K == 2) moe_flow_kernel<TE, 0, 2><<<grid, thr, smem, st>>>(g.map_x, g.map_w1h, g.map_y1, g.map_w2h, *fa_act, g.map_wgh, fa);
-    else if (act == 0) moe_flow_kernel<TE, 0, 0><<<grid, thr, smem, st>>>(g.map_x, g.map_w1h, g.map_y1, g.map_w2h, *fa_act, g.map_wgh, fa);
-    else if (K == 2) moe_flow_kernel<TE, 1, 2><<<grid, thr, smem, st>>>(g.map_x, g.map_w1h, g.map_y1, g.map_w2h, *fa_act, g.map_wgh, fa);
-    else moe_flow_kernel<TE, 1, 0><<<grid, thr, smem, st>>>(g.map_x, g.map_w1h, g.map_y1, g.map_w2h, *fa_act, g.map_wgh, fa);
+    if (act == 0 && K == 2) { ++g.launches; moe_flow_kernel<TE, 0, 2><<<grid, thr, smem, st>>>(g.map_x, g.map_w1h, g.map_y1, g.map_w2h, *fa_act, g.map_wgh, fa); }
+    else if (act == 0) { ++g.launches; moe_flow_kernel<TE, 0, 0><<<grid, thr, smem, st>>>(g.map_x, g.map_w1h, g.map_y1, g.map_w2h, *fa_act, g.map_wgh, fa); }
+    else if (K == 2) { ++g.launches; moe_flow_kernel<TE, 1, 2><<<grid, thr, smem, st>>>(g.map_x, g.map_w1h, g.map_y1, g.map_w2h, *fa_act, g.map_wgh, fa); }
+    else { ++g.launches; moe_flow_kernel<TE, 1, 0><<<grid, thr, smem, st>>>(g.map_x, g.map_w1h, g.map_y1, g.map_w2h, *fa_act, g.map_wgh, fa); }
 }
 
 // TF32 layers: one launch of the kind::tf32 GEMM with the epilogue chosen at compile time.
 void launch_tf32(int epi, cudaStream_t st, const CUtensorMap& map_a, const CUtensorMap& map_b,
                  const GemmArgs& ga) {
     const int grid = g.sm_count, smem = gemm_tf32::SMEM_BYTES;
-    if (epi == 0) ffn_gemm_tf32<0><<<grid, 256, smem, st>>>(map_a, map_b, ga);
-    else if (epi == 1) ffn_gemm_tf32<1><<<grid, 256, smem, st>>>(map_a, map_b, ga);
-    else ffn_gemm_tf32<2><<<grid, 256, smem, st>>>(map_a, map_b, ga);
+    if (epi == 0) { ++g.launches; ffn_gemm_tf32<0><<<grid, 256, smem, st>>>(map_a, map_b, ga); }
+    else if (epi == 1) { ++g.launches; ffn_gemm_tf32<1><<<grid, 256, smem, st>>>(map_a, map_b, ga); }
+    else { ++g.launches; ffn_gemm_tf32<2><<<grid, 256, smem, st>>>(map_a, map_b, ga); }
 }
 
 // Optional replacement of the activation input and the layer-output destination of one
@@ -417,9 +419,9 @@ int forward_dense(const Sections& s, const CUtensorMap* map_a, cudaStream_t st, 
         KLEOS_CUDA(mark());
         launch_tf32(2, st, g.map_y1, g.map_w2, g2);
     } else {
-        ffn_gemm_simt<T><<<g.sm_count * 2, 256, 0, st>>>(g1);
+        { ++g.launches; ffn_gemm_simt<T><<<g.sm_count * 2, 256, 0, st>>>(g1); }
         KLEOS_CUDA(mark());
-        ffn_gemm_simt<T><<<g.sm_count * 2, 256, 0, st>>>(g2);
+        { ++g.launches; ffn_gemm_simt<T><<<g.sm_count * 2, 256, 0, st>>>(g2); }
     }
     KLEOS_CUDA(mark());
     KLEOS_CUDA(mark());  // combine: nothing to do
@@ -445,8 +447,13 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed, const S
     auto mark = [&]() -> cudaError_t { return timed ? cudaEventRecord(g.ev[evi++], st) : cudaSuccess; };
     KLEOS_CUDA(mark());
 
+    const bool routed_in_kernel = g.use_flow && g.fuse_route;
+    if (routed_in_kernel) {
+        KLEOS_CUDA(mark());
+        KLEOS_CUDA(mark());
+    }
     // 1. router
-    KLEOS_CUDA(cudaMemsetAsync(g.refine_count, 0, sizeof(int), st));
+    if (!routed_in_kernel) KLEOS_CUDA(cudaMemsetAsync(g.refine_count, 0, sizeof(int), st));
     RouteArgs ra{};
     ra.A = s.A; ra.Wg = s.Wg; ra.bias = g.bias; ra.probs = s.probs; ra.topk = g.topk;
     ra.mcw = g.mcw; ra.refine_list = g.refine_list; ra.refine_count = g.refine_count;
@@ -454,22 +461,24 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed, const S
     ra.S = c.S; ra.H = c.H; ra.E = c.E; ra.K = c.K; ra.PX = c.PX; ra.tie_eps = 1e-4f;
     ra.col_partial = g.col_partial;  // null unless is_training
     int route_blocks = (c.S + 63) / 64;
-    if ((g.use_tc || g.use_tf32_tc) && c.PX <= 128) {
+    if (routed_in_kernel) {
+        // nothing to launch here
+    } else if ((g.use_tc || g.use_tf32_tc) && c.PX <= 128) {
         route_blocks = (c.S + route_tc::BM - 1) / route_tc::BM;
         if constexpr (!std::is_same<T, float>::value) {
             const int grid = (c.S + route_tc::BM - 1) / route_tc::BM;
             if (c.PX == 64)
-                route_tc_kernel<T, 64><<<grid, 256, route_tc::Shape<64>::SMEM_BYTES, st>>>(
-                    *act_map, g.map_wg, ra, g.status, g.wait_cycles, (int)g.epoch);
+                { ++g.launches; route_tc_kernel<T, 64><<<grid, 256, route_tc::Shape<64>::SMEM_BYTES, st>>>(
+                    *act_map, g.map_wg, ra, g.status, g.wait_cycles, (int)g.epoch); }
             else
-                route_tc_kernel<T, 128><<<grid, 256, route_tc::Shape<128>::SMEM_BYTES, st>>>(
-                    *act_map, g.map_wg, ra, g.status, g.wait_cycles, (int)g.epoch);
-            refine_kernel<T><<<148, 256, 0, st>>>(ra);
+                { ++g.launches; route_tc_kernel<T, 128><<<grid, 256, route_tc::Shape<128>::SMEM_BYTES, st>>>(
+                    *act_map, g.map_wg, ra, g.status, g.wait_cycles, (int)g.epoch); }
+            { ++g.launches; refine_kernel<T><<<148, 256, 0, st>>>(ra); }
         }
     } else if ((rc = launch_route<T>(ra, st))) {
         return rc;
     }
-    KLEOS_CUDA(mark());
+    if (!routed_in_kernel) KLEOS_CUDA(mark());
 
     // 2. slots
     SlotArgs sa{};
@@ -478,11 +487,13 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed, const S
     for (int r = 0; r < kMaxWorld; ++r) sa.peer_arena[r] = g.peers.arena[r];
     sa.cflag_offset = g.lay.cflag; sa.rank = g.rank; sa.nLx = g.nLx; sa.epoch = g.epoch;
     sa.tile_hist = g.tile_hist;
-    tile_hist_kernel<<<(c.S + kSlotTile - 1) / kSlotTile, 256, 0, st>>>(sa);
-    slot_kernel<<<(c.S + kSlotTile - 1) / kSlotTile, 256, 0, st>>>(sa);
-    if (g.col_partial)
-        gate_stats_kernel<<<1, 256, 0, st>>>(g.col_partial, route_blocks, c.PX, g.counts, c.S, c.E, g.gate_stats);
-    KLEOS_CUDA(mark());
+    if (!routed_in_kernel) {
+        { ++g.launches; tile_hist_kernel<<<(c.S + kSlotTile - 1) / kSlotTile, 256, 0, st>>>(sa); }
+        { ++g.launches; slot_kernel<<<(c.S + kSlotTile - 1) / kSlotTile, 256, 0, st>>>(sa); }
+        if (g.col_partial)
+            { ++g.launches; gate_stats_kernel<<<1, 256, 0, st>>>(g.col_partial, route_blocks, c.PX, g.counts, c.S, c.E, g.gate_stats); }
+        KLEOS_CUDA(mark());
+    }
 
     if (g.use_flow) {
         if constexpr (sizeof(T) == 2) {
@@ -498,6 +509,8 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed, const S
             // deep stages when an expert sees enough rows for the tensor pipe, not the weight
             // stream from HBM, to be the limit (about 260 FLOP per weight byte on this part)
             fa.sub = (long long)g.world * c.EC >= 512 ? 2 : 1;
+            fa.fuse_route = routed_in_kernel ? 1 : 0;
+            fa.Wg = s.Wg; fa.gate_bias = g.bias; fa.tile_hist = g.tile_hist; fa.tie_eps = 1e-4f;
             if (timed)
                 KLEOS_CUDA(cudaMemsetAsync(g.flow_stamps, 0,
                                            sizeof(long long) * g.flow_grid * flow::kStampSlots, st));
@@ -515,7 +528,7 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed, const S
     da.lay = g.lay; da.done_counter = g.done_dispatch; da.H = c.H; da.E = c.E; da.EC = c.EC;
     da.pEC = c.pEC; da.nLx = g.nLx; da.rank = g.rank; da.world = g.world; da.epoch = g.epoch;
     da.elem_bytes = c.elem_bytes; da.le_begin = 0; da.le_end = g.nLx;
-    dispatch_kernel<<<g.sm_count * 4, 256, 0, st>>>(da);
+    { ++g.launches; dispatch_kernel<<<g.sm_count * 4, 256, 0, st>>>(da); }
     KLEOS_CUDA(mark());
     // 4. plan: wait for every source's rows, list the panels
     PlanArgs pa{};
@@ -523,7 +536,7 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed, const S
     pa.cell_counts = g.cell_counts; pa.status = g.status; pa.world = g.world; pa.nLx = g.nLx;
     pa.pEC = c.pEC; pa.epoch = g.epoch; pa.wait_cycles = g.wait_cycles; pa.rank = g.rank;
     pa.le_begin = 0; pa.le_end = g.nLx;
-    plan_kernel<<<1, 1024, 0, st>>>(pa);
+    { ++g.launches; plan_kernel<<<1, 1024, 0, st>>>(pa); }
     KLEOS_CUDA(mark());
 
     // 5./6. expert FFN
@@ -561,9 +574,9 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed, const S
         launch_tf32(2, st, g.map_y1, g.map_w2, g2);
         KLEOS_CUDA(mark());
     } else {
-        ffn_gemm_simt<T><<<g.sm_count * 2, 256, 0, st>>>(g1);
+        { ++g.launches; ffn_gemm_simt<T><<<g.sm_count * 2, 256, 0, st>>>(g1); }
         KLEOS_CUDA(mark());
-        ffn_gemm_simt<T><<<g.sm_count * 2, 256, 0, st>>>(g2);
+        { ++g.launches; ffn_gemm_simt<T><<<g.sm_count * 2, 256, 0, st>>>(g2); }
         KLEOS_CUDA(mark());
     }
 
@@ -574,11 +587,11 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed, const S
     ca.PX = c.PX; ca.pEC = c.pEC; ca.world = g.world; ca.epoch = g.epoch;
     ca.wait_cycles = g.wait_cycles;
     if (c.K == 2)
-        combine_kernel<T, 2><<<g.sm_count * 4, 256, 0, st>>>(ca);
+        { ++g.launches; combine_kernel<T, 2><<<g.sm_count * 4, 256, 0, st>>>(ca); }
     else if (c.K == 1)
-        combine_kernel<T, 1><<<g.sm_count * 4, 256, 0, st>>>(ca);
+        { ++g.launches; combine_kernel<T, 1><<<g.sm_count * 4, 256, 0, st>>>(ca); }
     else
-        combine_kernel<T, 0><<<g.sm_count * 4, 256, 0, st>>>(ca);
+        { ++g.launches; combine_kernel<T, 0><<<g.sm_count * 4, 256, 0, st>>>(ca); }
     KLEOS_CUDA(mark());
     KLEOS_CUDA(cudaGetLastError());
     return KLEOS_OK;
@@ -869,6 +882,8 @@ static int initialize_impl(const char* config_json_path, int rank, int world, co
     g.use_flow = g.use_tc && !dense && !(phases && phases[0] == '1') && g.flow_grid >= 2 &&
                  (size_t)cfg.E * cfg.pEC / kTileM <= (size_t)flow::kMaxPanels && cfg.E <= flow::kMaxCells &&
                  g.nLx <= flow::kMaxLocal;
+    const char* fr = std::getenv("KLEOS_FUSE_ROUTE");
+    g.fuse_route = g.use_flow && cfg.PX <= 128 && !cfg.is_training && !(fr && fr[0] == '0');
     if (g.use_flow) {
         flow::Counters* ctr = nullptr;
         if ((rc = dev_alloc(&ctr, 2))) return rc;
@@ -988,8 +1003,12 @@ int kleos_forward_bench(const void* iP, void* oP, int skip, int trials, float* m
         // the per-phase slots, as far as phases still exist inside one kernel: when the last row was
         // dispatched and the plan was known (both from kernel start), the GEMM1 and GEMM2 spans of the
         // tile stream, and the tail between the last tile and the end (combine of the last tokens)
-        g.phase_ms[2] = m[flow::kDispatched];
-        g.phase_ms[3] = m[flow::kPlanned];
+        g.phase_ms[2] = m[flow::kDispatched] - m[flow::kSlotted];
+        g.phase_ms[3] = m[flow::kPlanned] - m[flow::kSlotted];
+        if (g.fuse_route) {  // the router's two stages, each ended by a grid barrier
+            g.phase_ms[0] = m[flow::kRouted];
+            g.phase_ms[1] = m[flow::kSlotted] - m[flow::kRouted];
+        }
         g.phase_ms[4] = m[flow::kLastGemm1] - m[flow::kFirstTile];
         g.phase_ms[5] = m[flow::kLastTile] - m[flow::kLastGemm1];
         g.phase_ms[6] = m[flow::kEnd] - m[flow::kLastTile];
@@ -1199,6 +1218,8 @@ int kleos_phase_times(float* ms, int n) {
     for (int p = 0; p < kPhases; ++p) ms[p] = g.phase_ms[p];
     return KLEOS_OK;
 }
+
+long long kleos_launch_count(void) { return g.initialised ? (long long)g.launches : (long long)KLEOS_E_STATE; }
 
 int kleos_flow_timeline(float* ms, int n) {
     if (!ms || n < flow::kStampSlots) return fail(KLEOS_E_ARG, "need room for %d floats", flow::kStampSlots);

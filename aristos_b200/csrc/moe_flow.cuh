@@ -65,7 +65,7 @@ constexpr int kMaxPasses = 8;      // combine passes (tokens grouped by when the
 constexpr int kRoleWarps = 10;     // producer, MMA, 4 read-back, 4 transport
 constexpr int kCtlBytes = 32768;
 constexpr int SMEM_BYTES = kSlices * SLICE_BYTES + 1024 + kCtlBytes;
-constexpr int kStampSlots = 8;     // per block: see Stamp
+constexpr int kStampSlots = 10;    // per block: see Stamp
 
 // Per-rank scheduler state in global memory.  Two copies: the forward of epoch n works on copy
 // n & 1 and clears the other one for the forward after it, so nothing is memset between launches.
@@ -82,7 +82,7 @@ struct Counters {
     unsigned panel_ret[kMaxPanels];   // read-back warps that finished a GEMM2 tile, per panel
 };
 
-enum Stamp { kStart = 0, kPlanned, kFirstTile, kLastGemm1, kLastTile, kDispatched, kCombined, kEnd };
+enum Stamp { kStart = 0, kPlanned, kFirstTile, kLastGemm1, kLastTile, kDispatched, kCombined, kEnd, kRouted, kSlotted };
 
 struct Control {
     unsigned long long full[kSlices];    // used on the leader
@@ -94,7 +94,7 @@ struct Control {
     uint32_t tmem_base;
     int abort;
     int roles_done;
-    int total_tiles, total_panels;
+    int total_tiles, total_panels, lag;
     unsigned total_units;
     int le_start[kMaxLocal + 1];             // first panel of every local expert
     int seg_prefix[2 * kMaxLocal + 1];       // tiles before every segment of the tile order
@@ -178,21 +178,53 @@ __device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v
     asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
 }
 
-// Segment s of the tile order: G1(0), then G1(i), G2(i-1) for i = 1..n-1, then G2(n-1).
-__device__ __forceinline__ void segment_of(int s, int n, int* phase, int* le) {
-    if (s == 0) {
+// Segment s of the tile order for n local experts and lag D (1 <= D <= n):
+//   G1(0) .. G1(D-1),  then G1(i), G2(i-D) for i = D .. n-1,  then G2(n-D) .. G2(n-1).
+// A GEMM2 segment therefore follows the GEMM1 segment it depends on by D GEMM1 segments and D-1
+// GEMM2 segments; D is chosen in the plan so that this distance exceeds the number of tiles in
+// flight (one per block pair): by the time a GEMM2 tile is claimed, the GEMM1 tiles of its row
+// panels have normally been finished and nobody waits.
+__device__ __forceinline__ void segment_of(int s, int n, int D, int* phase, int* le) {
+    if (s < D) {
         *phase = 0;
-        *le = 0;
-    } else if (s == 2 * n - 1) {
-        *phase = 1;
-        *le = n - 1;
-    } else if (s & 1) {
-        *phase = 0;
-        *le = (s + 1) >> 1;
+        *le = s;
+    } else if (s < 2 * n - D) {
+        const int r = s - D;
+        *phase = r & 1;
+        *le = (r & 1) ? (r >> 1) : D + (r >> 1);
     } else {
         *phase = 1;
-        *le = (s >> 1) - 1;
+        *le = s - n;  // n - D + (s - (2n - D))
     }
+}
+
+// Exclusive prefix sum of f(0) .. f(n-1), n <= 256, by one warp: out[i] = f(0) + .. + f(i-1) for
+// i = 0 .. n.  Returns the total in every lane.
+template <typename F, typename O>
+__device__ __forceinline__ int warp_prefix(F f, O* out, int n, int lane) {
+    int v[8], local = 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const int i = lane * 8 + k;
+        v[k] = i < n ? f(i) : 0;
+        local += v[k];
+    }
+    int incl = local;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+    }
+    int run = incl - local;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const int i = lane * 8 + k;
+        if (i < n) out[i] = (O)run;
+        run += v[k];
+    }
+    const int total = __shfl_sync(0xffffffffu, incl, 31);
+    if (lane == 0) out[n] = (O)total;
+    return total;
 }
 
 __device__ __forceinline__ Tile decode_tile(const Control* ctl, int t, int nLx) {
@@ -202,7 +234,7 @@ __device__ __forceinline__ Tile decode_tile(const Control* ctl, int t, int nLx) 
         if (ctl->seg_prefix[mid] <= t) lo = mid; else hi = mid;
     }
     Tile ti;
-    segment_of(lo, nLx, &ti.phase, &ti.le);
+    segment_of(lo, nLx, ctl->lag, &ti.phase, &ti.le);
     const int r = t - ctl->seg_prefix[lo];
     const int p0 = ctl->le_start[ti.le], np = ctl->le_start[ti.le + 1] - p0;
     const int npair = (np + 1) >> 1;
@@ -226,7 +258,7 @@ __device__ __forceinline__ void combine_row(const T* const* yrow, const float* p
                                             int chunks, int lane, int K) {
     constexpr int VEC = 16 / sizeof(T);
     constexpr int KMAX = KT > 0 ? KT : kMaxTopK;
-    constexpr int UNR = KT > 0 && KT <= 2 ? 4 : 1;
+    constexpr int UNR = KT > 0 && KT <= 2 ? 8 : 1;  // 16-byte loads in flight per lane and choice
     using P2 = Pack2<T>;
     const float inv_w = 1.f / w;
     for (int c0 = lane; c0 < chunks; c0 += 32 * UNR) {
@@ -423,7 +455,6 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     // the accumulator in turn continue from there).  The routing phase always runs the six
     // 32 KiB slices as six stages, whatever stage depth the tile stream uses afterwards.
     uint32_t route_slices = 0, route_tiles = 0;
-    bool alive = true;
 
     if (a.fuse_route) {
         // ================================================================== routing phase
@@ -735,8 +766,10 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         };
         if (*abort_flag) atomicExch(&ctr->abort_all, 1u);
         grid_barrier(0);
-        alive = !*abort_flag;
-        if (alive) {
+        if (stamp && tid == 0) stamp[kRouted] = global_ns();
+        // (after a failed wait the rest of the kernel still runs through its barriers, with the
+        // abort flag up, so that both blocks of a pair meet at the same cluster barriers)
+        if (!*abort_flag) {
             // Slots in ascending token order (the reference hands them out in atomicAdd arrival
             // order, moe/gate.cuh:689-718): base slot of every expert for a tile of 128 tokens = sum of
             // the earlier tiles' histograms, then each token's rank inside the tile; the last tile
@@ -811,7 +844,7 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             }
         }
         grid_barrier(1);
-        alive = !*abort_flag;
+        if (stamp && tid == 0) stamp[kSlotted] = global_ns();
     }
 
     // ------------------------------------------------------------------ plan (every block, same result)
@@ -841,40 +874,48 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         // any moment the source ranks write to different owners
         for (int i = tid; i < a.E; i += kThreads) {
             const int le = i / a.world, owner = (a.rank + 1 + i % a.world) % a.world;
-            ctl->own_s[i] = (int)min(a.counts[owner * a.nLx + le], (unsigned)a.EC);
+            ctl->own_s[i] = (int)min(__ldcg(a.counts + owner * a.nLx + le), (unsigned)a.EC);
         }
         __syncthreads();
-        if (tid == 0) {
-            unsigned run = 0;
-            for (int i = 0; i < a.E; ++i) {
-                ctl->prefix_s[i] = run;
-                run += (unsigned)(ctl->own_s[i] + kUnitRows - 1) / kUnitRows;
+        if (warp == 0) {
+            // dispatch units before every expert, in sending order
+            const int total = warp_prefix([&](int i) { return (ctl->own_s[i] + kUnitRows - 1) / kUnitRows; },
+                                          ctl->prefix_s, a.E, lane);
+            if (lane == 0) ctl->total_units = (unsigned)total;
+        } else if (warp == 1) {
+            // panels before every cell, cells in plan order o = le * world + j
+            const int n_panels = warp_prefix(
+                [&](int o) {
+                    const int le = o / a.world, j = o - le * a.world;
+                    return (ctl->cnt_s[((a.rank + 1 + j) % a.world) * a.nLx + le] + kTileM - 1) / kTileM;
+                },
+                ctl->poff_s, cells, lane);
+            __syncwarp();
+            for (int le = lane; le <= a.nLx; le += 32) ctl->le_start[le] = le < a.nLx ? ctl->poff_s[le * a.world] : n_panels;
+            __syncwarp();
+            // lag of the tile order: enough segments between a GEMM1 segment and its GEMM2 segment
+            // to cover one and a half times the tiles in flight
+            int pairs = 0;
+            for (int le = lane; le < a.nLx; le += 32)
+                pairs += (ctl->le_start[le + 1] - ctl->le_start[le] + 1) >> 1;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) pairs += __shfl_xor_sync(0xffffffffu, pairs, o);
+            const int t1 = max(1, pairs * NT1 / a.nLx), t2 = max(1, pairs * NT2 / a.nLx);
+            const int in_flight = (int)gridDim.x >> 1;
+            const int lag = min(a.nLx, max(1, (in_flight + in_flight / 2 + t2 + t1 + t2 - 1) / (t1 + t2)));
+            const int n_tiles = warp_prefix(
+                [&](int sg) {
+                    int phase, le;
+                    segment_of(sg, a.nLx, lag, &phase, &le);
+                    const int np = ctl->le_start[le + 1] - ctl->le_start[le];
+                    return ((np + 1) >> 1) * (phase ? NT2 : NT1);
+                },
+                ctl->seg_prefix, 2 * a.nLx, lane);
+            if (lane == 0) {
+                ctl->lag = lag;
+                ctl->total_panels = n_panels;
+                ctl->total_tiles = n_tiles;
             }
-            ctl->prefix_s[a.E] = run;
-            ctl->total_units = run;
-        } else if (tid == 32) {
-            int n = 0;
-            for (int o = 0; o < cells; ++o) {  // plan order: o = le * world + j
-                const int le = o / a.world, j = o - le * a.world;
-                const int src = (a.rank + 1 + j) % a.world;
-                if (j == 0) ctl->le_start[le] = n;
-                ctl->poff_s[o] = n;
-                n = min(n + (ctl->cnt_s[src * a.nLx + le] + kTileM - 1) / kTileM, kMaxPanels);
-            }
-            ctl->poff_s[cells] = n;
-            ctl->le_start[a.nLx] = n;
-            ctl->total_panels = n;
-            // tile order: G1(0), then G1(i), G2(i-1), ..., then G2(n-1)
-            int t = 0;
-            for (int s = 0; s < 2 * a.nLx; ++s) {
-                int phase, le;
-                segment_of(s, a.nLx, &phase, &le);
-                ctl->seg_prefix[s] = t;
-                const int np = ctl->le_start[le + 1] - ctl->le_start[le];
-                t += ((np + 1) >> 1) * (phase ? NT2 : NT1);
-            }
-            ctl->seg_prefix[2 * a.nLx] = t;
-            ctl->total_tiles = t;
         }
         __syncthreads();
         for (int o = tid; o < cells; o += kThreads) {
@@ -883,7 +924,7 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             const int c = src * a.nLx + le;
             const int cnt = ctl->cnt_s[c];
             int n = ctl->poff_s[o];
-            for (int r = 0; r < cnt && n < kMaxPanels; r += kTileM)
+            for (int r = 0; r < cnt && n < kMaxPanels; r += kTileM)  // the host never plans beyond the table
                 ctl->panel_s[n++] = make_uint2((unsigned)(c * a.pEC + r),
                                                (unsigned)min(kTileM, cnt - r) | ((unsigned)le << 8) |
                                                    ((unsigned)src << 16));
@@ -955,6 +996,82 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             }
         }
         return *reinterpret_cast<volatile int*>(&ctl->task_s[slot]);
+    };
+
+    // The combine, run by the transport warps once their rows are dispatched and by the read-back
+    // warps once the tile stream has ended.
+    auto run_combine = [&]() {
+        // (2) combine.  Tokens are visited in passes: the experts of one rank finish in the
+        // order of their local index, so a token's rows are all back once the LAST of its experts
+        // (by local index) has returned; pass q takes the tokens whose last expert falls into
+        // the q-th part of that order.  An item is (pass, block of 32 tokens); the warp that
+        // claims it waits (bounded) for the return flags of each token's panels and gathers the
+        // rows (reference: subscriber decodes returned tiles into combine tasks,
+        // os/subscriber.cuh:187-332; the sum itself processor.cuh:110-168).
+        const int passes = min(a.nLx, kMaxPasses);
+        const int nblk = (a.S + kCombineBlock - 1) / kCombineBlock;
+        const unsigned total_items = (unsigned)(passes * nblk);
+        const int K = KT > 0 ? KT : a.K;
+        const int TCM = a.pEC / kTileM;
+        const unsigned long long* ypflag =
+            reinterpret_cast<const unsigned long long*>(a.peers.arena[a.rank] + a.lay.ypflag);
+        const TE* ycell = reinterpret_cast<const TE*>(a.peers.arena[a.rank] + a.lay.ycell);
+        const TE* probs = static_cast<const TE*>(a.probs);
+        const int chunks = a.H / (16 / (int)sizeof(TE));
+        for (;;) {
+            unsigned item = 0;
+            if (lane == 0) item = (*abort_flag) ? 0xffffffffu : atomicAdd(&ctr->item_next, 1u);
+            item = __shfl_sync(0xffffffffu, item, 0);
+            if (item >= total_items) break;
+            const int q = (int)item / nblk, b = (int)item - q * nblk;
+            const int t_mine = b * kCombineBlock + lane;
+            int cls = -1;  // pass in which this lane's token is handled
+            if (t_mine < a.S) {
+                cls = 0;
+                for (int j = 0; j < K; ++j) {
+                    const int e = __ldcg(a.topk + (size_t)t_mine * K + j);
+                    const int sl = __ldcg(a.slots + (size_t)t_mine * K + j);
+                    if (sl != kDropped) cls = max(cls, (e % a.nLx) * passes / a.nLx);
+                }
+            }
+            unsigned todo = __ballot_sync(0xffffffffu, cls == q);
+            while (todo) {
+                const int src_lane = __ffs(todo) - 1;
+                todo &= todo - 1;
+                const int t = b * kCombineBlock + src_lane;
+                constexpr int KMAX = KT > 0 ? KT : kMaxTopK;
+                const TE* yrow[KMAX];
+                float p[KMAX];
+                bool failed = false;
+    #pragma unroll
+                for (int j = 0; j < KMAX; ++j) {
+                    yrow[j] = nullptr;
+                    p[j] = 0.f;
+                    if (j < K) {
+                        const int e = __ldcg(a.topk + (size_t)t * K + j);
+                        const int sl = __ldcg(a.slots + (size_t)t * K + j);
+                        p[j] = ld_cg_elem(probs + (size_t)t * a.PX + e);
+                        if (sl != kDropped) {
+                            yrow[j] = ycell + ((size_t)e * a.pEC + sl) * a.H;
+                            if (lane == j) {
+                                unsigned long long v;
+                                if (!wait_flag(ypflag + (size_t)e * TCM + sl / kTileM, a.epoch, budget, &v)) {
+                                    give_up(KLEOS_AT_COMBINE_WAIT, e);
+                                    failed = true;
+                                }
+                            }
+                        }
+                    }
+                }
+                failed = __any_sync(0xffffffffu, failed) || *abort_flag;
+                if (failed) {
+                    todo = 0;
+                    break;
+                }
+                combine_row<TE, KT>(yrow, p, __ldcg(a.mcw + t), static_cast<TE*>(a.out) + (size_t)t * a.H,
+                                    chunks, lane, K);
+            }
+        }
     };
 
     if (warp == 0) {
@@ -1192,6 +1309,8 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             }
             if (stamp && q == 0 && lane == 0) stamp[kLastTile] = global_ns();
         }
+        // no tiles left: help with the combine of the tokens whose rows return last
+        run_combine();
         if (lane == 0) atomicAdd(&ctl->roles_done, 1);
         __syncwarp();
     } else if (warp >= 8) {
@@ -1221,19 +1340,31 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             const int my_tok = lane < nrows ? __ldcg(a.cell_tokens + (size_t)e * a.pEC + slot0 + lane) : 0;
             char* cell = a.peers.arena[owner] + a.lay.xcell +
                          (((size_t)a.rank * a.nLx + le) * a.pEC + slot0) * a.H * sizeof(TE);
-            for (int r = 0; r < nrows; ++r) {
-                const int tok = __shfl_sync(0xffffffffu, my_tok, r);
-                const uint4* src = reinterpret_cast<const uint4*>(
-                    static_cast<const char*>(a.tokens) + (size_t)tok * a.H * sizeof(TE));
-                uint4* dst = reinterpret_cast<uint4*>(cell + (size_t)r * a.H * sizeof(TE));
+            // two rows at a time, eight 16-byte loads per lane and row in flight before the stores
+            for (int r = 0; r < nrows; r += 2) {
+                const int tok0 = __shfl_sync(0xffffffffu, my_tok, r);
+                const int tok1 = __shfl_sync(0xffffffffu, my_tok, min(r + 1, kUnitRows - 1));
+                const bool two = r + 1 < nrows;
+                const uint4* src0 = reinterpret_cast<const uint4*>(
+                    static_cast<const char*>(a.tokens) + (size_t)tok0 * a.H * sizeof(TE));
+                const uint4* src1 = reinterpret_cast<const uint4*>(
+                    static_cast<const char*>(a.tokens) + (size_t)tok1 * a.H * sizeof(TE));
+                uint4* dst0 = reinterpret_cast<uint4*>(cell + (size_t)r * a.H * sizeof(TE));
+                uint4* dst1 = reinterpret_cast<uint4*>(cell + (size_t)(r + 1) * a.H * sizeof(TE));
                 for (unsigned c0 = lane; c0 < row_chunks; c0 += 256) {
-                    uint4 v[8];
+                    uint4 v0[8], v1[8];
 #pragma unroll
                     for (int k = 0; k < 8; ++k)
-                        if (c0 + 32 * k < row_chunks) v[k] = __ldg(src + c0 + 32 * k);
+                        if (c0 + 32 * k < row_chunks) {
+                            v0[k] = __ldg(src0 + c0 + 32 * k);
+                            if (two) v1[k] = __ldg(src1 + c0 + 32 * k);
+                        }
 #pragma unroll
                     for (int k = 0; k < 8; ++k)
-                        if (c0 + 32 * k < row_chunks) dst[c0 + 32 * k] = v[k];
+                        if (c0 + 32 * k < row_chunks) {
+                            dst0[c0 + 32 * k] = v0[k];
+                            if (two) dst1[c0 + 32 * k] = v1[k];
+                        }
                 }
             }
             __threadfence_system();
@@ -1250,77 +1381,7 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         }
         if (stamp && warp == 8 && lane == 0) stamp[kDispatched] = global_ns();
 
-        // (2) combine.  Tokens are visited in passes: the experts of one rank finish in the
-        // order of their local index, so a token's rows are all back once the LAST of its experts
-        // (by local index) has returned; pass q takes the tokens whose last expert falls into
-        // the q-th part of that order.  An item is (pass, block of 32 tokens); the warp that
-        // claims it waits (bounded) for the return flags of each token's panels and gathers the
-        // rows (reference: subscriber decodes returned tiles into combine tasks,
-        // os/subscriber.cuh:187-332; the sum itself processor.cuh:110-168).
-        const int passes = min(a.nLx, kMaxPasses);
-        const int nblk = (a.S + kCombineBlock - 1) / kCombineBlock;
-        const unsigned total_items = (unsigned)(passes * nblk);
-        const int K = KT > 0 ? KT : a.K;
-        const int TCM = a.pEC / kTileM;
-        const unsigned long long* ypflag =
-            reinterpret_cast<const unsigned long long*>(a.peers.arena[a.rank] + a.lay.ypflag);
-        const TE* ycell = reinterpret_cast<const TE*>(a.peers.arena[a.rank] + a.lay.ycell);
-        const TE* probs = static_cast<const TE*>(a.probs);
-        const int chunks = a.H / (16 / (int)sizeof(TE));
-        for (;;) {
-            unsigned item = 0;
-            if (lane == 0) item = (*abort_flag) ? 0xffffffffu : atomicAdd(&ctr->item_next, 1u);
-            item = __shfl_sync(0xffffffffu, item, 0);
-            if (item >= total_items) break;
-            const int q = (int)item / nblk, b = (int)item - q * nblk;
-            const int t_mine = b * kCombineBlock + lane;
-            int cls = -1;  // pass in which this lane's token is handled
-            if (t_mine < a.S) {
-                cls = 0;
-                for (int j = 0; j < K; ++j) {
-                    const int e = __ldcg(a.topk + (size_t)t_mine * K + j);
-                    const int sl = __ldcg(a.slots + (size_t)t_mine * K + j);
-                    if (sl != kDropped) cls = max(cls, (e % a.nLx) * passes / a.nLx);
-                }
-            }
-            unsigned todo = __ballot_sync(0xffffffffu, cls == q);
-            while (todo) {
-                const int src_lane = __ffs(todo) - 1;
-                todo &= todo - 1;
-                const int t = b * kCombineBlock + src_lane;
-                constexpr int KMAX = KT > 0 ? KT : kMaxTopK;
-                const TE* yrow[KMAX];
-                float p[KMAX];
-                bool failed = false;
-#pragma unroll
-                for (int j = 0; j < KMAX; ++j) {
-                    yrow[j] = nullptr;
-                    p[j] = 0.f;
-                    if (j < K) {
-                        const int e = __ldcg(a.topk + (size_t)t * K + j);
-                        const int sl = __ldcg(a.slots + (size_t)t * K + j);
-                        p[j] = Elem<TE>::to_f(probs[(size_t)t * a.PX + e]);
-                        if (sl != kDropped) {
-                            yrow[j] = ycell + ((size_t)e * a.pEC + sl) * a.H;
-                            if (lane == j) {
-                                unsigned long long v;
-                                if (!wait_flag(ypflag + (size_t)e * TCM + sl / kTileM, a.epoch, budget, &v)) {
-                                    give_up(KLEOS_AT_COMBINE_WAIT, e);
-                                    failed = true;
-                                }
-                            }
-                        }
-                    }
-                }
-                failed = __any_sync(0xffffffffu, failed) || *abort_flag;
-                if (failed) {
-                    todo = 0;
-                    break;
-                }
-                combine_row<TE, KT>(yrow, p, __ldcg(a.mcw + t), static_cast<TE*>(a.out) + (size_t)t * a.H,
-                                    chunks, lane, K);
-            }
-        }
+        run_combine();
         if (stamp && warp == 8 && lane == 0) stamp[kCombined] = global_ns();
         // (3) nobody leaves the forward before every expert rank has finished with this rank's
         // cells and counts: the next forward may then overwrite them (flags carry the epoch, so

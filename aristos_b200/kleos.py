@@ -27,7 +27,7 @@ EXPORTS = (
     "kleos_forward", "kleos_forward_bench", "kleos_forward_host", "kleos_forward_host_async",
     "kleos_host_sync", "kleos_get_rank",
     "kleos_local_experts", "kleos_get_info", "kleos_last_status", "kleos_clear_status", "kleos_debug_routing",
-    "kleos_phase_times", "kleos_flow_timeline", "kleos_debug_gemm_stats", "kleos_debug_suppress_return_flag", "kleos_gate_stats", "kleos_plan_placement", "kleos_placement_model", "kleos_route_static", "kleos_finalize", "kleos_error_string",
+    "kleos_phase_times", "kleos_flow_timeline", "kleos_launch_count", "kleos_debug_gemm_stats", "kleos_debug_suppress_return_flag", "kleos_gate_stats", "kleos_plan_placement", "kleos_placement_model", "kleos_route_static", "kleos_finalize", "kleos_error_string",
 )
 
 PHASE_NAMES = ("route", "slots", "dispatch", "plan", "gemm1", "gemm2", "combine", "total")
@@ -207,7 +207,7 @@ def route_static(A, Wg, gate_bias, S, H, E, K, torch_dtype, probs, topk, mcw, st
 
 
 FLOW_MILESTONES = ("start", "planned", "first_tile", "last_gemm1_tile", "last_tile", "dispatched",
-                   "combined", "end")
+                   "combined", "end", "routed", "slotted")
 
 
 def flow_timeline() -> dict:
@@ -218,6 +218,16 @@ def flow_timeline() -> dict:
     lib.kleos_flow_timeline.argtypes = [ctypes.POINTER(ctypes.c_float), ctypes.c_int]
     _check(lib.kleos_flow_timeline(buf, len(FLOW_MILESTONES)), "kleos_flow_timeline")
     return {n: float(buf[i]) for i, n in enumerate(FLOW_MILESTONES)}
+
+
+def launch_count() -> int:
+    """Kernels the library has launched for forward calls since initialize()."""
+    lib = load_library()
+    lib.kleos_launch_count.restype = ctypes.c_longlong
+    n = lib.kleos_launch_count()
+    if n < 0:
+        raise KleosError(int(n), "kleos_launch_count")
+    return int(n)
 
 
 def last_status() -> Status:

@@ -28,7 +28,7 @@ sys.path.insert(0, ROOT)
 from aristos_b200.config import baseline_config  # noqa: E402
 
 METRIC = "moe_layer_fwd_tokens_per_s"
-KERNELS_PER_FORWARD = 9  # route, refine, tile histogram, slots, dispatch, plan, GEMM1, GEMM2, combine
+PARITY_ROWS = 64  # output rows per rank compared with the CPU oracle after the timed regions
 
 
 def workload(name: str):
@@ -70,8 +70,45 @@ def load_peaks():
     if os.path.exists(path):
         with open(path) as f:
             p = json.load(f)
-        return dict(tflops=float(p["bf16_tflops"]), hbm=float(p["hbm_gbs"]), source="measured")
-    return dict(tflops=1590.0, hbm=6650.0, source="fallback")
+        return dict(tflops=float(p["bf16_tflops"]), hbm=float(p["hbm_gbs"]),
+                    tflops_sustained=float(p.get("bf16_tflops_sustained", p["bf16_tflops"])),
+                    source="measured")
+    return dict(tflops=1590.0, hbm=6650.0, tflops_sustained=1400.0, source="fallback")
+
+
+def bind_to_gpu_numa_node(local_rank: int):
+    """Pins this process (and therefore the pinned host buffers it allocates afterwards) to the
+    CPUs of the NUMA node the GPU hangs off.  Reads sysfs only; returns what it did."""
+    try:
+        import torch
+        bdf = torch.cuda.get_device_properties(local_rank).pci_bus_id  # e.g. 0000:1B:00.0
+    except Exception:
+        bdf = None
+    try:
+        if not bdf:
+            import pynvml
+            pynvml.nvmlInit()
+            h = pynvml.nvmlDeviceGetHandleByIndex(local_rank)
+            bdf = pynvml.nvmlDeviceGetPciInfo(h).busId
+            bdf = bdf.decode() if isinstance(bdf, bytes) else bdf
+        bdf = bdf.lower()
+        if len(bdf.split(":")[0]) == 8:
+            bdf = bdf[4:]
+        with open(f"/sys/bus/pci/devices/{bdf}/numa_node") as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return dict(numa_node=None, note="the platform reports no NUMA node for the GPU")
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            cpus = set()
+            for part in f.read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if allowed:
+            os.sched_setaffinity(0, allowed)
+        return dict(numa_node=node, cpus=len(allowed))
+    except Exception as exc:  # no sysfs entry, no permission: run unbound
+        return dict(numa_node=None, note=f"not bound: {type(exc).__name__}")
 
 
 class ClockSampler:
@@ -187,6 +224,62 @@ def host_views_from_device(cfg, buf, world):
     return [synth.split_packed(cfg, host, world)]
 
 
+def expert_weights_on_device(cfg, e, device):
+    """(W1 [I,H], W2 [H,I]) of global expert e as fp32 values rounded to the element type: the same
+    draws synth_on_device() makes for the rank that owns e, so any rank can rebuild any expert."""
+    import torch
+    tdt = torch_dtype_of(cfg)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(100000 + e)
+    ih = cfg.I * cfg.H
+    w1 = (torch.randn(ih, generator=gen, device=device) / cfg.H ** 0.5).to(tdt)
+    w2 = (torch.randn(ih, generator=gen, device=device) / cfg.I ** 0.5).to(tdt)
+    return w1.float().reshape(cfg.I, cfg.H), w2.float().reshape(cfg.H, cfg.I)
+
+
+def parity_check(cfg, info, kleos, iP, oP, rank, world, device, gate_bias):
+    """One more forward, outside every timed region, compared with the CPU oracle: routing of all
+    of this rank's tokens bit-exact (top-k sets, counts, slots), PARITY_ROWS seeded output rows
+    within the dtype's tolerance.  Returns (routing_exact, worst relative error, rows)."""
+    import torch
+    from oracle import c_oracle
+    from aristos_b200 import synth
+    tol = {0: 1e-5, 1: 4e-3, 2: 2e-2, 3: 4e-3}[cfg.torch_dtype]
+    kleos.forward_host(iP, oP, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    routing = kleos.debug_routing(info)
+    off = cfg.input_offsets(world)
+    A = iP[off["A"]:off["Wg"]].float().cpu().numpy().reshape(cfg.S, cfg.H)
+    Wg = iP[off["Wg"]:off["W1"]].float().cpu().numpy().reshape(-1, cfg.H)
+    rng = np.random.default_rng(1234 + rank)
+    rows = np.sort(rng.choice(cfg.S, size=min(PARITY_ROWS, cfg.S), replace=False)).astype(np.int32)
+    zero_b1, zero_b2 = np.zeros(cfg.I, np.float32), np.zeros(cfg.H, np.float32)
+
+    def get_expert(e):
+        w1, w2 = expert_weights_on_device(cfg, e, device)
+        return w1.cpu().numpy(), w2.cpu().numpy(), zero_b1, zero_b2
+
+    c_oracle.use_all_cores()
+    ref = c_oracle.moe_forward_rank_lazy(cfg, A, Wg, get_expert, gate_bias=gate_bias, tokens=rows)
+    got_sets = np.sort(routing["topk"], axis=1)
+    ref_sets = np.sort(ref["topk"], axis=1)
+    exact = bool(np.array_equal(got_sets, ref_sets) and np.array_equal(routing["counts"], ref["counts"]))
+    if exact:
+        m_got = np.full((cfg.S, cfg.E), -2, dtype=np.int64)
+        m_ref = np.full((cfg.S, cfg.E), -2, dtype=np.int64)
+        np.put_along_axis(m_got, routing["topk"].astype(np.int64), routing["slots"].astype(np.int64), axis=1)
+        np.put_along_axis(m_ref, ref["topk"].astype(np.int64), ref["slots"].astype(np.int64), axis=1)
+        exact = bool(np.array_equal(m_got, m_ref))
+    out = oP[cfg.S * cfg.PX:].float().cpu().numpy().reshape(cfg.S, cfg.H)[rows]
+    err = float(np.abs(out - ref["out"]).max() / max(np.abs(ref["out"]).max(), 1e-30))
+    return exact, err, int(rows.size), tol
+
+
+def reference_sample_note(cfg, sample):
+    return (f"each step: first {sample} of {cfg.S} tokens of one rank through all {cfg.E} experts, "
+            f"routing over all {cfg.S} tokens, fp32 accumulation")
+
+
 def run_reference(args):
     """The reference's own path restated for the CPU (the reference has no CPU implementation
     and cannot be built for sm_100), timed on the host cores; rank 0 only."""
@@ -197,17 +290,19 @@ def run_reference(args):
     from aristos_b200 import synth
     from oracle import c_oracle
     torch.set_num_threads(c_oracle.use_all_cores())  # launchers export OMP_NUM_THREADS=1
-    cfg, _ = baseline_config("C3")
+    cfg, workload_desc = workload(args.workload)
     torch.manual_seed(0)
     off = cfg.input_offsets(1)
     buf = torch.zeros(off["end"], dtype=torch.float32)
     buf[off["A"]:off["Wg"]] = torch.randn(cfg.S * cfg.H)
-    buf[off["Wg"]:off["Wg"] + cfg.E * cfg.H] = torch.randn(cfg.E * cfg.H) / cfg.H ** 0.5
-    n = 2 * cfg.E * cfg.I * cfg.H
-    buf[off["W1"]:off["W1"] + n] = torch.randn(n) / cfg.H ** 0.5  # fan_in H = I for this layer
-    host = buf.bfloat16().float().numpy()
+    if not cfg.dense:
+        buf[off["Wg"]:off["Wg"] + cfg.E * cfg.H] = torch.randn(cfg.E * cfg.H) / cfg.H ** 0.5
+    n = cfg.E * cfg.I * cfg.H
+    buf[off["W1"]:off["W1"] + n] = torch.randn(n) / cfg.H ** 0.5
+    buf[off["W2"]:off["W2"] + n] = torch.randn(n) / cfg.I ** 0.5
+    host = synth.round_to_dtype(buf.numpy(), cfg.torch_dtype)
     views = [synth.split_packed(cfg, host, 1)]
-    sample = args.cpu_sample
+    sample = min(args.cpu_sample, cfg.S)
     for _ in range(args.warmup):
         cpu_sample_tokens_per_s(cfg, views, sample)
     t0 = time.perf_counter()
@@ -219,13 +314,12 @@ def run_reference(args):
     line = dict(
         impl="reference", metric=METRIC, value=value, unit="tokens/s", n_gpus=args.gpus,
         steps=args.steps, warmup=args.warmup, ms_per_step=1e3 * dt / args.steps,
-        higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16", data="synthetic",
-        config=dict(workload="C3: S=8192 tokens/rank, H=I=2048, E=64, top-2, CF=1, bf16",
-                    note="CPU restatement of the reference math; the reference has no CPU path "
-                         "and does not compile for sm_100"),
+        higher_is_better=True, scaling="weak", vs_baseline=None, dtype=cfg.dtype_name, data="synthetic",
+        config=dict(workload=workload_desc),
         cpu_baseline=dict(value=value, unit="tokens/s", cores=threads, kind="port",
-                          sample=f"each step: first {sample} of 8192 tokens of one rank through "
-                                 "all 64 experts, routing over all 8192 tokens, fp32 accumulation"),
+                          sample=reference_sample_note(cfg, sample),
+                          note="CPU restatement of the reference math (oracle/moe_oracle.c); the "
+                               "reference has no CPU path and does not compile for sm_100"),
         e2e=dict(value=value, unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
         gpu_launches=0,
     )
@@ -233,15 +327,17 @@ def run_reference(args):
 
 
 def run_cuda(args):
-    import torch
-    import torch.distributed as dist
-    from aristos_b200 import kleos
-
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    import torch
+    import torch.distributed as dist
+    from aristos_b200 import kleos
+
+    # before any pinned allocation: this rank's threads and host buffers on the GPU's NUMA node
+    numa = bind_to_gpu_numa_node(local_rank)
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     uid = None
@@ -259,9 +355,11 @@ def run_cuda(args):
     kleos.set_device(local_rank)
     info = kleos.initialize(cfg, rank, world, uid)
     iP = synth_on_device(cfg, rank, world, device)
+    gate_bias = None
     if args.workload == "C4":
         from aristos_b200 import synth
-        kleos.set_gate_bias(synth.zipf_gate_bias(cfg, 1.2))  # Zipf(1.2) expert popularity
+        gate_bias = synth.zipf_gate_bias(cfg, 1.2)  # Zipf(1.2) expert popularity
+        kleos.set_gate_bias(gate_bias)
     oP = torch.zeros(info.output_elems, dtype=tdt, device=device)
     stream = torch.cuda.current_stream().cuda_stream
 
@@ -278,6 +376,21 @@ def run_cuda(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    def min_over_ranks(v: float) -> float:
+        return -max_over_ranks(-v)
+
+    def timed_forwards(n):
+        """n device-resident forwards between two CUDA events on the launching stream, a barrier
+        and a synchronize on both sides; milliseconds, max over ranks."""
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(n):
+            kleos.forward_host(iP, oP, stream)
+        e1.record()
+        barrier()
+        return max_over_ranks(e0.elapsed_time(e1))
+
     # ---------------------------------------------------------------- device-resident timing
     barrier()  # ranks finish generating their inputs at different times
     # clocks are sampled from the warm-up on (nvidia-smi needs some tens of milliseconds to
@@ -289,17 +402,13 @@ def run_cuda(args):
     for _ in range(max(args.warmup, 64)):
         kleos.forward_host(iP, oP, stream)
     barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for _ in range(args.steps):
-        kleos.forward_host(iP, oP, stream)
-    e1.record()
-    barrier()
-    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    launches0 = kleos.launch_count()
+    ms_total = timed_forwards(args.steps)
+    launches = kleos.launch_count() - launches0
     st = kleos.last_status()
     if st.code:
         raise SystemExit(f"device status: where={st.where} detail={st.detail}")
+    ms_per_step = ms_total / args.steps
 
     # ---------------------------------------------------------------- end to end, host buffers
     act_elems = cfg.S * cfg.H
@@ -320,9 +429,45 @@ def run_cuda(args):
     e2e_s = max_over_ranks(time.perf_counter() - t0)
     clocks = sampler.stop() if rank == 0 else None
 
+    # the two copies alone, all ranks at once, same buffers and two streams: what the host side
+    # (PCIe, host memory, the root complexes the GPUs share) delivers without any forward
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    dev_in = torch.empty(act_elems, dtype=tdt, device=device)
+    dev_out = torch.empty(act_elems, dtype=tdt, device=device)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        with torch.cuda.stream(s_in):
+            dev_in.copy_(host_in, non_blocking=True)
+        with torch.cuda.stream(s_out):
+            host_out.copy_(dev_out, non_blocking=True)
+    barrier()
+    copy_s = max_over_ranks(time.perf_counter() - t0)
+    copy_gbs = act_elems * eb * args.steps / copy_s / 1e9  # per direction and GPU, both running
+
+    # ---------------------------------------------------------------- sustained figure
+    # the same loop for at least a second, clocks sampled over this region alone
+    sustained = None
+    if args.sustain_s > 0:
+        n_long = max(args.steps, int(args.sustain_s * 1e3 / max(ms_per_step, 1e-3)))
+        long_sampler = ClockSampler(local_rank)
+        if rank == 0:
+            long_sampler.start()
+            time.sleep(0.1)
+        ms_long = timed_forwards(n_long)
+        long_clocks = long_sampler.stop() if rank == 0 else None
+        sustained = dict(steps=n_long, ms_per_step=ms_long / n_long, clocks=long_clocks)
+        st = kleos.last_status()
+        if st.code:
+            raise SystemExit(f"device status: where={st.where} detail={st.detail}")
+
     # ---------------------------------------------------------------- per-phase times, roofline
     kleos.forward_host_bench(iP, oP, skip=2, trials=max(4, min(args.steps, 16)))
     phases = kleos.phase_times()
+    try:
+        timeline = kleos.flow_timeline()
+    except kleos.KleosError:
+        timeline = None  # this layer runs as separate launches
     # a single-expert layer has no routing: every token of every rank goes through the one expert
     routing = dict(counts=np.array([cfg.S], dtype=np.uint32)) if cfg.dense else kleos.debug_routing(info)
     routed_here = int(np.minimum(routing["counts"], info.EC).sum())  # pairs this rank dispatched
@@ -340,40 +485,75 @@ def run_cuda(args):
     if cfg.dense:
         pairs_per_rank, active_experts = float(cfg.S), 1
     peaks = load_peaks()
-    # dominant kernel: one FFN GEMM launch (GEMM1 and GEMM2 do the same work when H == I).
-    # Algorithmic work per launch: 2*R*H*I FLOP; bytes = the weights of this rank's experts that
-    # received rows, once, plus the R operand rows in and the R result rows out (R = routed
-    # pairs this rank's experts process).
-    gemm_flops = 2.0 * pairs_per_rank * cfg.H * cfg.I
-    gemm_bytes = (active_experts * cfg.I * cfg.H + pairs_per_rank * (cfg.H + cfg.I)) * float(eb)
-    gemm_ms = 0.5 * (phases["gemm1"] + phases["gemm2"])
-    gemm_ms = max_over_ranks(gemm_ms)
-    tflops = gemm_flops / (gemm_ms * 1e-3) / 1e12
-    gbs = gemm_bytes / (gemm_ms * 1e-3) / 1e9
     if cfg.torch_dtype == 0:
         # float layers run on FP32 FMA (as in the reference): nominal 148 SMs x 128 FMA x 1.965 GHz
-        peaks = dict(peaks, tflops=74.4, source="nominal fp32 FMA rate (no measured figure)")
+        peaks = dict(peaks, tflops=74.4, tflops_sustained=74.4,
+                     source="nominal fp32 FMA rate (no measured figure)")
     elif cfg.torch_dtype == 1:
-        peaks = dict(peaks, tflops=1125.0, source="nominal dense TF32 rate, half the bf16 figure (no measured figure)")
-    hbm_bound = gemm_bytes / (peaks["hbm"] * 1e9) > gemm_flops / (peaks["tflops"] * 1e12)
+        peaks = dict(peaks, tflops=1125.0, tflops_sustained=1125.0,
+                     source="nominal dense TF32 rate, half the bf16 figure (no measured figure)")
+    gate_flops = 0.0 if cfg.dense else 2.0 * cfg.S * cfg.H * cfg.E
+    ffn_flops = 4.0 * cfg.H * cfg.I * pairs_per_rank
+    total_flops = gate_flops + ffn_flops
+    remote_pairs = 0.0 if cfg.dense else pairs_per_rank * (world - 1) / world
+    link_bytes = 2.0 * remote_pairs * cfg.H * eb
+    t_roof_ms = max(total_flops / (peaks["tflops"] * 1e12), link_bytes / 770e9) * 1e3
+    if timeline is not None:
+        # Dominant kernel = the persistent kernel (router included when it runs inside): one launch
+        # per forward.  Algorithmic work per launch: the gate and FFN FLOPs above; bytes = the
+        # weights of this rank's experts that received rows (both GEMMs, once), the activations in,
+        # the R routed rows written into the cells, and the layer output out (R = routed pairs).
+        k_flops = (gate_flops if launches == args.steps else 0.0) + ffn_flops
+        k_bytes = (2.0 * active_experts * cfg.I * cfg.H + cfg.S * cfg.H * 2 + pairs_per_rank * cfg.H) * float(eb)
+        k_ms = max_over_ranks(timeline["end"])
+        kernel_name = "moe_flow_kernel (router, dispatch, plan, GEMM1, GEMM2, combine: one launch per forward)"
+    else:
+        # Separate launches: dominant kernel = one FFN GEMM launch (GEMM1 and GEMM2 do the same work
+        # when H == I).  Per launch: 2*R*H*I FLOP; bytes = the weights of this rank's experts that
+        # received rows, once, plus the R operand rows in and the R result rows out.
+        k_flops = 0.5 * ffn_flops
+        k_bytes = (active_experts * cfg.I * cfg.H + pairs_per_rank * (cfg.H + cfg.I)) * float(eb)
+        k_ms = max_over_ranks(0.5 * (phases["gemm1"] + phases["gemm2"]))
+        kernel_name = {0: "ffn_gemm_simt", 1: "ffn_gemm_tf32"}.get(cfg.torch_dtype, "ffn_gemm_tc2") + \
+            " (mean of the GEMM1 and GEMM2 launches)"
+    tflops = k_flops / (k_ms * 1e-3) / 1e12
+    gbs = k_bytes / (k_ms * 1e-3) / 1e9
+    hbm_bound = k_bytes / (peaks["hbm"] * 1e9) > k_flops / (peaks["tflops"] * 1e12)
     if hbm_bound:
         roof = dict(bound="hbm", achieved=gbs, peak=peaks["hbm"], unit="GB/s", frac=gbs / peaks["hbm"])
     else:
         roof = dict(bound="tensor", achieved=tflops, peak=peaks["tflops"], unit="TFLOP/s",
                     frac=tflops / peaks["tflops"])
-    # DRAM traffic per launch from the ncu capture of the quarter-size layer (155.3 MB, see
-    # profiles/), scaled by the units processed (experts x4, routed rows x4); one-GPU C3 only
-    roof["traffic"] = 621.2e6 if (world == 1 and args.workload == "C3") else None
-    roof.update(kernel={0: "ffn_gemm_simt", 1: "ffn_gemm_tf32"}.get(cfg.torch_dtype, "ffn_gemm_tc2") +
-                " (mean of the GEMM1 and GEMM2 launches)",
+    traffic, traffic_source = committed_traffic(args.workload, world, timeline is not None)
+    roof.update(traffic=traffic, traffic_source=traffic_source, kernel=kernel_name,
                 peak_source=peaks["source"], tensor_tflops=tflops, hbm_gbs=gbs,
-                algorithmic_bytes=gemm_bytes, algorithmic_flops=gemm_flops,
-                launch_ms=gemm_ms)
-    total_flops = (0.0 if cfg.dense else 2.0 * cfg.S * cfg.H * cfg.E) + 4.0 * cfg.H * cfg.I * pairs_per_rank
-    remote_pairs = 0.0 if cfg.dense else pairs_per_rank * (world - 1) / world
-    link_bytes = 2.0 * remote_pairs * cfg.H * eb
-    t_roof_ms = max(total_flops / (peaks["tflops"] * 1e12), link_bytes / 770e9) * 1e3
-    ms_per_step = ms_total / args.steps
+                algorithmic_bytes=k_bytes, algorithmic_flops=k_flops, launch_ms=k_ms,
+                # the whole layer against the slower of its FLOPs at the tensor peak and its
+                # dispatch + combine bytes at the measured 770 GB/s peer rate
+                layer_frac=t_roof_ms / ms_per_step, t_roof_ms=t_roof_ms, layer_flops=total_flops,
+                link_bytes_each_way=link_bytes, phases_ms=phases, timeline_ms=timeline,
+                routed_pairs_per_rank=pairs_per_rank)
+    if sustained is not None:
+        t_roof_sus = max(total_flops / (peaks["tflops_sustained"] * 1e12), link_bytes / 770e9) * 1e3
+        roof.update(sustained_ms_per_step=sustained["ms_per_step"], sustained_steps=sustained["steps"],
+                    sustained_clocks=sustained["clocks"], sustained_peak_tflops=peaks["tflops_sustained"],
+                    sustained_layer_frac=t_roof_sus / sustained["ms_per_step"])
+
+    # ---------------------------------------------------------------- parity of THIS run
+    parity = None
+    if not cfg.dense and args.parity:
+        exact, err, nrows, tol = parity_check(cfg, info, kleos, iP, oP, rank, world, device, gate_bias)
+        ok = exact and err <= tol
+        all_exact = min_over_ranks(1.0 if exact else 0.0) > 0.5
+        worst = max_over_ranks(err)
+        parity = dict(routing_exact=all_exact, out_rel_err=worst, tolerance=tol,
+                      rows_checked=nrows * world, tokens_routed=cfg.S * world,
+                      checker="oracle/moe_oracle.c on every rank, after the timed regions")
+        if min_over_ranks(1.0 if ok else 0.0) < 0.5:
+            if rank == 0:
+                print(json.dumps(dict(error="parity check failed", parity=parity)), flush=True)
+            kleos.finalize()
+            raise SystemExit(3)
 
     if rank == 0:
         tokens = cfg.S * world
@@ -385,16 +565,15 @@ def run_cuda(args):
             config=dict(workload=workload_desc,
                         experts_per_rank=info.local_experts,
                         parallelism=f"replicas{world}" if cfg.dense else f"ep{world}",
-                        l2="working set per step (weights + cells + activations) exceeds L2"),
+                        l2="working set per step (weights + cells + activations) exceeds L2",
+                        parity=parity, host_binding=numa),
             e2e=dict(value=tokens * args.steps / e2e_s, unit="tokens/s",
-                     h2d_bytes_per_step=act_elems * eb, d2h_bytes_per_step=act_elems * eb),
-            gpu_launches=(2 if cfg.dense else KERNELS_PER_FORWARD) * args.steps,
+                     h2d_bytes_per_step=act_elems * eb, d2h_bytes_per_step=act_elems * eb,
+                     copy_only_gbs=copy_gbs,
+                     copy_only_tokens_per_s=tokens * args.steps / copy_s),
+            gpu_launches=launches,
             clocks=clocks,
             roofline=roof,
-            layer_roofline=dict(t_roof_ms=t_roof_ms, frac=t_roof_ms / ms_per_step,
-                                flops=total_flops, link_bytes_each_way=link_bytes),
-            phases_ms=phases,
-            routed_pairs_per_rank=pairs_per_rank,
         )
         if args.cpu_baseline and world == 1:
             views = host_views_from_device(cfg, iP, world)
@@ -412,6 +591,21 @@ def run_cuda(args):
         dist.destroy_process_group()
 
 
+def committed_traffic(workload_name, world, persistent):
+    """DRAM bytes per launch of the dominant kernel from the committed profiler summary for this
+    workload (dram__bytes_read.sum + dram__bytes_write.sum of one capture), or (None, why)."""
+    path = os.path.join(ROOT, "profiles", "traffic.json")
+    try:
+        with open(path) as f:
+            table = json.load(f)
+        key = f"{workload_name}:{world}:{'flow' if persistent else 'phases'}"
+        if key in table:
+            return float(table[key]["bytes_per_launch"]), table[key]["source"]
+        return None, f"no capture for {key} in profiles/traffic.json"
+    except OSError:
+        return None, "profiles/traffic.json not present"
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -424,6 +618,10 @@ def main():
     ap.add_argument("--cpu-sample", type=int, default=0,
                     help="tokens in the CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
+    ap.add_argument("--no-parity", dest="parity", action="store_false",
+                    help="skip the comparison of this run's results with the CPU oracle")
+    ap.add_argument("--sustain-s", type=float, default=1.0,
+                    help="length of the second, long timed region in seconds (0: none)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

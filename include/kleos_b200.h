@@ -137,17 +137,25 @@ int kleos_debug_routing(int32_t* topk, int32_t* slots, uint32_t* counts, float* 
  * [6] combine, [7] whole forward.  n = number of floats the caller provides (>= 8). */
 int kleos_phase_times(float* ms, int n);
 
-/* 16-bit routed layers run dispatch, plan, both expert GEMMs and the combine as ONE persistent
- * kernel (the reference's arrangement, moe/moe.cuh:77-144), so phases [2]..[6] above are then
- * read from the blocks' global-timer stamps: [2] last row dispatched and [3] tile plan known, both
- * counted from the kernel's start; [4] span of the GEMM1 tiles; [5] from the last GEMM1 tile to
+/* 16-bit routed layers run the router, dispatch, plan, both expert GEMMs and the combine as ONE
+ * persistent kernel (the reference's arrangement, moe/moe.cuh:77-144), so the phases above are
+ * then read from the blocks' global-timer stamps: [0] gate GEMM + top-k up to the first grid
+ * barrier, [1] slots up to the second; [2] last row dispatched and [3] tile plan known, both
+ * counted from the second barrier; [4] span of the GEMM1 tiles; [5] from the last GEMM1 tile to
  * the last tile; [6] from the last tile to the kernel's end.  This call returns the raw
  * milestones of the most recent kleos_forward_bench, milliseconds after the earliest block's
  * start, latest block each: [0] 0, [1] plan known, [2] first tile begins (earliest block),
  * [3] last GEMM1 tile done, [4] last tile done, [5] last row dispatched, [6] last token combined,
- * [7] last block ends.  n >= 8.  KLEOS_E_STATE when the layer runs as separate launches
- * (float and TF32 layers, the dense layer, KLEOS_PHASES=1). */
+ * [7] last block ends, [8] routing done (first grid barrier), [9] slots done (second).  n >= 10.
+ * KLEOS_E_STATE when the layer runs as separate launches (float and TF32 layers, the dense
+ * layer, KLEOS_PHASES=1). */
 int kleos_flow_timeline(float* ms, int n);
+
+/* Kernels this library has launched for forward calls since kleos_initialize (every launch site
+ * counts itself; memory copies and memsets are not kernels).  A benchmark reads it before and
+ * after its timed region.  Negative (KLEOS_E_STATE) when not initialised.  No counterpart in the
+ * reference, whose forward is always one launch (moe/moe.cuh:198). */
+long long kleos_launch_count(void);
 
 /* Stall counters of the last GEMM1 and GEMM2 launches, only when the environment variable
  * KLEOS_GEMM_STATS=1 was set at initialise time: [2][blocks][12] clock cycles per block

@@ -98,7 +98,7 @@ def test_missing_key_and_uneven_sharding(tmp_path):
 
 def test_library_exports_every_declared_symbol():
     header = open(os.path.join(ROOT, "include", "kleos_b200.h")).read()
-    declared = set(re.findall(r"^(?:int|const char\*)\s+(kleos_\w+)\s*\(", header, flags=re.M))
+    declared = set(re.findall(r"^(?:int|long long|const char\*)\s+(kleos_\w+)\s*\(", header, flags=re.M))
     assert declared, "no declarations parsed from the header"
     lib = kleos.load_library()
     for name in declared:
