@@ -60,12 +60,12 @@ constexpr int kMaxPanels = 384;    // 128-row panels one rank can plan
 constexpr int kMaxLocal = 128;     // local experts per rank
 constexpr int kMaxCells = 256;     // (source, local expert) cells = number of experts
 constexpr int kUnitRows = 8;       // rows of one cell a transport warp sends between two publications
-constexpr int kCombineBlock = 32;  // tokens a transport warp classifies at a time
+constexpr int kCombineBlock = 8;   // tokens a warp classifies at a time (one per lane, first lanes)
 constexpr int kMaxPasses = 8;      // combine passes (tokens grouped by when their last row returns)
 constexpr int kRoleWarps = 10;     // producer, MMA, 4 read-back, 4 transport
 constexpr int kCtlBytes = 32768;
 constexpr int SMEM_BYTES = kSlices * SLICE_BYTES + 1024 + kCtlBytes;
-constexpr int kStampSlots = 10;    // per block: see Stamp
+constexpr int kStampSlots = 12;    // per block: see Stamp
 
 // Per-rank scheduler state in global memory.  Two copies: the forward of epoch n works on copy
 // n & 1 and clears the other one for the forward after it, so nothing is memset between launches.
@@ -82,7 +82,12 @@ struct Counters {
     unsigned panel_ret[kMaxPanels];   // read-back warps that finished a GEMM2 tile, per panel
 };
 
-enum Stamp { kStart = 0, kPlanned, kFirstTile, kLastGemm1, kLastTile, kDispatched, kCombined, kEnd, kRouted, kSlotted };
+enum Stamp {
+    kStart = 0, kPlanned, kFirstTile, kLastGemm1, kLastTile, kDispatched, kCombined, kEnd,
+    kRouted, kSlotted,  // the two grid barriers of the routing phase passed
+    kGateAcc,           // gate logits of the block's last token tile complete in tensor memory
+    kGateDone           // ... and turned into probabilities, choices and the tile histogram
+};
 
 struct Control {
     unsigned long long full[kSlices];    // used on the leader
@@ -565,6 +570,7 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                     break;
                 }
                 tc_fence_after();
+                if (stamp && q == 0 && lane == 0) stamp[kGateAcc] = global_ns();
                 const int row_w = rt * 2 * BM + (int)cta_rank * BM + q * 32;  // this warp's first token
                 const int row = row_w + lane;
                 const bool valid = row < a.S;
@@ -739,6 +745,7 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 for (int e = tid - 128; e < a.E; e += 128) hist_s[e] = 0;
                 asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (stamp && q == 0 && lane == 0) stamp[kGateDone] = global_ns();
             }
         }
 
@@ -959,24 +966,23 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     };
     if (stamp && tid == 0) stamp[kPlanned] = global_ns();
 
-    // The leader's producer claims tiles from the rank's task queue and hands every claimed index
-    // (or -1: no more work) to the roles of both blocks through an eight-entry ring.  The ring
+    // The leader's producer claims tiles from the rank's task queue (claim) and hands every claimed
+    // index (or -1: no more work) to the roles of both blocks through an eight-entry ring (hand_out).  The ring
     // needs no "empty" signal: the producer is at most one tile ahead of the MMA issuer (six
     // K slices of shared memory), the issuer at most two tiles ahead of the read-back warps (two
     // accumulators), and every role copies its entry into registers before it does anything
     // else, so at most four entries are live at any time.
-    auto hand_out = [&](uint32_t i) -> int {  // leader's producer thread only
-        int t = -1;
-        if (!*abort_flag && !ld_relaxed_gpu(&ctr->abort_all)) {
-            const unsigned c = atomicAdd(&ctr->tile_next, 1u);
-            if (c < (unsigned)total_tiles) t = (int)c;
-        }
+    auto claim = [&]() -> int {  // leader's producer thread only: next tile of the rank's queue, or -1
+        if (*abort_flag || ld_relaxed_gpu(&ctr->abort_all)) return -1;
+        const unsigned c = atomicAdd(&ctr->tile_next, 1u);
+        return c < (unsigned)total_tiles ? (int)c : -1;
+    };
+    auto hand_out = [&](uint32_t i, int t) {  // ... and its publication to the roles of both blocks
         const int slot = i % kRing;
         ctl->task_s[slot] = t;
         st_cluster_u32(map_to_cta(smem_u32(&ctl->task_s[slot]), 1), (uint32_t)t);
         mbar_arrive(&ctl->task_full[slot]);
         mbar_arrive_cluster(map_to_cta(smem_u32(&ctl->task_full[slot]), 1));
-        return t;
     };
     auto take = [&](uint32_t i, int where) -> int {  // every other role
         const int slot = i % kRing;
@@ -1001,13 +1007,15 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     // The combine, run by the transport warps once their rows are dispatched and by the read-back
     // warps once the tile stream has ended.
     auto run_combine = [&]() {
-        // (2) combine.  Tokens are visited in passes: the experts of one rank finish in the
-        // order of their local index, so a token's rows are all back once the LAST of its experts
-        // (by local index) has returned; pass q takes the tokens whose last expert falls into
-        // the q-th part of that order.  An item is (pass, block of 32 tokens); the warp that
-        // claims it waits (bounded) for the return flags of each token's panels and gathers the
-        // rows (reference: subscriber decodes returned tiles into combine tasks,
-        // os/subscriber.cuh:187-332; the sum itself processor.cuh:110-168).
+        // Tokens are visited in passes: the experts of one rank finish in the order of their local
+        // index, so a token's rows are all back once the LAST of its experts (by local index) has
+        // returned; pass q takes the tokens whose last expert falls into the q-th part of that
+        // order.  An item is (pass, block of eight tokens): the first eight lanes each load one
+        // token's choices, slots, gate probabilities and mCw; the warp then takes the block's
+        // tokens of this pass one by one, waits (bounded) for the return flags of the token's
+        // panels and gathers the rows (reference: the subscriber decodes returned tiles into
+        // combine tasks, os/subscriber.cuh:187-332; the sum itself processor.cuh:110-168).
+        constexpr int KMAX = KT > 0 ? KT : kMaxTopK;
         const int passes = min(a.nLx, kMaxPasses);
         const int nblk = (a.S + kCombineBlock - 1) / kCombineBlock;
         const unsigned total_items = (unsigned)(passes * nblk);
@@ -1026,12 +1034,28 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             const int q = (int)item / nblk, b = (int)item - q * nblk;
             const int t_mine = b * kCombineBlock + lane;
             int cls = -1;  // pass in which this lane's token is handled
-            if (t_mine < a.S) {
+            int e_m[KMAX], sl_m[KMAX];
+            float p_m[KMAX], w_m = 1.f;
+#pragma unroll
+            for (int j = 0; j < KMAX; ++j) {
+                e_m[j] = 0;
+                sl_m[j] = kDropped;
+                p_m[j] = 0.f;
+            }
+            if (lane < kCombineBlock && t_mine < a.S) {
                 cls = 0;
-                for (int j = 0; j < K; ++j) {
-                    const int e = __ldcg(a.topk + (size_t)t_mine * K + j);
-                    const int sl = __ldcg(a.slots + (size_t)t_mine * K + j);
-                    if (sl != kDropped) cls = max(cls, (e % a.nLx) * passes / a.nLx);
+#pragma unroll
+                for (int j = 0; j < KMAX; ++j)
+                    if (j < K) {
+                        e_m[j] = __ldcg(a.topk + (size_t)t_mine * K + j);
+                        sl_m[j] = __ldcg(a.slots + (size_t)t_mine * K + j);
+                        if (sl_m[j] != kDropped) cls = max(cls, (e_m[j] % a.nLx) * passes / a.nLx);
+                    }
+                if (cls == q) {
+                    w_m = __ldcg(a.mcw + t_mine);
+#pragma unroll
+                    for (int j = 0; j < KMAX; ++j)
+                        if (j < K) p_m[j] = ld_cg_elem(probs + (size_t)t_mine * a.PX + e_m[j]);
                 }
             }
             unsigned todo = __ballot_sync(0xffffffffu, cls == q);
@@ -1039,37 +1063,34 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 const int src_lane = __ffs(todo) - 1;
                 todo &= todo - 1;
                 const int t = b * kCombineBlock + src_lane;
-                constexpr int KMAX = KT > 0 ? KT : kMaxTopK;
                 const TE* yrow[KMAX];
                 float p[KMAX];
                 bool failed = false;
-    #pragma unroll
+#pragma unroll
                 for (int j = 0; j < KMAX; ++j) {
+                    const int e = __shfl_sync(0xffffffffu, e_m[j], src_lane);
+                    const int sl = __shfl_sync(0xffffffffu, sl_m[j], src_lane);
+                    p[j] = __shfl_sync(0xffffffffu, p_m[j], src_lane);
                     yrow[j] = nullptr;
-                    p[j] = 0.f;
-                    if (j < K) {
-                        const int e = __ldcg(a.topk + (size_t)t * K + j);
-                        const int sl = __ldcg(a.slots + (size_t)t * K + j);
-                        p[j] = ld_cg_elem(probs + (size_t)t * a.PX + e);
-                        if (sl != kDropped) {
-                            yrow[j] = ycell + ((size_t)e * a.pEC + sl) * a.H;
-                            if (lane == j) {
-                                unsigned long long v;
-                                if (!wait_flag(ypflag + (size_t)e * TCM + sl / kTileM, a.epoch, budget, &v)) {
-                                    give_up(KLEOS_AT_COMBINE_WAIT, e);
-                                    failed = true;
-                                }
+                    if (j < K && sl != kDropped) {
+                        yrow[j] = ycell + ((size_t)e * a.pEC + sl) * a.H;
+                        if (lane == j) {
+                            unsigned long long v;
+                            if (!wait_flag(ypflag + (size_t)e * TCM + sl / kTileM, a.epoch, budget, &v)) {
+                                give_up(KLEOS_AT_COMBINE_WAIT, e);
+                                failed = true;
                             }
                         }
                     }
                 }
+                const float w = __shfl_sync(0xffffffffu, w_m, src_lane);
+                __syncwarp();  // the polling lanes' acquires order every lane's row loads behind the flags
                 failed = __any_sync(0xffffffffu, failed) || *abort_flag;
                 if (failed) {
                     todo = 0;
                     break;
                 }
-                combine_row<TE, KT>(yrow, p, __ldcg(a.mcw + t), static_cast<TE*>(a.out) + (size_t)t * a.H,
-                                    chunks, lane, K);
+                combine_row<TE, KT>(yrow, p, w, static_cast<TE*>(a.out) + (size_t)t * a.H, chunks, lane, K);
             }
         }
     };
@@ -1079,8 +1100,19 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         if (lane == 0) {
             asm volatile("fence.proxy.async;" ::: "memory");
             uint32_t it = 0;
+            // The leader claims one tile ahead: the round trip of the claim for tile i+1 runs under
+            // the loads of tile i.  (Claims stay in order, so the tile a block waits for is still
+            // either running or held by a block whose current tile has a smaller index.)
+            int ahead = leader ? claim() : -1;
             for (uint32_t i = 0;; ++i) {
-                const int t = leader ? hand_out(i) : take(i, KLEOS_AT_GEMM_PRODUCER);
+                int t;
+                if (leader) {
+                    t = *abort_flag ? -1 : ahead;
+                    hand_out(i, t);
+                    if (t >= 0) ahead = claim();
+                } else {
+                    t = take(i, KLEOS_AT_GEMM_PRODUCER);
+                }
                 if (t < 0) break;
                 const Tile ti = decode_tile(ctl, t, a.nLx);
                 // the block without a panel of its own re-reads the first one and discards
@@ -1214,6 +1246,54 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         const int q = warp - 4;
         const uint32_t acc_empty0 = smem_u32(&ctl->acc_empty[0]);
         const int TCM = a.pEC / kTileM;
+        // Publication of a finished tile.  The stores of the tile must be visible before its
+        // counter moves, which costs a fence that waits for those stores; issued right behind
+        // them it would hold this warp for microseconds per tile.  So a tile is published when
+        // the warp next has nothing to do (its next accumulator is not ready yet) or, at the
+        // latest, just before it reads the next accumulator back: by then the stores have
+        // drained and the fence returns at once.
+        int pend_phase = 0, pend_panel = -1;
+        auto publish = [&]() {
+            if (pend_panel < 0) return;
+            if (pend_phase == 0) {
+                // GEMM1: the pair's counter releases its GEMM2 tiles (reference processor.cuh:717-729)
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) {
+                    atomicAdd(&ctr->pair_done[pend_panel], 1u);
+                    if (stamp && q == 0) stamp[kLastGemm1] = global_ns();
+                }
+            } else {
+                // GEMM2: one return flag per (expert, 128-row panel), raised by the warp that stores
+                // the panel's last piece (reference: one signal per returned tile, processor.cuh:745-769)
+                __threadfence_system();
+                __syncwarp();
+                if (lane == 0) {
+                    const unsigned prev = atomicAdd(&ctr->panel_ret[pend_panel], 1u);
+                    if (prev + 1u == 4u * (unsigned)NT2) {
+                        const PanelEntry pp = panel_of(ctl, pend_panel);
+                        const int cell = pp.src * a.nLx + pp.le;
+                        const int r0 = pp.row_base - cell * a.pEC;
+                        const size_t e_global = (size_t)a.rank * a.nLx + pp.le;
+                        if (!a.suppress)
+                            st_release_sys(reinterpret_cast<unsigned long long*>(a.peers.arena[pp.src] + a.lay.ypflag) +
+                                               (e_global * TCM + r0 / kTileM),
+                                           make_flag(a.epoch, 1u));
+                        const unsigned done = atomicAdd(&ctr->panels_returned, 1u);
+                        if (done + 1u == (unsigned)ctl->total_panels && !a.suppress) {
+                            // everything this rank's experts owed has been returned: tell every
+                            // source (they leave the forward only after all owners said so)
+                            __threadfence_system();
+                            for (int r = 0; r < a.world; ++r)
+                                st_release_sys(reinterpret_cast<unsigned long long*>(a.peers.arena[r] + a.lay.yflag) + a.rank,
+                                               make_flag(a.epoch, 1u));
+                        }
+                    }
+                }
+            }
+            pend_panel = -1;
+            __syncwarp();
+        };
         for (uint32_t i = 0;; ++i) {
             const int t = take(i, KLEOS_AT_GEMM_EPILOGUE);
             if (t < 0) break;
@@ -1245,10 +1325,16 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 }
                 __syncwarp();
             }
+            {
+                // (warp-uniform decision: lane 0's view)
+                const int ready = __shfl_sync(0xffffffffu, mbar_try_wait(&ctl->acc_full[buf], use & 1) ? 1 : 0, 0);
+                if (!ready) publish();  // idle: publish the last tile now
+            }
             if (!mbar_wait(&ctl->acc_full[buf], use & 1, budget, abort_flag)) {
                 if (!*abort_flag && lane == 0) give_up(KLEOS_AT_GEMM_EPILOGUE, t);
                 break;
             }
+            publish();
             tc_fence_after();
             const int n0 = ti.nt * BN;
             const uint32_t taddr = tmem_base + buf * BN + (static_cast<uint32_t>(q * 32) << 16);
@@ -1272,43 +1358,13 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 read_back<TE, 2>(taddr, ctl->bias_s[q], ctl->stage_s[q], obase, (size_t)a.H, rows_w, n0, N,
                                  lane, acc_empty_leader);
             }
-            // completion bookkeeping: every read-back warp of the pair counts, with or without rows
-            if (ti.phase == 0) {
-                __threadfence();
-                __syncwarp();
-                if (lane == 0) {
-                    atomicAdd(&ctr->pair_done[ti.panel0], 1u);
-                    if (stamp && q == 0) stamp[kLastGemm1] = global_ns();
-                }
-            } else if (have_panel) {
-                // one return flag per (expert, 128-row panel), raised by the warp that stores the
-                // panel's last piece (reference: one signal per returned tile, processor.cuh:745-769)
-                __threadfence_system();
-                __syncwarp();
-                if (lane == 0) {
-                    const unsigned prev = atomicAdd(&ctr->panel_ret[my_panel], 1u);
-                    if (prev + 1u == 4u * (unsigned)NT2) {
-                        const int cell = p.src * a.nLx + p.le;
-                        const int r0 = p.row_base - cell * a.pEC;
-                        const size_t e_global = (size_t)a.rank * a.nLx + p.le;
-                        if (!a.suppress)
-                            st_release_sys(reinterpret_cast<unsigned long long*>(a.peers.arena[p.src] + a.lay.ypflag) +
-                                               (e_global * TCM + r0 / kTileM),
-                                           make_flag(a.epoch, 1u));
-                        const unsigned done = atomicAdd(&ctr->panels_returned, 1u);
-                        if (done + 1u == (unsigned)ctl->total_panels && !a.suppress) {
-                            // everything this rank's experts owed has been returned: tell every
-                            // source (they leave the forward only after all owners said so)
-                            __threadfence_system();
-                            for (int r = 0; r < a.world; ++r)
-                                st_release_sys(reinterpret_cast<unsigned long long*>(a.peers.arena[r] + a.lay.yflag) + a.rank,
-                                               make_flag(a.epoch, 1u));
-                        }
-                    }
-                }
-            }
+            // completion bookkeeping: every read-back warp of the pair counts, with or without rows;
+            // it is published later (see publish above)
+            pend_phase = ti.phase;
+            pend_panel = ti.phase == 0 ? ti.panel0 : (have_panel ? my_panel : -1);
             if (stamp && q == 0 && lane == 0) stamp[kLastTile] = global_ns();
         }
+        if (!*abort_flag) publish();
         // no tiles left: help with the combine of the tokens whose rows return last
         run_combine();
         if (lane == 0) atomicAdd(&ctl->roles_done, 1);

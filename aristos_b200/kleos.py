@@ -207,7 +207,7 @@ def route_static(A, Wg, gate_bias, S, H, E, K, torch_dtype, probs, topk, mcw, st
 
 
 FLOW_MILESTONES = ("start", "planned", "first_tile", "last_gemm1_tile", "last_tile", "dispatched",
-                   "combined", "end", "routed", "slotted")
+                   "combined", "end", "routed", "slotted", "gate_logits", "gate_done")
 
 
 def flow_timeline() -> dict:

@@ -78,21 +78,12 @@ def load_peaks():
 
 def bind_to_gpu_numa_node(local_rank: int):
     """Pins this process (and therefore the pinned host buffers it allocates afterwards) to the
-    CPUs of the NUMA node the GPU hangs off.  Reads sysfs only; returns what it did."""
+    CPUs of the NUMA node the GPU hangs off.  Queries only (nvidia-smi, sysfs); returns what it did."""
     try:
-        import torch
-        bdf = torch.cuda.get_device_properties(local_rank).pci_bus_id  # e.g. 0000:1B:00.0
-    except Exception:
-        bdf = None
-    try:
-        if not bdf:
-            import pynvml
-            pynvml.nvmlInit()
-            h = pynvml.nvmlDeviceGetHandleByIndex(local_rank)
-            bdf = pynvml.nvmlDeviceGetPciInfo(h).busId
-            bdf = bdf.decode() if isinstance(bdf, bytes) else bdf
-        bdf = bdf.lower()
-        if len(bdf.split(":")[0]) == 8:
+        bdf = subprocess.run(["nvidia-smi", "-i", str(local_rank), "--query-gpu=pci.bus_id",
+                              "--format=csv,noheader"], capture_output=True, text=True,
+                             timeout=20).stdout.strip().lower()
+        if len(bdf.split(":")[0]) == 8:  # 00000000:1b:00.0 -> 0000:1b:00.0
             bdf = bdf[4:]
         with open(f"/sys/bus/pci/devices/{bdf}/numa_node") as f:
             node = int(f.read().strip())
@@ -106,9 +97,10 @@ def bind_to_gpu_numa_node(local_rank: int):
         allowed = cpus & os.sched_getaffinity(0)
         if allowed:
             os.sched_setaffinity(0, allowed)
-        return dict(numa_node=node, cpus=len(allowed))
+            return dict(numa_node=node, cpus=len(allowed))
+        return dict(numa_node=node, note="none of the node's CPUs is available to this process")
     except Exception as exc:  # no sysfs entry, no permission: run unbound
-        return dict(numa_node=None, note=f"not bound: {type(exc).__name__}")
+        return dict(numa_node=None, note=f"not bound: {type(exc).__name__}: {exc}"[:160])
 
 
 class ClockSampler:

@@ -146,7 +146,8 @@ int kleos_phase_times(float* ms, int n);
  * milestones of the most recent kleos_forward_bench, milliseconds after the earliest block's
  * start, latest block each: [0] 0, [1] plan known, [2] first tile begins (earliest block),
  * [3] last GEMM1 tile done, [4] last tile done, [5] last row dispatched, [6] last token combined,
- * [7] last block ends, [8] routing done (first grid barrier), [9] slots done (second).  n >= 10.
+ * [7] last block ends, [8] routing done (first grid barrier), [9] slots done (second),
+ * [10] gate logits of the last token tile complete, [11] ... and turned into choices.  n >= 12.
  * KLEOS_E_STATE when the layer runs as separate launches (float and TF32 layers, the dense
  * layer, KLEOS_PHASES=1). */
 int kleos_flow_timeline(float* ms, int n);

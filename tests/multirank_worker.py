@@ -84,10 +84,10 @@ def main():
     st = kleos.last_status()
     routing = kleos.debug_routing(info)
     o = oP.cpu().numpy().view(raw.dtype)
-    out = synth.decode(o[cfg.S * cfg.PX:], cfg.torch_dtype).reshape(cfg.S, cfg.H)
-    if host_mode:
-        out_h = synth.decode(host_out.numpy().view(raw.dtype), cfg.torch_dtype).reshape(cfg.S, cfg.H)
-        assert np.array_equal(out_h, out), "host copy of the layer output differs from the device's"
+    if host_mode:  # the pipelined entry point delivers the layer output to the host buffer only
+        out = synth.decode(host_out.numpy().view(raw.dtype), cfg.torch_dtype).reshape(cfg.S, cfg.H)
+    else:
+        out = synth.decode(o[cfg.S * cfg.PX:], cfg.torch_dtype).reshape(cfg.S, cfg.H)
     rows = spec.get("rows")
     if rows is not None:
         out = out[np.asarray(rows, dtype=np.int64)]
