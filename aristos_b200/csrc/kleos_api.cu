@@ -68,6 +68,9 @@ struct State {
     int flow_grid = 0;                       // blocks of the persistent kernel (co-resident pairs x 2)
     flow::Counters* flow_ctr = nullptr;      // [2] scheduler state, see moe_flow.cuh
     long long* flow_stamps = nullptr;        // [flow_grid][kStampSlots] timeline of a timed forward
+    long long* flow_stalls = nullptr;        // [flow_grid][kStallSlots] wait cycles of a timed forward
+    int flow_debug = 0;                      // KLEOS_FLOW_DEBUG
+    double clock_khz = 0;
     float flow_ms[flow::kStampSlots] = {};   // last kleos_forward_bench: milestones after kernel start
 
     // symmetric arena
@@ -503,6 +506,7 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed, const S
             fa.topk = g.topk; fa.slots = g.slots; fa.mcw = g.mcw; fa.cell_tokens = g.cell_tokens;
             fa.counts = g.counts; fa.peers = g.peers; fa.lay = g.lay; fa.ctr = g.flow_ctr;
             fa.status = g.status; fa.stamps = timed ? g.flow_stamps : nullptr;
+            fa.stalls = timed ? g.flow_stalls : nullptr; fa.debug = g.flow_debug;
             fa.wait_cycles = g.wait_cycles; fa.S = c.S; fa.H = c.H; fa.I = c.I; fa.E = c.E; fa.K = c.K;
             fa.PX = c.PX; fa.EC = c.EC; fa.pEC = c.pEC; fa.nLx = g.nLx; fa.rank = g.rank;
             fa.world = g.world; fa.epoch = g.epoch; fa.suppress = g.suppress_return_flag ? 1 : 0;
@@ -511,9 +515,12 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed, const S
             fa.sub = (long long)g.world * c.EC >= 512 ? 2 : 1;
             fa.fuse_route = routed_in_kernel ? 1 : 0;
             fa.Wg = s.Wg; fa.gate_bias = g.bias; fa.tile_hist = g.tile_hist; fa.tie_eps = 1e-4f;
-            if (timed)
+            if (timed) {
                 KLEOS_CUDA(cudaMemsetAsync(g.flow_stamps, 0,
                                            sizeof(long long) * g.flow_grid * flow::kStampSlots, st));
+                KLEOS_CUDA(cudaMemsetAsync(g.flow_stalls, 0,
+                                           sizeof(long long) * g.flow_grid * flow::kStallSlots, st));
+            }
             for (int i = 0; i < 4; ++i) KLEOS_CUDA(mark());  // dispatch .. GEMM2: inside the kernel
             launch_flow<T>(c.hidden_act, c.K, st, fa, act_map);
         }
@@ -686,7 +693,7 @@ void release_all() {
     cudaFree(g.y1); cudaFree(g.topk); cudaFree(g.slots); cudaFree(g.cell_tokens);
     cudaFree(g.refine_list); cudaFree(g.refine_count); cudaFree(g.tile_hist); cudaFree(g.refine_done); cudaFree(g.refine_logits); cudaFree(g.le_start); cudaFree(g.mcw);
     cudaFree(g.bias); cudaFree(g.counts); cudaFree(g.done_dispatch); cudaFree(g.done_gemm2);
-    cudaFree(g.cell_counts); cudaFree(g.flow_ctr); cudaFree(g.flow_stamps); cudaFree(g.panels); cudaFree(g.status); cudaFree(g.gemm_stats);
+    cudaFree(g.cell_counts); cudaFree(g.flow_ctr); cudaFree(g.flow_stamps); cudaFree(g.flow_stalls); cudaFree(g.panels); cudaFree(g.status); cudaFree(g.gemm_stats);
     cudaFree(g.col_partial); cudaFree(g.gate_stats);
     for (auto& e : g.ev)
         if (e) cudaEventDestroy(e);
@@ -808,6 +815,7 @@ static int initialize_impl(const char* config_json_path, int rank, int world, co
         return fail(KLEOS_E_UNSUPPORTED, "device is sm_%d%d; this library is built for sm_100a only",
                     prop.major, prop.minor);
     g.sm_count = prop.multiProcessorCount;
+    g.clock_khz = prop.clockRate;
     g.cfg = cfg;
     g.rank = rank;
     g.world = world;
@@ -889,6 +897,8 @@ static int initialize_impl(const char* config_json_path, int rank, int world, co
         if ((rc = dev_alloc(&ctr, 2))) return rc;
         g.flow_ctr = ctr;
         if ((rc = dev_alloc(&g.flow_stamps, (size_t)g.flow_grid * flow::kStampSlots))) return rc;
+        if ((rc = dev_alloc(&g.flow_stalls, (size_t)g.flow_grid * flow::kStallSlots))) return rc;
+        if (const char* dbg = std::getenv("KLEOS_FLOW_DEBUG")) g.flow_debug = std::atoi(dbg);
     }
 
     for (int r = 0; r < kMaxWorld; ++r) g.peers.arena[r] = nullptr;
@@ -1220,6 +1230,27 @@ int kleos_phase_times(float* ms, int n) {
 }
 
 long long kleos_launch_count(void) { return g.initialised ? (long long)g.launches : (long long)KLEOS_E_STATE; }
+
+int kleos_debug_flow_stalls(float* ms, int n) {
+    if (!ms || n < flow::kStallSlots) return fail(KLEOS_E_ARG, "need room for %d floats", flow::kStallSlots);
+    if (!g.initialised || !g.use_flow) return fail(KLEOS_E_STATE, "this layer does not run the persistent kernel");
+    { const int src = sync_last_forward(); if (src) return src; }
+    std::vector<long long> v((size_t)g.flow_grid * flow::kStallSlots);
+    KLEOS_CUDA(cudaMemcpy(v.data(), g.flow_stalls, v.size() * sizeof(long long), cudaMemcpyDeviceToHost));
+    for (int k = 0; k < flow::kStallSlots; ++k) {
+        double sum = 0;
+        int cnt = 0;
+        for (int b = 0; b < g.flow_grid; ++b) {
+            const long long c = v[(size_t)b * flow::kStallSlots + k];
+            if (c > 0) {
+                sum += (double)c;
+                ++cnt;
+            }
+        }
+        ms[k] = cnt ? (float)(sum / cnt / g.clock_khz) : 0.f;  // cycles / kHz = milliseconds
+    }
+    return KLEOS_OK;
+}
 
 int kleos_flow_timeline(float* ms, int n) {
     if (!ms || n < flow::kStampSlots) return fail(KLEOS_E_ARG, "need room for %d floats", flow::kStampSlots);

@@ -66,6 +66,7 @@ constexpr int kRoleWarps = 10;     // producer, MMA, 4 read-back, 4 transport
 constexpr int kCtlBytes = 32768;
 constexpr int SMEM_BYTES = kSlices * SLICE_BYTES + 1024 + kCtlBytes;
 constexpr int kStampSlots = 12;    // per block: see Stamp
+constexpr int kStallSlots = 12;    // per block: see Stall
 
 // Per-rank scheduler state in global memory.  Two copies: the forward of epoch n works on copy
 // n & 1 and clears the other one for the forward after it, so nothing is memset between launches.
@@ -87,6 +88,22 @@ enum Stamp {
     kRouted, kSlotted,  // the two grid barriers of the routing phase passed
     kGateAcc,           // gate logits of the block's last token tile complete in tensor memory
     kGateDone           // ... and turned into probabilities, choices and the tile histogram
+};
+
+// Cycles per block, tile stream only (a tuning aid, filled when Args::stalls is set).
+enum Stall {
+    kProdEmpty = 0,  // producer: waiting for a free pipeline stage
+    kProdReady,      // producer: waiting for a cell's data flag or a pair's GEMM1 counter
+    kProdTotal,      // producer: whole tile stream
+    kMmaAcc,         // MMA issuer: waiting for a free accumulator
+    kMmaFull,        // MMA issuer: waiting for operands
+    kMmaTask,        // MMA issuer: waiting for the next claimed tile
+    kMmaTotal,
+    kBackAcc,        // read-back warp 0: waiting for a finished accumulator
+    kBackPublish,    // ... publishing (fence + counters)
+    kBackRead,       // ... reading back and storing
+    kBackTotal,
+    kStallUnused
 };
 
 struct Control {
@@ -132,6 +149,8 @@ struct Args {
     Counters* ctr;           // [2]
     DeviceStatus* status;
     long long* stamps;       // optional [grid][kStampSlots] global-timer values, or null
+    long long* stalls;       // optional [grid][kStallSlots] cycles the roles of the tile stream spent waiting, or null
+    int debug;               // tuning switches (KLEOS_FLOW_DEBUG): 1 = combine only after the last tile
     long long wait_cycles;
     int S, H, I, E, K, PX, EC, pEC, nLx, rank, world;
     uint32_t epoch;
@@ -420,6 +439,15 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     const long long budget = a.wait_cycles;
     long long* stamp = a.stamps ? a.stamps + (size_t)blockIdx.x * kStampSlots : nullptr;
     if (stamp && tid == 0) stamp[kStart] = global_ns();
+    long long* stall = a.stalls ? a.stalls + (size_t)blockIdx.x * kStallSlots : nullptr;
+    // waits of the tile stream, timed only when the caller asked for the counters
+    auto timed_wait = [&](unsigned long long* bar, uint32_t parity, int slot) -> bool {
+        if (!stall) return mbar_wait(bar, parity, budget, abort_flag);
+        const long long c0 = clock64();
+        const bool ok = mbar_wait(bar, parity, budget, abort_flag);
+        stall[slot] += clock64() - c0;
+        return ok;
+    };
 
     // Giving up: remember where, stop this block and, through the rank's abort word that every
     // block's monitor warp mirrors, all others.
@@ -1104,6 +1132,7 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             // the loads of tile i.  (Claims stay in order, so the tile a block waits for is still
             // either running or held by a block whose current tile has a smaller index.)
             int ahead = leader ? claim() : -1;
+            const long long c_begin = clock64();
             for (uint32_t i = 0;; ++i) {
                 int t;
                 if (leader) {
@@ -1124,6 +1153,7 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 const CUtensorMap* ma = ti.phase ? &map_y1 : &map_x;
                 const CUtensorMap* mb = ti.phase ? &map_w2 : &map_w1;
                 bool ok = true;
+                const long long c_ready = stall ? clock64() : 0;
                 if (ti.phase == 0) {
                     // rows of this panel's cell may still be on their way from the source rank
                     // (reference: the subscriber polls the first-stage flag, os/subscriber.cuh:107)
@@ -1159,11 +1189,12 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                     ctl->pair_ready_s[ti.panel0] = 1;
                     asm volatile("fence.proxy.async;" ::: "memory");
                 }
+                if (stall) stall[kProdReady] += clock64() - c_ready;
                 if (!ok) continue;  // the next claim returns -1 (abort is up) and ends every role
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const int s = it % NST;
                     const uint32_t ph = stage_parity(s, it);
-                    if (!mbar_wait(&ctl->empty[s], ph ^ 1, budget, abort_flag)) {
+                    if (!timed_wait(&ctl->empty[s], ph ^ 1, kProdEmpty)) {
                         if (!*abort_flag) give_up(KLEOS_AT_GEMM_PRODUCER, t);
                         break;
                     }
@@ -1178,6 +1209,7 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                     }
                 }
             }
+            if (stall) stall[kProdTotal] = clock64() - c_begin;
             atomicAdd(&ctl->roles_done, 1);
         }
         __syncwarp();
@@ -1186,13 +1218,16 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         if (lane == 0) {
             if (leader) {
                 uint32_t it = 0;
+                const long long c_begin = clock64();
                 for (uint32_t i = 0;; ++i) {
+                    const long long c_task = stall ? clock64() : 0;
                     const int t = take(i, KLEOS_AT_GEMM_MMA);
+                    if (stall) stall[kMmaTask] += clock64() - c_task;
                     if (t < 0) break;
                     const Tile ti = decode_tile(ctl, t, a.nLx);
                     const int KS = (ti.phase ? a.I : a.H) / BK, KB = (KS + SUB - 1) / SUB;
                     const uint32_t tn = route_tiles + i, buf = tn & 1, use = tn >> 1;
-                    if (!mbar_wait(&ctl->acc_empty[buf], (use & 1) ^ 1, budget, abort_flag)) {
+                    if (!timed_wait(&ctl->acc_empty[buf], (use & 1) ^ 1, kMmaAcc)) {
                         if (!*abort_flag) give_up(KLEOS_AT_GEMM_MMA, t);
                         break;
                     }
@@ -1202,7 +1237,7 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                     for (int kb = 0; kb < KB; ++kb, ++it) {
                         const int s = it % NST;
                         const uint32_t ph = stage_parity(s, it);
-                        if (!mbar_wait(&ctl->full[s], ph, budget, abort_flag)) {
+                        if (!timed_wait(&ctl->full[s], ph, kMmaFull)) {
                             if (!*abort_flag) give_up(KLEOS_AT_GEMM_MMA, t);
                             ok = false;
                             break;
@@ -1227,6 +1262,7 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                     umma_commit_pair(map_to_cta(f_local, 0));
                     umma_commit_pair(map_to_cta(f_local, 1));
                 }
+                if (stall) stall[kMmaTotal] = clock64() - c_begin;
             }
             atomicAdd(&ctl->roles_done, 1);
         }
@@ -1294,6 +1330,8 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             pend_panel = -1;
             __syncwarp();
         };
+        const bool tally = stall && q == 0 && lane == 0;
+        const long long c_begin = clock64();
         for (uint32_t i = 0;; ++i) {
             const int t = take(i, KLEOS_AT_GEMM_EPILOGUE);
             if (t < 0) break;
@@ -1325,16 +1363,29 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 }
                 __syncwarp();
             }
+            long long c0 = tally ? clock64() : 0;
             {
                 // (warp-uniform decision: lane 0's view)
                 const int ready = __shfl_sync(0xffffffffu, mbar_try_wait(&ctl->acc_full[buf], use & 1) ? 1 : 0, 0);
                 if (!ready) publish();  // idle: publish the last tile now
             }
+            if (tally) {
+                stall[kBackPublish] += clock64() - c0;
+                c0 = clock64();
+            }
             if (!mbar_wait(&ctl->acc_full[buf], use & 1, budget, abort_flag)) {
                 if (!*abort_flag && lane == 0) give_up(KLEOS_AT_GEMM_EPILOGUE, t);
                 break;
             }
+            if (tally) {
+                stall[kBackAcc] += clock64() - c0;
+                c0 = clock64();
+            }
             publish();
+            if (tally) {
+                stall[kBackPublish] += clock64() - c0;
+                c0 = clock64();
+            }
             tc_fence_after();
             const int n0 = ti.nt * BN;
             const uint32_t taddr = tmem_base + buf * BN + (static_cast<uint32_t>(q * 32) << 16);
@@ -1362,9 +1413,11 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             // it is published later (see publish above)
             pend_phase = ti.phase;
             pend_panel = ti.phase == 0 ? ti.panel0 : (have_panel ? my_panel : -1);
+            if (tally) stall[kBackRead] += clock64() - c0;
             if (stamp && q == 0 && lane == 0) stamp[kLastTile] = global_ns();
         }
         if (!*abort_flag) publish();
+        if (tally) stall[kBackTotal] = clock64() - c_begin;
         // no tiles left: help with the combine of the tokens whose rows return last
         run_combine();
         if (lane == 0) atomicAdd(&ctl->roles_done, 1);
@@ -1436,6 +1489,13 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             }
         }
         if (stamp && warp == 8 && lane == 0) stamp[kDispatched] = global_ns();
+        if (a.debug & 1) {
+            // tuning switch: leave the memory system to the tile stream until its last tile is done
+            // (the producer, the issuer and the four read-back warps have all signed off)
+            const long long t0 = clock64();
+            while (*reinterpret_cast<volatile int*>(&ctl->roles_done) < 6 && !*abort_flag && clock64() - t0 < budget)
+                __nanosleep(1000);
+        }
 
         run_combine();
         if (stamp && warp == 8 && lane == 0) stamp[kCombined] = global_ns();

@@ -27,7 +27,7 @@ EXPORTS = (
     "kleos_forward", "kleos_forward_bench", "kleos_forward_host", "kleos_forward_host_async",
     "kleos_host_sync", "kleos_get_rank",
     "kleos_local_experts", "kleos_get_info", "kleos_last_status", "kleos_clear_status", "kleos_debug_routing",
-    "kleos_phase_times", "kleos_flow_timeline", "kleos_launch_count", "kleos_debug_gemm_stats", "kleos_debug_suppress_return_flag", "kleos_gate_stats", "kleos_plan_placement", "kleos_placement_model", "kleos_route_static", "kleos_finalize", "kleos_error_string",
+    "kleos_phase_times", "kleos_flow_timeline", "kleos_debug_flow_stalls", "kleos_launch_count", "kleos_debug_gemm_stats", "kleos_debug_suppress_return_flag", "kleos_gate_stats", "kleos_plan_placement", "kleos_placement_model", "kleos_route_static", "kleos_finalize", "kleos_error_string",
 )
 
 PHASE_NAMES = ("route", "slots", "dispatch", "plan", "gemm1", "gemm2", "combine", "total")
@@ -218,6 +218,21 @@ def flow_timeline() -> dict:
     lib.kleos_flow_timeline.argtypes = [ctypes.POINTER(ctypes.c_float), ctypes.c_int]
     _check(lib.kleos_flow_timeline(buf, len(FLOW_MILESTONES)), "kleos_flow_timeline")
     return {n: float(buf[i]) for i, n in enumerate(FLOW_MILESTONES)}
+
+
+FLOW_STALLS = ("producer_wait_stage", "producer_wait_data", "producer_total", "mma_wait_accumulator",
+               "mma_wait_operands", "mma_wait_task", "mma_total", "readback_wait_accumulator",
+               "readback_publish", "readback_store", "readback_total", "unused")
+
+
+def flow_stalls() -> dict:
+    """Where the tile-stream roles of the persistent kernel waited in the last timed forward
+    (kleos_debug_flow_stalls), milliseconds averaged over blocks."""
+    buf = (ctypes.c_float * len(FLOW_STALLS))()
+    lib = load_library()
+    lib.kleos_debug_flow_stalls.argtypes = [ctypes.POINTER(ctypes.c_float), ctypes.c_int]
+    _check(lib.kleos_debug_flow_stalls(buf, len(FLOW_STALLS)), "kleos_debug_flow_stalls")
+    return {n: float(buf[i]) for i, n in enumerate(FLOW_STALLS) if n != "unused"}
 
 
 def launch_count() -> int:

@@ -458,8 +458,9 @@ def run_cuda(args):
     phases = kleos.phase_times()
     try:
         timeline = kleos.flow_timeline()
+        stalls = kleos.flow_stalls()
     except kleos.KleosError:
-        timeline = None  # this layer runs as separate launches
+        timeline, stalls = None, None  # this layer runs as separate launches
     # a single-expert layer has no routing: every token of every rank goes through the one expert
     routing = dict(counts=np.array([cfg.S], dtype=np.uint32)) if cfg.dense else kleos.debug_routing(info)
     routed_here = int(np.minimum(routing["counts"], info.EC).sum())  # pairs this rank dispatched
@@ -523,7 +524,7 @@ def run_cuda(args):
                 # the whole layer against the slower of its FLOPs at the tensor peak and its
                 # dispatch + combine bytes at the measured 770 GB/s peer rate
                 layer_frac=t_roof_ms / ms_per_step, t_roof_ms=t_roof_ms, layer_flops=total_flops,
-                link_bytes_each_way=link_bytes, phases_ms=phases, timeline_ms=timeline,
+                link_bytes_each_way=link_bytes, phases_ms=phases, timeline_ms=timeline, role_waits_ms=stalls,
                 routed_pairs_per_rank=pairs_per_rank)
     if sustained is not None:
         t_roof_sus = max(total_flops / (peaks["tflops_sustained"] * 1e12), link_bytes / 770e9) * 1e3

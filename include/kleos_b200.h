@@ -152,6 +152,15 @@ int kleos_phase_times(float* ms, int n);
  * layer, KLEOS_PHASES=1). */
 int kleos_flow_timeline(float* ms, int n);
 
+/* Wait times of the persistent kernel's tile-stream roles in the LAST timed forward of
+ * kleos_forward_bench, milliseconds averaged over the blocks that recorded a value:
+ * [0] producer waiting for a free stage, [1] for cell data / GEMM1 counters, [2] producer total,
+ * [3] MMA issuer waiting for an accumulator, [4] for operands, [5] for the next claimed tile,
+ * [6] issuer total, [7] read-back warp waiting for an accumulator, [8] publishing, [9] reading back
+ * and storing, [10] read-back total, [11] unused.  n >= 12.  A tuning aid with no counterpart in
+ * the reference. */
+int kleos_debug_flow_stalls(float* ms, int n);
+
 /* Kernels this library has launched for forward calls since kleos_initialize (every launch site
  * counts itself; memory copies and memsets are not kernels).  A benchmark reads it before and
  * after its timed region.  Negative (KLEOS_E_STATE) when not initialised.  No counterpart in the
