@@ -187,6 +187,11 @@ __device__ __forceinline__ unsigned ld_relaxed_gpu(const unsigned* p) {
     asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
+// Release fences of the publication patterns below.  (__threadfence() and __threadfence_system()
+// are the sequentially consistent forms, which cost several times as much under memory load.)
+__device__ __forceinline__ void fence_release_gpu() { asm volatile("fence.acq_rel.gpu;" ::: "memory"); }
+__device__ __forceinline__ void fence_release_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
+
 __device__ __forceinline__ bool mbar_try_wait_cluster(unsigned long long* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
@@ -441,11 +446,11 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     if (stamp && tid == 0) stamp[kStart] = global_ns();
     long long* stall = a.stalls ? a.stalls + (size_t)blockIdx.x * kStallSlots : nullptr;
     // waits of the tile stream, timed only when the caller asked for the counters
-    auto timed_wait = [&](unsigned long long* bar, uint32_t parity, int slot) -> bool {
+    auto timed_wait = [&](unsigned long long* bar, uint32_t parity, long long* acc) -> bool {
         if (!stall) return mbar_wait(bar, parity, budget, abort_flag);
         const long long c0 = clock64();
         const bool ok = mbar_wait(bar, parity, budget, abort_flag);
-        stall[slot] += clock64() - c0;
+        *acc += clock64() - c0;
         return ok;
     };
 
@@ -779,9 +784,9 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
 
         // -------------------------------------------------------------- grid barrier, slots, grid barrier
         auto grid_barrier = [&](int which) {
-            __threadfence();
             __syncthreads();
             if (tid == 0) {
+                fence_release_gpu();  // cumulative over the block's writes observed through the barrier
                 atomicAdd(&ctr->grid_bar[which], 1u);
                 const long long t0 = clock64();
                 while (ld_acquire_gpu(&ctr->grid_bar[which]) < gridDim.x) {
@@ -795,7 +800,6 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                         break;
                     }
                 }
-                __threadfence();
             }
             __syncthreads();
         };
@@ -929,7 +933,8 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             for (int le = lane; le <= a.nLx; le += 32) ctl->le_start[le] = le < a.nLx ? ctl->poff_s[le * a.world] : n_panels;
             __syncwarp();
             // lag of the tile order: enough segments between a GEMM1 segment and its GEMM2 segment
-            // to cover one and a half times the tiles in flight
+            // to cover two and a half times the tiles in flight (a tile is published up to one tile
+            // time after it is finished)
             int pairs = 0;
             for (int le = lane; le < a.nLx; le += 32)
                 pairs += (ctl->le_start[le + 1] - ctl->le_start[le] + 1) >> 1;
@@ -937,7 +942,7 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             for (int o = 16; o > 0; o >>= 1) pairs += __shfl_xor_sync(0xffffffffu, pairs, o);
             const int t1 = max(1, pairs * NT1 / a.nLx), t2 = max(1, pairs * NT2 / a.nLx);
             const int in_flight = (int)gridDim.x >> 1;
-            const int lag = min(a.nLx, max(1, (in_flight + in_flight / 2 + t2 + t1 + t2 - 1) / (t1 + t2)));
+            const int lag = min(a.nLx, max(1, (2 * in_flight + in_flight / 2 + t2 + t1 + t2 - 1) / (t1 + t2)));
             const int n_tiles = warp_prefix(
                 [&](int sg) {
                     int phase, le;
@@ -1133,6 +1138,7 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             // either running or held by a block whose current tile has a smaller index.)
             int ahead = leader ? claim() : -1;
             const long long c_begin = clock64();
+            long long w_empty = 0, w_ready = 0;
             for (uint32_t i = 0;; ++i) {
                 int t;
                 if (leader) {
@@ -1189,12 +1195,12 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                     ctl->pair_ready_s[ti.panel0] = 1;
                     asm volatile("fence.proxy.async;" ::: "memory");
                 }
-                if (stall) stall[kProdReady] += clock64() - c_ready;
+                if (stall) w_ready += clock64() - c_ready;
                 if (!ok) continue;  // the next claim returns -1 (abort is up) and ends every role
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const int s = it % NST;
                     const uint32_t ph = stage_parity(s, it);
-                    if (!timed_wait(&ctl->empty[s], ph ^ 1, kProdEmpty)) {
+                    if (!timed_wait(&ctl->empty[s], ph ^ 1, &w_empty)) {
                         if (!*abort_flag) give_up(KLEOS_AT_GEMM_PRODUCER, t);
                         break;
                     }
@@ -1209,7 +1215,11 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                     }
                 }
             }
-            if (stall) stall[kProdTotal] = clock64() - c_begin;
+            if (stall) {
+                stall[kProdEmpty] = w_empty;
+                stall[kProdReady] = w_ready;
+                stall[kProdTotal] = clock64() - c_begin;
+            }
             atomicAdd(&ctl->roles_done, 1);
         }
         __syncwarp();
@@ -1219,15 +1229,16 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             if (leader) {
                 uint32_t it = 0;
                 const long long c_begin = clock64();
+                long long w_acc = 0, w_full = 0, w_task = 0;
                 for (uint32_t i = 0;; ++i) {
                     const long long c_task = stall ? clock64() : 0;
                     const int t = take(i, KLEOS_AT_GEMM_MMA);
-                    if (stall) stall[kMmaTask] += clock64() - c_task;
+                    if (stall) w_task += clock64() - c_task;
                     if (t < 0) break;
                     const Tile ti = decode_tile(ctl, t, a.nLx);
                     const int KS = (ti.phase ? a.I : a.H) / BK, KB = (KS + SUB - 1) / SUB;
                     const uint32_t tn = route_tiles + i, buf = tn & 1, use = tn >> 1;
-                    if (!timed_wait(&ctl->acc_empty[buf], (use & 1) ^ 1, kMmaAcc)) {
+                    if (!timed_wait(&ctl->acc_empty[buf], (use & 1) ^ 1, &w_acc)) {
                         if (!*abort_flag) give_up(KLEOS_AT_GEMM_MMA, t);
                         break;
                     }
@@ -1237,7 +1248,7 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                     for (int kb = 0; kb < KB; ++kb, ++it) {
                         const int s = it % NST;
                         const uint32_t ph = stage_parity(s, it);
-                        if (!timed_wait(&ctl->full[s], ph, kMmaFull)) {
+                        if (!timed_wait(&ctl->full[s], ph, &w_full)) {
                             if (!*abort_flag) give_up(KLEOS_AT_GEMM_MMA, t);
                             ok = false;
                             break;
@@ -1262,7 +1273,12 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                     umma_commit_pair(map_to_cta(f_local, 0));
                     umma_commit_pair(map_to_cta(f_local, 1));
                 }
-                if (stall) stall[kMmaTotal] = clock64() - c_begin;
+                if (stall) {
+                    stall[kMmaAcc] = w_acc;
+                    stall[kMmaFull] = w_full;
+                    stall[kMmaTask] = w_task;
+                    stall[kMmaTotal] = clock64() - c_begin;
+                }
             }
             atomicAdd(&ctl->roles_done, 1);
         }
@@ -1291,20 +1307,23 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         int pend_phase = 0, pend_panel = -1;
         auto publish = [&]() {
             if (pend_panel < 0) return;
+            // The warp's stores are ordered before the counter update by ONE fence of the lane that
+            // updates it, after the warp has met (the fence is cumulative over what that lane has
+            // observed through the warp barrier): the pattern of a grid-wide barrier, per warp.
             if (pend_phase == 0) {
                 // GEMM1: the pair's counter releases its GEMM2 tiles (reference processor.cuh:717-729)
-                __threadfence();
                 __syncwarp();
                 if (lane == 0) {
+                    fence_release_gpu();
                     atomicAdd(&ctr->pair_done[pend_panel], 1u);
                     if (stamp && q == 0) stamp[kLastGemm1] = global_ns();
                 }
             } else {
                 // GEMM2: one return flag per (expert, 128-row panel), raised by the warp that stores
                 // the panel's last piece (reference: one signal per returned tile, processor.cuh:745-769)
-                __threadfence_system();
                 __syncwarp();
                 if (lane == 0) {
+                    fence_release_sys();
                     const unsigned prev = atomicAdd(&ctr->panel_ret[pend_panel], 1u);
                     if (prev + 1u == 4u * (unsigned)NT2) {
                         const PanelEntry pp = panel_of(ctl, pend_panel);
@@ -1319,7 +1338,7 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                         if (done + 1u == (unsigned)ctl->total_panels && !a.suppress) {
                             // everything this rank's experts owed has been returned: tell every
                             // source (they leave the forward only after all owners said so)
-                            __threadfence_system();
+                            fence_release_sys();
                             for (int r = 0; r < a.world; ++r)
                                 st_release_sys(reinterpret_cast<unsigned long long*>(a.peers.arena[r] + a.lay.yflag) + a.rank,
                                                make_flag(a.epoch, 1u));
@@ -1332,6 +1351,7 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         };
         const bool tally = stall && q == 0 && lane == 0;
         const long long c_begin = clock64();
+        long long w_pub = 0, w_acc = 0, w_read = 0;
         for (uint32_t i = 0;; ++i) {
             const int t = take(i, KLEOS_AT_GEMM_EPILOGUE);
             if (t < 0) break;
@@ -1370,7 +1390,7 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 if (!ready) publish();  // idle: publish the last tile now
             }
             if (tally) {
-                stall[kBackPublish] += clock64() - c0;
+                w_pub += clock64() - c0;
                 c0 = clock64();
             }
             if (!mbar_wait(&ctl->acc_full[buf], use & 1, budget, abort_flag)) {
@@ -1378,12 +1398,12 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 break;
             }
             if (tally) {
-                stall[kBackAcc] += clock64() - c0;
+                w_acc += clock64() - c0;
                 c0 = clock64();
             }
             publish();
             if (tally) {
-                stall[kBackPublish] += clock64() - c0;
+                w_pub += clock64() - c0;
                 c0 = clock64();
             }
             tc_fence_after();
@@ -1413,11 +1433,16 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             // it is published later (see publish above)
             pend_phase = ti.phase;
             pend_panel = ti.phase == 0 ? ti.panel0 : (have_panel ? my_panel : -1);
-            if (tally) stall[kBackRead] += clock64() - c0;
+            if (tally) w_read += clock64() - c0;
             if (stamp && q == 0 && lane == 0) stamp[kLastTile] = global_ns();
         }
         if (!*abort_flag) publish();
-        if (tally) stall[kBackTotal] = clock64() - c_begin;
+        if (tally) {
+            stall[kBackPublish] = w_pub;
+            stall[kBackAcc] = w_acc;
+            stall[kBackRead] = w_read;
+            stall[kBackTotal] = clock64() - c_begin;
+        }
         // no tiles left: help with the combine of the tokens whose rows return last
         run_combine();
         if (lane == 0) atomicAdd(&ctl->roles_done, 1);
@@ -1476,12 +1501,12 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                         }
                 }
             }
-            __threadfence_system();
             __syncwarp();
             if (lane == 0) {
+                fence_release_sys();
                 const unsigned prev = atomicAdd(&ctr->cell_done[e], (unsigned)nrows);
                 if ((int)prev + nrows == routed) {
-                    __threadfence_system();
+                    fence_release_sys();
                     st_release_sys(reinterpret_cast<unsigned long long*>(a.peers.arena[owner] + a.lay.xflag) +
                                        ((size_t)a.rank * a.nLx + le),
                                    make_flag(a.epoch, (unsigned)routed));
