@@ -17,7 +17,8 @@
 //     blocks of the pair);
 //   * one 384-thread block per SM, paired with its neighbour (tcgen05 cta_group::2):
 //       warp 0      TMA producer             warp 1      MMA issuer (leader block)
-//       warp 2      tensor-memory owner      warp 3      monitor (abort propagation)
+//       warp 2      tensor-memory owner      warp 3      subscriber (polls the flag the producer's
+//                                                        NEXT tile depends on; abort propagation)
 //       warps 4-7   accumulator read-back, bias / activation, stores (local y1 or the SOURCE
 //                   rank's result cell over NVLink), completion counters and return flags
 //       warps 8-11  transport: first this rank's token rows into the owners' cells (per-cell
@@ -118,6 +119,8 @@ struct Control {
     int roles_done;
     int total_tiles, total_panels, lag;
     unsigned total_units;
+    unsigned sub_req;   // producer -> subscriber: (sequence << 16) | (kind << 15) | index, see the subscriber warp
+
     int le_start[kMaxLocal + 1];             // first panel of every local expert
     int seg_prefix[2 * kMaxLocal + 1];       // tiles before every segment of the tile order
     __align__(16) float bias_s[4][256];
@@ -474,6 +477,7 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         for (int r = 0; r < kRing; ++r) mbar_init(&ctl->task_full[r], 1);
         ctl->abort = 0;
         ctl->roles_done = 0;
+        ctl->sub_req = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 2) {
@@ -895,20 +899,12 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     // (os/os.cuh:104-105).
     const int cells = a.world * a.nLx;
     const int NT1 = (a.I + BN - 1) / BN, NT2 = (a.H + BN - 1) / BN;
+    const bool transport = warp >= 8;
+    // barrier among the eight planning warps (the transport warps are already moving rows)
+    auto planners_sync = [&]() { asm volatile("bar.sync 2, 256;" ::: "memory"); };
     {
-        const unsigned long long* cflag =
-            reinterpret_cast<const unsigned long long*>(a.peers.arena[a.rank] + a.lay.cflag);
         for (int c = tid; c < kMaxCells; c += kThreads) ctl->ready_s[c] = 0;
         for (int c = tid; c < kMaxPanels; c += kThreads) ctl->pair_ready_s[c] = 0;
-        __syncthreads();  // abort flag initialised before anybody may raise it
-        for (int c = tid; c < cells; c += kThreads) {
-            unsigned long long v = 0;
-            if (!wait_flag(cflag + c, a.epoch, budget, &v)) {
-                give_up(KLEOS_AT_PLAN_WAIT, c);
-                v = 0;
-            }
-            ctl->cnt_s[c] = (int)min((unsigned)(v & 0xffffffffu), (unsigned)a.pEC);
-        }
         // sending order of this rank's rows: local expert index first, owners rotated so that at
         // any moment the source ranks write to different owners
         for (int i = tid; i < a.E; i += kThreads) {
@@ -921,7 +917,27 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             const int total = warp_prefix([&](int i) { return (ctl->own_s[i] + kUnitRows - 1) / kUnitRows; },
                                           ctl->prefix_s, a.E, lane);
             if (lane == 0) ctl->total_units = (unsigned)total;
-        } else if (warp == 1) {
+        }
+        __syncthreads();
+    }
+    if (transport) {
+        // The transport warps know all they need (what this rank sends where) and start moving rows
+        // while the other warps wait for the counts of the other ranks and build the tile plan.
+        // They sign the cluster barrier that ends the plan now and collect it before the teardown.
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    } else {
+        const unsigned long long* cflag =
+            reinterpret_cast<const unsigned long long*>(a.peers.arena[a.rank] + a.lay.cflag);
+        for (int c = tid; c < cells; c += 256) {
+            unsigned long long v = 0;
+            if (!wait_flag(cflag + c, a.epoch, budget, &v)) {
+                give_up(KLEOS_AT_PLAN_WAIT, c);
+                v = 0;
+            }
+            ctl->cnt_s[c] = (int)min((unsigned)(v & 0xffffffffu), (unsigned)a.pEC);
+        }
+        planners_sync();
+        if (warp == 1) {
             // panels before every cell, cells in plan order o = le * world + j
             const int n_panels = warp_prefix(
                 [&](int o) {
@@ -957,8 +973,8 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 ctl->total_tiles = n_tiles;
             }
         }
-        __syncthreads();
-        for (int o = tid; o < cells; o += kThreads) {
+        planners_sync();
+        for (int o = tid; o < cells; o += 256) {
             const int le = o / a.world, j = o - le * a.world;
             const int src = (a.rank + 1 + j) % a.world;
             const int c = src * a.nLx + le;
@@ -972,7 +988,7 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         if (blockIdx.x == 0) {
             // cells this rank sends nothing to: nothing will complete them, so their data flags
             // go out now (reference os/packet.cuh:240-259)
-            for (int i = tid; i < a.E; i += kThreads)
+            for (int i = tid; i < a.E; i += 256)
                 if (ctl->own_s[i] == 0) {
                     const int le = i / a.world, owner = (a.rank + 1 + i % a.world) % a.world;
                     st_release_sys(reinterpret_cast<unsigned long long*>(a.peers.arena[owner] + a.lay.xflag) +
@@ -984,11 +1000,11 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 st_release_sys(reinterpret_cast<unsigned long long*>(a.peers.arena[tid] + a.lay.yflag) + a.rank,
                                make_flag(a.epoch, 1u));
         }
+        tc_fence_before();
+        planners_sync();
+        cluster_sync_all();  // both blocks' barriers exist before anything remote touches them
+        tc_fence_after();
     }
-    tc_fence_before();
-    __syncthreads();
-    cluster_sync_all();  // both blocks' barriers exist before anything remote touches them
-    tc_fence_after();
     const uint32_t tmem_base = ctl->tmem_base;
     const int total_tiles = ctl->total_tiles;
     // parity of pipeline barrier s after `it` stage uses of the tile stream: the routing phase used
@@ -1135,15 +1151,38 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             uint32_t it = 0;
             // The leader claims one tile ahead: the round trip of the claim for tile i+1 runs under
             // the loads of tile i.  (Claims stay in order, so the tile a block waits for is still
-            // either running or held by a block whose current tile has a smaller index.)
+            // either running or held by a block whose current tile has a smaller index.)  A few
+            // K slices into tile i both producers look at tile i+1 and, if it depends on a flag this
+            // block has not seen yet, ask the subscriber warp to watch that flag: an acquiring poll
+            // of a flag in global memory costs microseconds, which the subscriber spends while the
+            // producer keeps loading.
             int ahead = leader ? claim() : -1;
+            if (leader) hand_out(0, ahead);
             const long long c_begin = clock64();
             long long w_empty = 0, w_ready = 0;
+            uint32_t req_seq = 0;
+            int asked_for = -1;  // tile whose dependency the subscriber has been asked to watch
+            // what tile t waits for: kind 0 = data flag of a cell, kind 1 = GEMM1 counter of a pair
+            auto dependency = [&](const Tile& x, int* kind, int* id) -> bool {
+                if (x.phase == 0) {
+                    const PanelEntry px = panel_of(ctl, x.panel0 + ((int)cta_rank < x.n_left ? (int)cta_rank : 0));
+                    *kind = 0;
+                    *id = px.src * a.nLx + px.le;
+                    return !*reinterpret_cast<volatile unsigned char*>(&ctl->ready_s[*id]);
+                }
+                *kind = 1;
+                *id = x.panel0;
+                return !*reinterpret_cast<volatile unsigned char*>(&ctl->pair_ready_s[*id]);
+            };
+            auto ask = [&](int t_for, int kind, int id) {
+                ++req_seq;
+                asked_for = t_for;
+                *reinterpret_cast<volatile unsigned*>(&ctl->sub_req) = (req_seq << 16) | ((unsigned)kind << 15) | (unsigned)id;
+            };
             for (uint32_t i = 0;; ++i) {
                 int t;
                 if (leader) {
-                    t = *abort_flag ? -1 : ahead;
-                    hand_out(i, t);
+                    t = *abort_flag ? -1 : ahead;  // handed out already (tile 0 above, later ones below)
                     if (t >= 0) ahead = claim();
                 } else {
                     t = take(i, KLEOS_AT_GEMM_PRODUCER);
@@ -1160,39 +1199,30 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 const CUtensorMap* mb = ti.phase ? &map_w2 : &map_w1;
                 bool ok = true;
                 const long long c_ready = stall ? clock64() : 0;
-                if (ti.phase == 0) {
-                    // rows of this panel's cell may still be on their way from the source rank
-                    // (reference: the subscriber polls the first-stage flag, os/subscriber.cuh:107)
-                    const int cell = p.src * a.nLx + p.le;
-                    if (!ctl->ready_s[cell]) {
-                        unsigned long long v;
-                        const unsigned long long* xf =
-                            reinterpret_cast<const unsigned long long*>(a.peers.arena[a.rank] + a.lay.xflag) + cell;
-                        if (!wait_flag(xf, a.epoch, budget, &v)) {
-                            give_up(KLEOS_AT_PLAN_WAIT, 1000 + cell);
-                            ok = false;
+                {
+                    // GEMM1: rows of the panel's cell may still be on their way from the source rank
+                    // (reference: the subscriber polls the first-stage flag, os/subscriber.cuh:107);
+                    // GEMM2: starts when all GEMM1 tiles of the panel pair are stored (reference: tQS
+                    // counter and notifyNext, processor.cuh:717-729)
+                    int kind, id;
+                    if (dependency(ti, &kind, &id)) {
+                        if (asked_for != t) ask(t, kind, id);
+                        volatile unsigned char* memo = kind ? &ctl->pair_ready_s[id] : &ctl->ready_s[id];
+                        const long long t0 = clock64();
+                        while (!*memo) {
+                            __nanosleep(32);
+                            if (*abort_flag) {
+                                ok = false;
+                                break;
+                            }
+                            if (clock64() - t0 > 2 * budget) {  // the subscriber gives up first
+                                give_up(kind ? KLEOS_AT_GEMM_PRODUCER : KLEOS_AT_PLAN_WAIT, 4000 + id);
+                                ok = false;
+                                break;
+                            }
                         }
-                        ctl->ready_s[cell] = 1;
-                        asm volatile("fence.proxy.async;" ::: "memory");
+                        asm volatile("fence.acq_rel.cta;" ::: "memory");
                     }
-                } else if (!ctl->pair_ready_s[ti.panel0]) {
-                    // GEMM2 of a panel pair starts when all GEMM1 tiles of the pair are stored
-                    // (reference: tQS counter and notifyNext, processor.cuh:717-729)
-                    const unsigned need = 8u * (unsigned)NT1;
-                    const long long t0 = clock64();
-                    while (ld_acquire_gpu(&ctr->pair_done[ti.panel0]) < need) {
-                        __nanosleep(64);
-                        if (*abort_flag) {
-                            ok = false;
-                            break;
-                        }
-                        if (clock64() - t0 > budget) {
-                            give_up(KLEOS_AT_GEMM_PRODUCER, 3000 + ti.panel0);
-                            ok = false;
-                            break;
-                        }
-                    }
-                    ctl->pair_ready_s[ti.panel0] = 1;
                     asm volatile("fence.proxy.async;" ::: "memory");
                 }
                 if (stall) w_ready += clock64() - c_ready;
@@ -1212,6 +1242,24 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                         const int kx = (kb * SUB + sub) * BK;
                         tma_load_2d_pair(sa + sub * SLICE_BYTES, ma, kx, p.row_base, full_leader);
                         tma_load_2d_pair(sa + sub * SLICE_BYTES + A_STAGE_BYTES, mb, kx, brow, full_leader);
+                    }
+                    if (kb == min(2, KB - 1)) {
+                        // look at the next tile: the leader hands its claim out now, the partner reads
+                        // it if it is there already
+                        int nxt = -1;
+                        if (leader) {
+                            hand_out(i + 1, ahead);
+                            nxt = ahead;
+                        } else {
+                            const int slot = (i + 1) % kRing;
+                            if (mbar_try_wait_cluster(&ctl->task_full[slot], ((i + 1) / kRing) & 1u))
+                                nxt = *reinterpret_cast<volatile int*>(&ctl->task_s[slot]);
+                        }
+                        if (nxt >= 0) {
+                            int kind, id;
+                            const Tile tn = decode_tile(ctl, nxt, a.nLx);
+                            if (dependency(tn, &kind, &id)) ask(nxt, kind, id);
+                        }
                     }
                 }
             }
@@ -1284,12 +1332,49 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         }
         __syncwarp();
     } else if (warp == 3) {
-        // ------------------------------------------------------------ monitor
-        // mirrors the rank's abort word into this block while any role is still working
+        // ------------------------------------------------------------ subscriber
+        // Watches, on behalf of this block's producer, the one flag the producer's next tile depends
+        // on (the data flag of a dispatched cell, or the GEMM1 counter of a panel pair) and notes
+        // in shared memory when it has been seen (reference: the subscriber warps poll the flags
+        // and turn arrivals into tasks, os/subscriber.cuh:56-185).  Also mirrors the rank's abort
+        // word into this block while any role is still working.
         if (lane == 0) {
+            unsigned seen = 0;
+            const unsigned need = 8u * (unsigned)NT1;
+            const unsigned long long* xflag =
+                reinterpret_cast<const unsigned long long*>(a.peers.arena[a.rank] + a.lay.xflag);
             while (*reinterpret_cast<volatile int*>(&ctl->roles_done) < kRoleWarps) {
                 if (ld_relaxed_gpu(&ctr->abort_all)) *abort_flag = 1;
-                __nanosleep(2000);
+                const unsigned r = *reinterpret_cast<volatile unsigned*>(&ctl->sub_req);
+                if ((r >> 16) == seen) {
+                    __nanosleep(200);
+                    continue;
+                }
+                seen = r >> 16;
+                const int kind = (int)((r >> 15) & 1u), id = (int)(r & 0x7fffu);
+                const long long t0 = clock64();
+                bool ok = true;
+                for (;;) {
+                    const bool up = kind ? ld_acquire_gpu(&ctr->pair_done[id]) >= need
+                                         : (uint32_t)(ld_acquire_sys(xflag + id) >> 32) == a.epoch;
+                    if (up) break;
+                    __nanosleep(100);
+                    if (*abort_flag || ld_relaxed_gpu(&ctr->abort_all)) {
+                        *abort_flag = 1;
+                        ok = false;
+                        break;
+                    }
+                    if (clock64() - t0 > budget) {
+                        give_up(kind ? KLEOS_AT_GEMM_PRODUCER : KLEOS_AT_PLAN_WAIT, kind ? 3000 + id : 1000 + id);
+                        ok = false;
+                        break;
+                    }
+                }
+                if (ok) {
+                    asm volatile("fence.acq_rel.cta;" ::: "memory");
+                    if (kind) *reinterpret_cast<volatile unsigned char*>(&ctl->pair_ready_s[id]) = 1;
+                    else *reinterpret_cast<volatile unsigned char*>(&ctl->ready_s[id]) = 1;
+                }
             }
         }
         __syncwarp();
@@ -1539,6 +1624,7 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
 
     // teardown: neither block may leave while its partner can still touch its shared memory,
     // barriers or tensor memory
+    if (transport) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");  // the plan's barrier
     tc_fence_before();
     __syncthreads();
     cluster_sync_all();

@@ -108,6 +108,34 @@ def route(cfg, a: np.ndarray, wg: np.ndarray, gate_bias=None) -> dict:
                 mean_prob=mean_prob, mean_count=mean_count, gate_loss=gate_loss)
 
 
+def route_reference_rule(cfg, a: np.ndarray, wg: np.ndarray, gate_bias=None) -> dict:
+    """The reference gate's selection rule taken literally, as a second opinion on ``route``:
+    fp32 logits (fp32 accumulation, BLAS order), fp32 softmax with expf over the E real experts
+    (moe/gate.cuh:574-584), then k rounds of arg-max on the PROBABILITIES with strict '>' over
+    ascending ids and the winner masked out (:654-670).  Returns the top-k ids in selection order
+    and the smallest gap, over all tokens, between the k-th and (k+1)-th largest probability: where
+    that gap is far above fp32 rounding, selecting on fp64 logits (``route``) must pick the same
+    sets."""
+    S, E, K = cfg.S, cfg.E, cfg.K
+    l32 = a.astype(np.float32) @ wg[:E].astype(np.float32).T
+    if gate_bias is not None:
+        l32 = l32 + np.asarray(gate_bias, dtype=np.float32)[None, :]
+    m = l32.max(axis=1, keepdims=True)
+    ex = np.exp(l32 - m, dtype=np.float32)
+    probs = (ex / ex.sum(axis=1, keepdims=True, dtype=np.float32)).astype(np.float32)
+    work = probs.copy()
+    topk = np.zeros((S, K), dtype=np.int32)
+    rows = np.arange(S)
+    for j in range(K):
+        best = np.argmax(work, axis=1)  # first maximum = lowest id among equals, as strict '>' does
+        topk[:, j] = best
+        work[rows, best] = -1.0
+    srt = -np.sort(-probs, axis=1)
+    gap = float((srt[:, K - 1] - srt[:, K]).min()) if K < E else float("inf")
+    rel_gap = float(((srt[:, K - 1] - srt[:, K]) / srt[:, K - 1]).min()) if K < E else float("inf")
+    return dict(topk=topk, probs_f32=probs, min_prob_gap=gap, min_rel_prob_gap=rel_gap)
+
+
 def expert_ffn(cfg, x: np.ndarray, w1, w2, b1, b2) -> np.ndarray:
     """y2 rows of one expert for token rows x (all dtype-rounded fp32)."""
     z = x.astype(np.float64) @ w1.astype(np.float64).T + b1.astype(np.float64)[None, :]
