@@ -1229,6 +1229,18 @@ int kleos_phase_times(float* ms, int n) {
     return KLEOS_OK;
 }
 
+int kleos_debug_tile_order(int local_experts, int lag, int32_t* phase, int32_t* expert) {
+    if (local_experts < 1 || local_experts > flow::kMaxLocal || lag < 1 || lag > local_experts || !phase || !expert)
+        return fail(KLEOS_E_ARG, "tile order: 1 <= lag <= local experts <= %d", flow::kMaxLocal);
+    for (int s = 0; s < 2 * local_experts; ++s) {
+        int ph, le;
+        flow::segment_of(s, local_experts, lag, &ph, &le);
+        phase[s] = ph;
+        expert[s] = le;
+    }
+    return 2 * local_experts;
+}
+
 long long kleos_launch_count(void) { return g.initialised ? (long long)g.launches : (long long)KLEOS_E_STATE; }
 
 int kleos_debug_flow_stalls(float* ms, int n) {

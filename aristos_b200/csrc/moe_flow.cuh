@@ -104,7 +104,7 @@ enum Stall {
     kBackPublish,    // ... publishing (fence + counters)
     kBackRead,       // ... reading back and storing
     kBackTotal,
-    kStallUnused
+    kProdFence       // producer: proxy fences in front of each tile's loads
 };
 
 struct Control {
@@ -216,7 +216,7 @@ __device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v
 // GEMM2 segments; D is chosen in the plan so that this distance exceeds the number of tiles in
 // flight (one per block pair): by the time a GEMM2 tile is claimed, the GEMM1 tiles of its row
 // panels have normally been finished and nobody waits.
-__device__ __forceinline__ void segment_of(int s, int n, int D, int* phase, int* le) {
+__host__ __device__ __forceinline__ void segment_of(int s, int n, int D, int* phase, int* le) {
     if (s < D) {
         *phase = 0;
         *le = s;
@@ -1159,7 +1159,7 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             int ahead = leader ? claim() : -1;
             if (leader) hand_out(0, ahead);
             const long long c_begin = clock64();
-            long long w_empty = 0, w_ready = 0;
+            long long w_empty = 0, w_ready = 0, w_fence = 0;
             uint32_t req_seq = 0;
             int asked_for = -1;  // tile whose dependency the subscriber has been asked to watch
             // what tile t waits for: kind 0 = data flag of a cell, kind 1 = GEMM1 counter of a pair
@@ -1223,9 +1223,11 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                         }
                         asm volatile("fence.acq_rel.cta;" ::: "memory");
                     }
+                    if (stall) w_ready += clock64() - c_ready;
+                    const long long c_fence = stall ? clock64() : 0;
                     asm volatile("fence.proxy.async;" ::: "memory");
+                    if (stall) w_fence += clock64() - c_fence;
                 }
-                if (stall) w_ready += clock64() - c_ready;
                 if (!ok) continue;  // the next claim returns -1 (abort is up) and ends every role
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const int s = it % NST;
@@ -1266,6 +1268,7 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             if (stall) {
                 stall[kProdEmpty] = w_empty;
                 stall[kProdReady] = w_ready;
+                stall[kProdFence] = w_fence;
                 stall[kProdTotal] = clock64() - c_begin;
             }
             atomicAdd(&ctl->roles_done, 1);

@@ -27,7 +27,7 @@ EXPORTS = (
     "kleos_forward", "kleos_forward_bench", "kleos_forward_host", "kleos_forward_host_async",
     "kleos_host_sync", "kleos_get_rank",
     "kleos_local_experts", "kleos_get_info", "kleos_last_status", "kleos_clear_status", "kleos_debug_routing",
-    "kleos_phase_times", "kleos_flow_timeline", "kleos_debug_flow_stalls", "kleos_launch_count", "kleos_debug_gemm_stats", "kleos_debug_suppress_return_flag", "kleos_gate_stats", "kleos_plan_placement", "kleos_placement_model", "kleos_route_static", "kleos_finalize", "kleos_error_string",
+    "kleos_phase_times", "kleos_flow_timeline", "kleos_debug_flow_stalls", "kleos_debug_tile_order", "kleos_launch_count", "kleos_debug_gemm_stats", "kleos_debug_suppress_return_flag", "kleos_gate_stats", "kleos_plan_placement", "kleos_placement_model", "kleos_route_static", "kleos_finalize", "kleos_error_string",
 )
 
 PHASE_NAMES = ("route", "slots", "dispatch", "plan", "gemm1", "gemm2", "combine", "total")
@@ -222,7 +222,7 @@ def flow_timeline() -> dict:
 
 FLOW_STALLS = ("producer_wait_stage", "producer_wait_data", "producer_total", "mma_wait_accumulator",
                "mma_wait_operands", "mma_wait_task", "mma_total", "readback_wait_accumulator",
-               "readback_publish", "readback_store", "readback_total", "unused")
+               "readback_publish", "readback_store", "readback_total", "producer_proxy_fence")
 
 
 def flow_stalls() -> dict:

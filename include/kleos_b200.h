@@ -157,9 +157,17 @@ int kleos_flow_timeline(float* ms, int n);
  * [0] producer waiting for a free stage, [1] for cell data / GEMM1 counters, [2] producer total,
  * [3] MMA issuer waiting for an accumulator, [4] for operands, [5] for the next claimed tile,
  * [6] issuer total, [7] read-back warp waiting for an accumulator, [8] publishing, [9] reading back
- * and storing, [10] read-back total, [11] unused.  n >= 12.  A tuning aid with no counterpart in
+ * and storing, [10] read-back total, [11] producer's proxy fences.  n >= 12.  A tuning aid with no counterpart in
  * the reference. */
 int kleos_debug_flow_stalls(float* ms, int n);
+
+/* The segment order of the persistent kernel's tile queue for `local_experts` experts and a lag
+ * of `lag` segments: phase[s] is 0 for the first expert GEMM and 1 for the second, expert[s] the
+ * local expert of segment s; returns the number of segments (2 * local_experts).  Host only,
+ * needs no GPU and no kleos_initialize; lets a test check that every second-GEMM segment follows
+ * the first-GEMM segment it consumes (the reference chains the two per row panel at run time,
+ * os/processor/processor.cuh:717-729). */
+int kleos_debug_tile_order(int local_experts, int lag, int32_t* phase, int32_t* expert);
 
 /* Kernels this library has launched for forward calls since kleos_initialize (every launch site
  * counts itself; memory copies and memsets are not kernels).  A benchmark reads it before and

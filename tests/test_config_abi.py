@@ -122,3 +122,31 @@ def test_no_gpu_means_loud_failure():
     with pytest.raises(kleos.KleosError) as e:
         kleos.initialize(cfg)
     assert e.value.code == -3  # no CPU fallback
+
+
+def test_tile_order_of_the_persistent_kernel():
+    """Host-side check of the on-GPU scheduler's segment order: for every number of local experts
+    and every lag, each (GEMM, expert) segment appears exactly once, a second-GEMM segment comes
+    after the first-GEMM segment it consumes, and exactly `lag` first-GEMM segments (fewer at the
+    end) separate the two."""
+    import ctypes
+    lib = kleos.load_library()
+    for n in (1, 2, 3, 8, 31, 64, 128):
+        for lag in sorted({1, 2, min(8, n), n}):
+            if lag > n:
+                continue
+            phase = (ctypes.c_int32 * (2 * n))()
+            expert = (ctypes.c_int32 * (2 * n))()
+            assert lib.kleos_debug_tile_order(n, lag, phase, expert) == 2 * n
+            seen = {}
+            for s in range(2 * n):
+                key = (phase[s], expert[s])
+                assert key not in seen and 0 <= expert[s] < n and phase[s] in (0, 1), (n, lag, s, key)
+                seen[key] = s
+            for e in range(n):
+                first, second = seen[(0, e)], seen[(1, e)]
+                assert second > first
+                between = sum(1 for s in range(first + 1, second) if phase[s] == 0)
+                assert between == min(lag, n - 1 - e), (n, lag, e, between)
+    phase = (ctypes.c_int32 * 4)()
+    assert lib.kleos_debug_tile_order(2, 3, phase, phase) == -8   # lag beyond the experts
