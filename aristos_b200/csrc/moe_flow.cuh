@@ -120,6 +120,7 @@ struct Control {
     int total_tiles, total_panels, lag;
     unsigned total_units;
     unsigned sub_req;   // producer -> subscriber: (sequence << 16) | (kind << 15) | index, see the subscriber warp
+    unsigned seen_s[kMaxPanels / 32];  // return flags (expert, panel) some warp of this block has seen up
 
     int le_start[kMaxLocal + 1];             // first panel of every local expert
     int seg_prefix[2 * kMaxLocal + 1];       // tiles before every segment of the tile order
@@ -183,6 +184,11 @@ __device__ __forceinline__ long long global_ns() {
 __device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned* p) {
     unsigned v;
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned long long ld_relaxed_sys(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
     return v;
 }
 __device__ __forceinline__ unsigned ld_relaxed_gpu(const unsigned* p) {
@@ -478,6 +484,7 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         ctl->abort = 0;
         ctl->roles_done = 0;
         ctl->sub_req = 0;
+        for (int i = 0; i < kMaxPanels / 32; ++i) ctl->seen_s[i] = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 2) {
@@ -928,11 +935,21 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     } else {
         const unsigned long long* cflag =
             reinterpret_cast<const unsigned long long*>(a.peers.arena[a.rank] + a.lay.cflag);
+        // (relaxed polls: the count travels inside the flag word itself, nothing else is read on
+        // the strength of it, and an acquiring load costs a fence that waits for this SM's stores in
+        // flight -- the transport warps are already streaming rows to the peers)
         for (int c = tid; c < cells; c += 256) {
             unsigned long long v = 0;
-            if (!wait_flag(cflag + c, a.epoch, budget, &v)) {
-                give_up(KLEOS_AT_PLAN_WAIT, c);
-                v = 0;
+            const long long t0 = clock64();
+            for (;;) {
+                v = ld_relaxed_sys(cflag + c);
+                if ((uint32_t)(v >> 32) == a.epoch) break;
+                if (clock64() - t0 > budget) {
+                    give_up(KLEOS_AT_PLAN_WAIT, c);
+                    v = 0;
+                    break;
+                }
+                __nanosleep(64);
             }
             ctl->cnt_s[c] = (int)min((unsigned)(v & 0xffffffffu), (unsigned)a.pEC);
         }
@@ -1007,12 +1024,15 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     }
     const uint32_t tmem_base = ctl->tmem_base;
     const int total_tiles = ctl->total_tiles;
-    // parity of pipeline barrier s after `it` stage uses of the tile stream: the routing phase used
-    // barrier s ceil((route_slices - s) / 6) times before
-    auto stage_parity = [&](int s, uint32_t it) -> uint32_t {
-        const uint32_t before = s < kSlices ? (route_slices + (uint32_t)(kSlices - 1 - s)) / (uint32_t)kSlices : 0u;
-        return (before + it / (uint32_t)NST) & 1u;
-    };
+    // Parity of every pipeline barrier at the start of the tile stream, one bit per barrier: the
+    // routing phase used barrier s ceil((route_slices - s) / 6) times before.  Producer and issuer
+    // each keep their own copy and flip bit s whenever they have used stage s, so the inner
+    // loops carry no divisions (they run in ONE thread each, whose instruction latencies add up
+    // to the time per stage).
+    uint32_t parity0 = 0;
+#pragma unroll
+    for (int sg = 0; sg < kSlices; ++sg)
+        parity0 |= (((route_slices + (uint32_t)(kSlices - 1 - sg)) / (uint32_t)kSlices) & 1u) << sg;
     if (stamp && tid == 0) stamp[kPlanned] = global_ns();
 
     // The leader's producer claims tiles from the rank's task queue (claim) and hands every claimed
@@ -1124,10 +1144,20 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                     if (j < K && sl != kDropped) {
                         yrow[j] = ycell + ((size_t)e * a.pEC + sl) * a.H;
                         if (lane == j) {
-                            unsigned long long v;
-                            if (!wait_flag(ypflag + (size_t)e * TCM + sl / kTileM, a.epoch, budget, &v)) {
-                                give_up(KLEOS_AT_COMBINE_WAIT, e);
-                                failed = true;
+                            // a flag another warp of this block has already seen up needs no poll
+                            const int f = e * TCM + sl / kTileM;
+                            volatile unsigned* word = &ctl->seen_s[f >> 5];
+                            if (!((*word >> (f & 31)) & 1u)) {
+                                unsigned long long v;
+                                if (!wait_flag(ypflag + f, a.epoch, budget, &v)) {
+                                    give_up(KLEOS_AT_COMBINE_WAIT, e);
+                                    failed = true;
+                                } else {
+                                    asm volatile("fence.acq_rel.cta;" ::: "memory");
+                                    atomicOr(const_cast<unsigned*>(word), 1u << (f & 31));
+                                }
+                            } else {
+                                asm volatile("fence.acq_rel.cta;" ::: "memory");
                             }
                         }
                     }
@@ -1148,7 +1178,8 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         // ------------------------------------------------------------ TMA producer (both blocks)
         if (lane == 0) {
             asm volatile("fence.proxy.async;" ::: "memory");
-            uint32_t it = 0;
+            uint32_t par = parity0;
+            int s = 0;
             // The leader claims one tile ahead: the round trip of the claim for tile i+1 runs under
             // the loads of tile i.  (Claims stay in order, so the tile a block waits for is still
             // either running or held by a block whose current tile has a smaller index.)  A few
@@ -1159,9 +1190,12 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             int ahead = leader ? claim() : -1;
             if (leader) hand_out(0, ahead);
             const long long c_begin = clock64();
-            long long w_empty = 0, w_ready = 0, w_fence = 0;
+            long long w_empty = 0, w_ready = 0;
+            const long long w_fence = 0;
             uint32_t req_seq = 0;
             int asked_for = -1;  // tile whose dependency the subscriber has been asked to watch
+            int peeked = -1;     // tile already decoded during the tile before it
+            Tile peeked_tile{};
             // what tile t waits for: kind 0 = data flag of a cell, kind 1 = GEMM1 counter of a pair
             auto dependency = [&](const Tile& x, int* kind, int* id) -> bool {
                 if (x.phase == 0) {
@@ -1188,7 +1222,7 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                     t = take(i, KLEOS_AT_GEMM_PRODUCER);
                 }
                 if (t < 0) break;
-                const Tile ti = decode_tile(ctl, t, a.nLx);
+                const Tile ti = t == peeked ? peeked_tile : decode_tile(ctl, t, a.nLx);
                 // the block without a panel of its own re-reads the first one and discards
                 const int my_panel = ti.panel0 + ((int)cta_rank < ti.n_left ? (int)cta_rank : 0);
                 const PanelEntry p = panel_of(ctl, my_panel);
@@ -1224,14 +1258,10 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                         asm volatile("fence.acq_rel.cta;" ::: "memory");
                     }
                     if (stall) w_ready += clock64() - c_ready;
-                    const long long c_fence = stall ? clock64() : 0;
-                    asm volatile("fence.proxy.async;" ::: "memory");
-                    if (stall) w_fence += clock64() - c_fence;
                 }
                 if (!ok) continue;  // the next claim returns -1 (abort is up) and ends every role
-                for (int kb = 0; kb < KB; ++kb, ++it) {
-                    const int s = it % NST;
-                    const uint32_t ph = stage_parity(s, it);
+                for (int kb = 0; kb < KB; ++kb) {
+                    const uint32_t ph = (par >> s) & 1u;
                     if (!timed_wait(&ctl->empty[s], ph ^ 1, &w_empty)) {
                         if (!*abort_flag) give_up(KLEOS_AT_GEMM_PRODUCER, t);
                         break;
@@ -1259,10 +1289,13 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                         }
                         if (nxt >= 0) {
                             int kind, id;
-                            const Tile tn = decode_tile(ctl, nxt, a.nLx);
-                            if (dependency(tn, &kind, &id)) ask(nxt, kind, id);
+                            peeked_tile = decode_tile(ctl, nxt, a.nLx);
+                            peeked = nxt;
+                            if (dependency(peeked_tile, &kind, &id)) ask(nxt, kind, id);
                         }
                     }
+                    par ^= 1u << s;
+                    s = s + 1 == NST ? 0 : s + 1;
                 }
             }
             if (stall) {
@@ -1278,7 +1311,8 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         // ------------------------------------------------------------ MMA issuer (leader only)
         if (lane == 0) {
             if (leader) {
-                uint32_t it = 0;
+                uint32_t par = parity0;
+                int s = 0;
                 const long long c_begin = clock64();
                 long long w_acc = 0, w_full = 0, w_task = 0;
                 for (uint32_t i = 0;; ++i) {
@@ -1296,9 +1330,8 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                     tc_fence_after();
                     const uint32_t d_tmem = tmem_base + buf * BN;
                     bool ok = true;
-                    for (int kb = 0; kb < KB; ++kb, ++it) {
-                        const int s = it % NST;
-                        const uint32_t ph = stage_parity(s, it);
+                    for (int kb = 0; kb < KB; ++kb) {
+                        const uint32_t ph = (par >> s) & 1u;
                         if (!timed_wait(&ctl->full[s], ph, &w_full)) {
                             if (!*abort_flag) give_up(KLEOS_AT_GEMM_MMA, t);
                             ok = false;
@@ -1318,6 +1351,8 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                         const uint32_t e_local = smem_u32(&ctl->empty[s]);
                         umma_commit_pair(map_to_cta(e_local, 0));
                         umma_commit_pair(map_to_cta(e_local, 1));
+                        par ^= 1u << s;
+                        s = s + 1 == NST ? 0 : s + 1;
                     }
                     if (!ok) break;
                     const uint32_t f_local = smem_u32(&ctl->acc_full[buf]);
@@ -1358,9 +1393,16 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 const long long t0 = clock64();
                 bool ok = true;
                 for (;;) {
-                    const bool up = kind ? ld_acquire_gpu(&ctr->pair_done[id]) >= need
-                                         : (uint32_t)(ld_acquire_sys(xflag + id) >> 32) == a.epoch;
-                    if (up) break;
+                    // relaxed polls; one acquiring load and one proxy fence (the operands are read
+                    // through the async proxy) once the flag is up
+                    const bool up = kind ? ld_relaxed_gpu(&ctr->pair_done[id]) >= need
+                                         : (uint32_t)(ld_relaxed_sys(xflag + id) >> 32) == a.epoch;
+                    if (up) {
+                        if (kind) (void)ld_acquire_gpu(&ctr->pair_done[id]);
+                        else (void)ld_acquire_sys(xflag + id);
+                        asm volatile("fence.proxy.async;" ::: "memory");
+                        break;
+                    }
                     __nanosleep(100);
                     if (*abort_flag || ld_relaxed_gpu(&ctr->abort_all)) {
                         *abort_flag = 1;
