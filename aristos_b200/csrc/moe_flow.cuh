@@ -1042,7 +1042,7 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     // accumulators), and every role copies its entry into registers before it does anything
     // else, so at most four entries are live at any time.
     auto claim = [&]() -> int {  // leader's producer thread only: next tile of the rank's queue, or -1
-        if (*abort_flag || ld_relaxed_gpu(&ctr->abort_all)) return -1;
+        if (*abort_flag) return -1;  // (the subscriber mirrors the rank's abort word into this flag)
         const unsigned c = atomicAdd(&ctr->tile_next, 1u);
         return c < (unsigned)total_tiles ? (int)c : -1;
     };

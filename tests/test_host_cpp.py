@@ -166,3 +166,25 @@ def test_id_rendezvous_between_two_ranks(tmp_path):
                                                  KLEOS_ID_FILE=str(tmp_path / "never")),
                             capture_output=True, text=True, timeout=120)
     assert lonely.returncode == 1 and "waited 3 s for the NCCL id" in lonely.stderr
+
+
+@pytest.mark.gpu
+def test_driver_two_ranks_through_the_cpp_mirror(tmp_path, gpu_count):
+    """Two kleos_driver processes started the way a launcher would (RANK / WORLD_SIZE in the
+    environment, the NCCL id through the rendezvous file): both must run the timed forward of
+    the reference's shipped layer shape and print the reference's line."""
+    if gpu_count < 2:
+        pytest.skip("needs 2 GPUs")
+    driver = kbuild.build_driver()
+    cfg = KleosConfig(sequence_len=2048, hidden_size=1024, intermediate_size=1024, num_experts=16)
+    cfg.to_json(os.path.join(tmp_path, "kleos_config.json"))
+    base = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "KLEOS_CONFIG")}
+    env = dict(base, WORLD_SIZE="2", KLEOS_ID_FILE=str(tmp_path / "id"), KLEOS_WAIT_MS="3000",
+               NCCL_NVLS_ENABLE="0")
+    procs = [subprocess.Popen([driver], cwd=tmp_path, env=dict(env, RANK=str(r)),
+                              stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True) for r in (0, 1)]
+    outs = [p.communicate(timeout=300) for p in procs]
+    for r, (p, (so, se)) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0, se[-2000:]
+        m = re.search(rf"epRank: {r} took ([0-9.]+)ms", so)
+        assert m and 0.0 < float(m.group(1)) < 50.0, so
