@@ -60,7 +60,7 @@ constexpr int kRing = 8;           // claimed-tile ring per block (see hand_out(
 constexpr int kMaxPanels = 384;    // 128-row panels one rank can plan
 constexpr int kMaxLocal = 128;     // local experts per rank
 constexpr int kMaxCells = 256;     // (source, local expert) cells = number of experts
-constexpr int kUnitRows = 8;       // rows of one cell a transport warp sends between two publications
+constexpr int kUnitRows = 8;       // most rows of one cell a transport warp sends between two publications (Args::unit_rows)
 constexpr int kCombineBlock = 8;   // tokens a warp classifies at a time (one per lane, first lanes)
 constexpr int kMaxPasses = 8;      // combine passes (tokens grouped by when their last row returns)
 constexpr int kRoleWarps = 10;     // producer, MMA, 4 read-back, 4 transport
@@ -160,6 +160,7 @@ struct Args {
     uint32_t epoch;
     int suppress;            // test hook: no return flags (the combine's bounded wait then runs out)
     int sub;                 // 64-wide K slices per pipeline stage: 1 or 2
+    int unit_rows;           // rows per dispatch unit, 1..kUnitRows: bounds the stores a warp has in flight
     // routing inside the kernel (fuse_route != 0): the kernel then WRITES probs, topk, slots, mcw,
     // cell_tokens and counts before it reads them
     int fuse_route;
@@ -921,7 +922,7 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         __syncthreads();
         if (warp == 0) {
             // dispatch units before every expert, in sending order
-            const int total = warp_prefix([&](int i) { return (ctl->own_s[i] + kUnitRows - 1) / kUnitRows; },
+            const int total = warp_prefix([&](int i) { return (ctl->own_s[i] + a.unit_rows - 1) / a.unit_rows; },
                                           ctl->prefix_s, a.E, lane);
             if (lane == 0) ctl->total_units = (unsigned)total;
         }
@@ -1599,8 +1600,8 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             const int le = lo / a.world, owner = (a.rank + 1 + lo % a.world) % a.world;
             const int e = owner * a.nLx + le;
             const int routed = ctl->own_s[lo];
-            const int slot0 = (int)(u - ctl->prefix_s[lo]) * kUnitRows;
-            const int nrows = min(kUnitRows, routed - slot0);
+            const int slot0 = (int)(u - ctl->prefix_s[lo]) * a.unit_rows;
+            const int nrows = min(a.unit_rows, routed - slot0);
             const int my_tok = lane < nrows ? __ldcg(a.cell_tokens + (size_t)e * a.pEC + slot0 + lane) : 0;
             char* cell = a.peers.arena[owner] + a.lay.xcell +
                          (((size_t)a.rank * a.nLx + le) * a.pEC + slot0) * a.H * sizeof(TE);
