@@ -71,6 +71,7 @@ struct State {
     long long* flow_stalls = nullptr;        // [flow_grid][kStallSlots] wait cycles of a timed forward
     int flow_debug = 0;                      // KLEOS_FLOW_DEBUG
     int flow_unit_rows = flow::kUnitRows;    // KLEOS_UNIT_ROWS
+    int flow_sub = 0;                        // KLEOS_FLOW_SUB: 1 or 2 forces the stage depth
     double clock_khz = 0;
     float flow_ms[flow::kStampSlots] = {};   // last kleos_forward_bench: milestones after kernel start
 
@@ -514,6 +515,7 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed, const S
             // deep stages when an expert sees enough rows for the tensor pipe, not the weight
             // stream from HBM, to be the limit (about 260 FLOP per weight byte on this part)
             fa.sub = (long long)g.world * c.EC >= 512 ? 2 : 1;
+            if (g.flow_sub) fa.sub = g.flow_sub;  // KLEOS_FLOW_SUB
             fa.unit_rows = g.flow_unit_rows;
             fa.fuse_route = routed_in_kernel ? 1 : 0;
             fa.Wg = s.Wg; fa.gate_bias = g.bias; fa.tile_hist = g.tile_hist; fa.tie_eps = 1e-4f;
@@ -901,6 +903,7 @@ static int initialize_impl(const char* config_json_path, int rank, int world, co
         if ((rc = dev_alloc(&g.flow_stamps, (size_t)g.flow_grid * flow::kStampSlots))) return rc;
         if ((rc = dev_alloc(&g.flow_stalls, (size_t)g.flow_grid * flow::kStallSlots))) return rc;
         if (const char* dbg = std::getenv("KLEOS_FLOW_DEBUG")) g.flow_debug = std::atoi(dbg);
+        if (const char* fs = std::getenv("KLEOS_FLOW_SUB")) g.flow_sub = std::atoi(fs) == 1 ? 1 : (std::atoi(fs) == 2 ? 2 : 0);
         if (const char* ur = std::getenv("KLEOS_UNIT_ROWS"))
             g.flow_unit_rows = std::min(flow::kUnitRows, std::max(1, std::atoi(ur)));
     }

@@ -154,7 +154,7 @@ struct Args {
     DeviceStatus* status;
     long long* stamps;       // optional [grid][kStampSlots] global-timer values, or null
     long long* stalls;       // optional [grid][kStallSlots] cycles the roles of the tile stream spent waiting, or null
-    int debug;               // tuning switches (KLEOS_FLOW_DEBUG): 1 = combine only after the last tile
+    int debug;               // tuning switches (KLEOS_FLOW_DEBUG): 1 = combine only after the last tile, 2 = static tile split
     long long wait_cycles;
     int S, H, I, E, K, PX, EC, pEC, nLx, rank, world;
     uint32_t epoch;
@@ -1042,8 +1042,14 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     // K slices of shared memory), the issuer at most two tiles ahead of the read-back warps (two
     // accumulators), and every role copies its entry into registers before it does anything
     // else, so at most four entries are live at any time.
+    unsigned static_claims = 0;
     auto claim = [&]() -> int {  // leader's producer thread only: next tile of the rank's queue, or -1
         if (*abort_flag) return -1;  // (the subscriber mirrors the rank's abort word into this flag)
+        if (a.debug & 2) {
+            // tuning switch: static split of the same tile order (pair c takes tiles c, c + pairs, ...)
+            const unsigned c = (blockIdx.x >> 1) + static_claims++ * (gridDim.x >> 1);
+            return c < (unsigned)total_tiles ? (int)c : -1;
+        }
         const unsigned c = atomicAdd(&ctr->tile_next, 1u);
         return c < (unsigned)total_tiles ? (int)c : -1;
     };
