@@ -60,9 +60,8 @@ struct State {
     // buffers carry no gate weight and no probabilities (moe/fffn.cuh:47-53)
     bool dense = false;
     bool suppress_return_flag = false;  // test hook: see kleos_debug_suppress_return_flag
-    // 16-bit routed layers: dispatch, plan, both expert GEMMs and the combine run as ONE persistent
-    // kernel (moe_flow.cuh).  KLEOS_PHASES=1, or a layer beyond the kernel's shared-memory tables,
-    // selects the same work as separate launches (dispatch, plan, GEMM1, GEMM2, combine).
+    // KLEOS_FLOW=1, 16-bit routed layers: router, dispatch, plan, both expert GEMMs and the combine run
+    // as ONE persistent kernel (moe_flow.cuh) instead of separate launches.
     bool use_flow = false;
     bool fuse_route = false;                 // ... and the router runs inside it too (KLEOS_FUSE_ROUTE=0: separate launches)
     int flow_grid = 0;                       // blocks of the persistent kernel (co-resident pairs x 2)
@@ -888,10 +887,14 @@ static int initialize_impl(const char* config_json_path, int rank, int world, co
         KLEOS_CUDA(cudaFuncSetAttribute(route_tc_kernel<tf32_t, 64>, dyn, route_tc::Shape<64>::SMEM_BYTES));
         KLEOS_CUDA(cudaFuncSetAttribute(route_tc_kernel<tf32_t, 128>, dyn, route_tc::Shape<128>::SMEM_BYTES));
     }
-    // the persistent kernel keeps its panel list and per-cell tables in shared memory; layers
-    // beyond those tables (and KLEOS_PHASES=1, for comparisons) run as separate launches
-    const char* phases = std::getenv("KLEOS_PHASES");
-    g.use_flow = g.use_tc && !dense && !(phases && phases[0] == '1') && g.flow_grid >= 2 &&
+    // KLEOS_FLOW=1 runs 16-bit routed layers as ONE persistent kernel (moe_flow.cuh).  It is the
+    // reference's arrangement and passes the same parity tests, but on this machine it has so far
+    // measured slower than the separate launches at every world size (its dispatch and combine
+    // traffic share the SMs' memory pipeline with the tile stream), so the separate launches stay
+    // the default.  The kernel keeps its panel list and per-cell tables in shared memory; layers
+    // beyond those tables always run as separate launches.
+    const char* flow_env = std::getenv("KLEOS_FLOW");
+    g.use_flow = g.use_tc && !dense && flow_env && flow_env[0] == '1' && g.flow_grid >= 2 &&
                  (size_t)cfg.E * cfg.pEC / kTileM <= (size_t)flow::kMaxPanels && cfg.E <= flow::kMaxCells &&
                  g.nLx <= flow::kMaxLocal;
     const char* fr = std::getenv("KLEOS_FUSE_ROUTE");

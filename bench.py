@@ -548,6 +548,55 @@ def run_cuda(args):
             kleos.finalize()
             raise SystemExit(3)
 
+    # ---------------------------------------------------------------- the persistent kernel, same run
+    # 16-bit routed layers can also run as ONE persistent kernel (KLEOS_FLOW=1, the reference's
+    # arrangement); it is measured here on the same buffers so that both arrangements appear in
+    # one record: device-timed steps, kernel timeline, and its own parity check.
+    persistent = None
+    if not cfg.dense and cfg.torch_dtype in (2, 3) and args.persistent and timeline is None:
+        kleos.finalize()
+        os.environ["KLEOS_FLOW"] = "1"
+        uid2 = None
+        if world > 1:
+            idt = torch.zeros(128, dtype=torch.uint8, device=device)
+            if rank == 0:
+                idt.copy_(torch.frombuffer(bytearray(kleos.get_unique_id()), dtype=torch.uint8))
+            dist.broadcast(idt, 0)
+            uid2 = bytes(idt.cpu().numpy().tobytes())
+        info = kleos.initialize(cfg, rank, world, uid2)
+        if gate_bias is not None:
+            kleos.set_gate_bias(gate_bias)
+        for _ in range(max(args.warmup, 32)):
+            kleos.forward_host(iP, oP, stream)
+        l0 = kleos.launch_count()
+        p_ms = timed_forwards(args.steps) / args.steps
+        p_launches = kleos.launch_count() - l0
+        st = kleos.last_status()
+        if st.code:
+            raise SystemExit(f"persistent kernel, device status: where={st.where} detail={st.detail}")
+        kleos.forward_host_bench(iP, oP, skip=2, trials=4)
+        try:
+            p_timeline, p_waits = kleos.flow_timeline(), kleos.flow_stalls()
+        except kleos.KleosError:
+            p_timeline, p_waits = None, None  # the layer is beyond the kernel's tables
+        p_parity = None
+        if args.parity and p_timeline is not None:
+            exact, err, nrows, tol = parity_check(cfg, info, kleos, iP, oP, rank, world, device, gate_bias)
+            p_parity = dict(routing_exact=min_over_ranks(1.0 if exact else 0.0) > 0.5,
+                            out_rel_err=max_over_ranks(err), tolerance=tol, rows_checked=nrows * world)
+            if min_over_ranks(1.0 if (exact and err <= tol) else 0.0) < 0.5:
+                if rank == 0:
+                    print(json.dumps(dict(error="parity check of the persistent kernel failed",
+                                          parity=p_parity)), flush=True)
+                kleos.finalize()
+                raise SystemExit(3)
+        if p_timeline is not None:
+            persistent = dict(ms_per_step=p_ms, tokens_per_s=cfg.S * world / (p_ms * 1e-3),
+                              gpu_launches=p_launches, layer_frac=t_roof_ms / p_ms,
+                              timeline_ms=p_timeline, role_waits_ms=p_waits, parity=p_parity,
+                              how="KLEOS_FLOW=1: router, dispatch, plan, GEMM1, GEMM2, combine in one launch")
+    roof["persistent_kernel"] = persistent
+
     if rank == 0:
         tokens = cfg.S * world
         line = dict(
@@ -613,6 +662,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
     ap.add_argument("--no-parity", dest="parity", action="store_false",
                     help="skip the comparison of this run's results with the CPU oracle")
+    ap.add_argument("--no-persistent", dest="persistent", action="store_false",
+                    help="skip the second pass that times the persistent kernel (KLEOS_FLOW=1)")
     ap.add_argument("--sustain-s", type=float, default=1.0,
                     help="length of the second, long timed region in seconds (0: none)")
     args = ap.parse_args()

@@ -137,8 +137,8 @@ int kleos_debug_routing(int32_t* topk, int32_t* slots, uint32_t* counts, float* 
  * [6] combine, [7] whole forward.  n = number of floats the caller provides (>= 8). */
 int kleos_phase_times(float* ms, int n);
 
-/* 16-bit routed layers run the router, dispatch, plan, both expert GEMMs and the combine as ONE
- * persistent kernel (the reference's arrangement, moe/moe.cuh:77-144), so the phases above are
+/* With KLEOS_FLOW=1 16-bit routed layers run the router, dispatch, plan, both expert GEMMs and the
+ * combine as ONE persistent kernel (the reference's arrangement, moe/moe.cuh:77-144); the phases above are
  * then read from the blocks' global-timer stamps: [0] gate GEMM + top-k up to the first grid
  * barrier, [1] slots up to the second; [2] last row dispatched and [3] tile plan known, both
  * counted from the second barrier; [4] span of the GEMM1 tiles; [5] from the last GEMM1 tile to
@@ -149,7 +149,7 @@ int kleos_phase_times(float* ms, int n);
  * [7] last block ends, [8] routing done (first grid barrier), [9] slots done (second),
  * [10] gate logits of the last token tile complete, [11] ... and turned into choices.  n >= 12.
  * KLEOS_E_STATE when the layer runs as separate launches (float and TF32 layers, the dense
- * layer, KLEOS_PHASES=1). */
+ * layer, and every layer unless KLEOS_FLOW=1 is set). */
 int kleos_flow_timeline(float* ms, int n);
 
 /* Wait times of the persistent kernel's tile-stream roles in the LAST timed forward of

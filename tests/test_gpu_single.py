@@ -10,6 +10,23 @@ from tests import moe_harness as hz
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(autouse=True, params=["launches", "persistent"])
+def arrangement(request, monkeypatch):
+    """Every case runs twice: as separate launches (the default) and with KLEOS_FLOW=1, where
+    16-bit routed layers run as ONE persistent kernel.  Cases whose element type never takes the
+    persistent kernel are not repeated."""
+    if request.param == "persistent":
+        args = getattr(getattr(request.node, "callspec", None), "params", {})
+        if args.get("dtype", 2) not in (2, 3) or "tf32" in request.node.name or "dense" in request.node.name \
+                or "single_expert" in request.node.name or args.get("name") in ("C2", "fp32_w1", "fp32_top1",
+                                                                                "tf32_gelu_biased"):
+            pytest.skip("this layer never runs the persistent kernel")
+        monkeypatch.setenv("KLEOS_FLOW", "1")
+    else:
+        monkeypatch.delenv("KLEOS_FLOW", raising=False)
+    return request.param
+
+
 def _small(dtype, **kw):
     base = dict(sequence_len=256, hidden_size=512, intermediate_size=1024, num_experts=8,
                 torch_dtype=dtype)
@@ -302,27 +319,31 @@ def test_large_baseline_layers_single_gpu_sampled(name):
          hidden_act=1),
     dict(num_experts=8, sequence_len=256, hidden_size=256, intermediate_size=512, expert_top_k=4),
 ], ids=["e16", "e128-gelu-tail", "top4"])
-def test_separate_launches_give_the_persistent_kernels_results(monkeypatch, kw):
-    """KLEOS_PHASES=1 runs dispatch, plan, GEMM1, GEMM2 and combine as separate launches (the path
-    that layers beyond the persistent kernel's tables take); both arrangements must match the
-    oracle, and each other bit for bit."""
+def test_separate_launches_give_the_persistent_kernels_results(monkeypatch, kw, arrangement):
+    """KLEOS_FLOW=1 runs router, dispatch, plan, GEMM1, GEMM2 and combine as one persistent kernel,
+    the default as separate launches; both arrangements must match the oracle, and each other
+    bit for bit."""
+    if arrangement == "persistent":
+        pytest.skip("compares both arrangements itself")
     cfg = _small(2, **kw)
     packed, views = hz.make_inputs(cfg, 1, bias_scale=0.5)
     ref = moe_oracle.moe_forward(cfg, 1, views)[0]
     outs = []
-    for phases in ("0", "1"):
-        monkeypatch.setenv("KLEOS_PHASES", phases)
+    for flow in ("0", "1"):
+        monkeypatch.setenv("KLEOS_FLOW", flow)
         probs, out, routing = hz.run_layer_single_gpu(cfg, packed[0], forwards=3)
         hz.check_against_oracle(cfg, ref, probs, out, routing)
         outs.append(out)
     assert np.array_equal(outs[0], outs[1])
 
 
-def test_persistent_kernel_reports_its_timeline():
+def test_persistent_kernel_reports_its_timeline(arrangement):
     """kleos_forward_bench on a 16-bit routed layer: the milestones of the one kernel are ordered
     (plan, first tile, last GEMM1 tile, last tile, end) and lie inside the forward's duration."""
     import torch
     from aristos_b200 import kleos
+    if arrangement != "persistent":
+        pytest.skip("separate launches have no kernel timeline")
     cfg = _small(2, sequence_len=1024, num_experts=16)
     raw = synth.encode(synth.packed_input(cfg, 0, 1), 2)
     info = kleos.initialize(cfg, 0, 1)
