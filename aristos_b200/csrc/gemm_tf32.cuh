@@ -1,7 +1,7 @@
 // Expert-FFN GEMM for TF32 layers (torch_dtype 1) on the 5th-generation tensor cores:
 // tcgen05.mma kind::tf32 over 4-byte operands staged by TMA (128-byte swizzle, 32 elements per
 // row), 128x256 fp32 accumulator in tensor memory, double-buffered, read back with tcgen05.ld.
-// Same block roles, tile order and bounded waits as gemm_tc.cuh; the differences are the
+// Same block roles and bounded waits as the 16-bit GEMM (gemm_tc2.cuh) without the pairing; the differences are the
 // operand width (K slices of 32 elements, 8 per instruction), the 4-byte epilogue (bias read as
 // fp32 words, results rounded to TF32, each lane storing whole 128-byte lines of its own row)
 // and the instruction descriptor.
