@@ -64,6 +64,7 @@ struct State {
     // as ONE persistent kernel (moe_flow.cuh) instead of separate launches.
     bool use_flow = false;
     bool fuse_route = false;                 // ... and the router runs inside it too (KLEOS_FUSE_ROUTE=0: separate launches)
+    bool route_by_flow = false;              // separate launches: the router is the persistent kernel's routing phase alone
     int flow_grid = 0;                       // blocks of the persistent kernel (co-resident pairs x 2)
     flow::Counters* flow_ctr = nullptr;      // [2] scheduler state, see moe_flow.cuh
     long long* flow_stamps = nullptr;        // [flow_grid][kStampSlots] timeline of a timed forward
@@ -451,10 +452,27 @@ int forward_typed(const void* iP, void* oP, cudaStream_t st, bool timed, const S
     auto mark = [&]() -> cudaError_t { return timed ? cudaEventRecord(g.ev[evi++], st) : cudaSuccess; };
     KLEOS_CUDA(mark());
 
-    const bool routed_in_kernel = g.use_flow && g.fuse_route;
+    bool routed_in_kernel = g.use_flow && g.fuse_route;
     if (routed_in_kernel) {
         KLEOS_CUDA(mark());
         KLEOS_CUDA(mark());
+    } else if (g.route_by_flow) {
+        if constexpr (sizeof(T) == 2) {
+            // router of the separate launches: the routing phase of moe_flow_kernel on its own (gate
+            // GEMM, top-k, in-place near-tie re-evaluation, grid barrier, slots, counts)
+            flow::Args fr{};
+            fr.tokens = s.A; fr.probs = s.probs; fr.topk = g.topk; fr.slots = g.slots; fr.mcw = g.mcw;
+            fr.cell_tokens = g.cell_tokens; fr.counts = g.counts; fr.peers = g.peers; fr.lay = g.lay;
+            fr.ctr = g.flow_ctr; fr.status = g.status; fr.wait_cycles = g.wait_cycles;
+            fr.S = c.S; fr.H = c.H; fr.I = c.I; fr.E = c.E; fr.K = c.K; fr.PX = c.PX; fr.EC = c.EC;
+            fr.pEC = c.pEC; fr.nLx = g.nLx; fr.rank = g.rank; fr.world = g.world; fr.epoch = g.epoch;
+            fr.sub = 1; fr.unit_rows = flow::kUnitRows; fr.fuse_route = 1; fr.route_only = 1;
+            fr.Wg = s.Wg; fr.gate_bias = g.bias; fr.tile_hist = g.tile_hist; fr.tie_eps = 1e-4f;
+            launch_flow<T>(c.hidden_act, c.K, st, fr, act_map);
+        }
+        KLEOS_CUDA(mark());
+        KLEOS_CUDA(mark());
+        routed_in_kernel = true;  // nothing left to launch for routing and slots
     }
     // 1. router
     if (!routed_in_kernel) KLEOS_CUDA(cudaMemsetAsync(g.refine_count, 0, sizeof(int), st));
@@ -899,7 +917,12 @@ static int initialize_impl(const char* config_json_path, int rank, int world, co
                  g.nLx <= flow::kMaxLocal;
     const char* fr = std::getenv("KLEOS_FUSE_ROUTE");
     g.fuse_route = g.use_flow && cfg.PX <= 128 && !cfg.is_training && !(fr && fr[0] == '0');
-    if (g.use_flow) {
+    // Separate launches of a 16-bit layer use the same kernel's routing phase as their router
+    // (KLEOS_ROUTE_KERNELS=1: the gate, near-tie, histogram and slot kernels instead)
+    const char* rk = std::getenv("KLEOS_ROUTE_KERNELS");
+    g.route_by_flow = g.use_tc && !dense && !g.use_flow && cfg.PX <= 128 && !cfg.is_training &&
+                      g.flow_grid >= 2 && cfg.E <= flow::kMaxCells && !(rk && rk[0] == '1');
+    if (g.use_flow || g.route_by_flow) {
         flow::Counters* ctr = nullptr;
         if ((rc = dev_alloc(&ctr, 2))) return rc;
         g.flow_ctr = ctr;

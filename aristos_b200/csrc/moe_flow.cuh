@@ -164,6 +164,7 @@ struct Args {
     // routing inside the kernel (fuse_route != 0): the kernel then WRITES probs, topk, slots, mcw,
     // cell_tokens and counts before it reads them
     int fuse_route;
+    int route_only;          // with fuse_route: leave after the routing phase (router of the separate launches)
     const void* Wg;          // [PX,H] gate weight, row e = expert e
     const float* gate_bias;  // [E]
     int* tile_hist;          // [S/128][E] per-tile histogram of the chosen experts
@@ -896,6 +897,21 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         }
         grid_barrier(1);
         if (stamp && tid == 0) stamp[kSlotted] = global_ns();
+    }
+    if (a.route_only) {
+        // The router alone (the separate-launch arrangement uses this kernel as its router: one
+        // launch instead of gate, near-tie, histogram and slot kernels).  Same teardown as below.
+        tc_fence_before();
+        __syncthreads();
+        cluster_sync_all();
+        if (warp == 2) {
+            tc_fence_after();
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(ctl->tmem_base),
+                         "r"(TMEM_COLS)
+                         : "memory");
+        }
+        if (stamp && tid == 0) stamp[kEnd] = global_ns();
+        return;
     }
 
     // ------------------------------------------------------------------ plan (every block, same result)
