@@ -115,8 +115,8 @@ def test_ranks_skewed_in_time_with_new_tokens_every_forward(tmp_path, gpu_count,
 
 BASELINE_CASES = [("C3", 2, "launches"), ("C3", 2, "persistent"), ("C5", 2, "persistent"),
                   ("C3", 4, "launches"), ("C3", 4, "persistent"), ("C5", 4, "persistent"),
-                  ("C3", 8, "launches"), ("C3", 8, "persistent"), ("C4", 8, "launches"),
-                  ("C4", 8, "persistent"), ("C5", 8, "persistent")]
+                  ("C3", 8, "launches"), ("C3", 8, "persistent"), ("C4", 8, "persistent"),
+                  ("C5", 8, "launches")]
 
 
 @pytest.mark.parametrize("name,world,arr", BASELINE_CASES, ids=[f"{n}-w{w}-{a}" for n, w, a in BASELINE_CASES])
