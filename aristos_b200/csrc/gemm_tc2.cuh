@@ -158,7 +158,6 @@ ffn_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
                 // the block without a panel of its own re-reads the first one and discards
                 const int my_panel = pt.panel0 + ((int)cta_rank < pt.n_panels_left ? (int)cta_rank : 0);
                 const PanelEntry p = panel_at(my_panel);
-                const int brow = pt.le * g.N + pt.nt * BN + (int)cta_rank * (BN / 2);
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const int s = it % NST;
                     const uint32_t ph = (it / NST) & 1;
@@ -175,14 +174,46 @@ ffn_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
                     for (int sub = 0; sub < nsub; ++sub) {
                         const int kx = (kb * SUB + sub) * BK;
                         tma_load_2d_pair(sa + sub * SLICE_BYTES, &map_a, kx, p.row_base, full_leader);
-                        tma_load_2d_pair(sa + sub * SLICE_BYTES + A_STAGE_BYTES, &map_b, kx, brow,
-                                         full_leader);
                     }
                 }
             }
             if (g.stats) {
                 g.stats[blockIdx.x * kStatSlots + 0] = w_empty;
                 g.stats[blockIdx.x * kStatSlots + 1] = clock64() - t_begin;
+            }
+        }
+        __syncwarp();
+    } else if (warp == 3) {
+        // ------------------------------------------------------------ second TMA producer (both blocks)
+        // The weight slices are issued by a thread of their own, next to the panel slices of
+        // warp 0 (measured: 1.6 % off the launch).  It waits for the same free-stage barrier and
+        // its bytes complete on the same full barrier; the byte count announced by warp 0 covers
+        // both, and a slice landing before that announcement only makes the barrier's byte
+        // count negative for a moment (the phase cannot complete before warp 0 has arrived).
+        if (lane == 0) {
+            asm volatile("fence.proxy.async;" ::: "memory");
+            uint32_t it = 0;
+            long long w_unused = 0;
+            for (int t = cluster_id; t < total && !*abort_flag; t += n_clusters) {
+                PairTile pt;
+                if (!decode_pair_tile(t, ctl->le_start, g.le_begin, g.le_end, NT, &pt)) break;
+                const int brow = pt.le * g.N + pt.nt * BN + (int)cta_rank * (BN / 2);
+                bool ok = true;
+                for (int kb = 0; kb < KB; ++kb, ++it) {
+                    const int s = it % NST;
+                    const uint32_t ph = (it / NST) & 1;
+                    if (!mbar_wait_timed(&ctl->empty[s], ph ^ 1, g.wait_cycles, abort_flag, &w_unused)) {
+                        ok = false;  // the first producer reports the failure
+                        break;
+                    }
+                    const int nsub = min(SUB, KS - kb * SUB);
+                    const uint32_t full_leader = map_to_cta(smem_u32(&ctl->full[s]), 0);
+                    uint8_t* sa = tiles + s * STAGE_BYTES;
+                    for (int sub = 0; sub < nsub; ++sub)
+                        tma_load_2d_pair(sa + sub * SLICE_BYTES + A_STAGE_BYTES, &map_b, (kb * SUB + sub) * BK, brow,
+                                         full_leader);
+                }
+                if (!ok) break;
             }
         }
         __syncwarp();

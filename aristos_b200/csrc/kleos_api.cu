@@ -74,6 +74,7 @@ struct State {
     int flow_sub = 0;                        // KLEOS_FLOW_SUB: 1 or 2 forces the stage depth
     double clock_khz = 0;
     float flow_ms[flow::kStampSlots] = {};   // last kleos_forward_bench: milestones after kernel start
+    std::vector<long long> flow_raw;         // ... and the blocks' own stamps of its last timed forward
 
     // symmetric arena
     ArenaLayout lay{};
@@ -1041,6 +1042,7 @@ int kleos_forward_bench(const void* iP, void* oP, int skip, int trials, float* m
                 for (int k = 0; k < flow::kStampSlots; ++k) hi[k] = std::max(hi[k], sb[k]);
             }
             hi[flow::kFirstTile] = first_tile;
+            g.flow_raw = stamps;
             for (int k = 0; k < flow::kStampSlots; ++k) macc[k] += hi[k] > t0 ? (double)(hi[k] - t0) * 1e-6 : 0.0;
         }
     }
@@ -1303,9 +1305,20 @@ int kleos_debug_flow_stalls(float* ms, int n) {
 }
 
 int kleos_flow_timeline(float* ms, int n) {
-    if (!ms || n < flow::kStampSlots) return fail(KLEOS_E_ARG, "need room for %d floats", flow::kStampSlots);
+    if (!ms || n < 12) return fail(KLEOS_E_ARG, "need room for at least 12 floats");
     if (!g.initialised || !g.use_flow) return fail(KLEOS_E_STATE, "this layer does not run the persistent kernel");
-    for (int k = 0; k < flow::kStampSlots; ++k) ms[k] = g.flow_ms[k];
+    for (int k = 0; k < n; ++k) ms[k] = k < flow::kStampSlots ? g.flow_ms[k] : 0.f;
+    return KLEOS_OK;
+}
+
+int kleos_debug_flow_stamps(long long* ns, int capacity, int* blocks, int* per_block) {
+    if (!blocks || !per_block) return fail(KLEOS_E_ARG, "null argument");
+    if (!g.initialised || !g.use_flow) return fail(KLEOS_E_STATE, "this layer does not run the persistent kernel");
+    *blocks = g.flow_grid;
+    *per_block = flow::kStampSlots;
+    if (!ns) return KLEOS_OK;  // sizes only
+    if ((size_t)capacity < g.flow_raw.size()) return fail(KLEOS_E_ARG, "need room for %zu values", g.flow_raw.size());
+    std::copy(g.flow_raw.begin(), g.flow_raw.end(), ns);
     return KLEOS_OK;
 }
 

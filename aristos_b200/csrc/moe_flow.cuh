@@ -66,7 +66,7 @@ constexpr int kMaxPasses = 8;      // combine passes (tokens grouped by when the
 constexpr int kRoleWarps = 10;     // producer, MMA, 4 read-back, 4 transport
 constexpr int kCtlBytes = 32768;
 constexpr int SMEM_BYTES = kSlices * SLICE_BYTES + 1024 + kCtlBytes;
-constexpr int kStampSlots = 12;    // per block: see Stamp
+constexpr int kStampSlots = 20;    // per block: see Stamp
 constexpr int kStallSlots = 12;    // per block: see Stall
 
 // Per-rank scheduler state in global memory.  Two copies: the forward of epoch n works on copy
@@ -88,7 +88,14 @@ enum Stamp {
     kStart = 0, kPlanned, kFirstTile, kLastGemm1, kLastTile, kDispatched, kCombined, kEnd,
     kRouted, kSlotted,  // the two grid barriers of the routing phase passed
     kGateAcc,           // gate logits of the block's last token tile complete in tensor memory
-    kGateDone           // ... and turned into probabilities, choices and the tile histogram
+    kGateDone,          // ... and turned into probabilities, choices and the tile histogram
+    kTopkDone,          // between the two: top-k and softmax sum of the tile known (before near-ties)
+    kProbsDone,         // ... near-ties re-evaluated and probabilities stored
+    kSlotBase,          // slot stage: base slot of every expert for the block's last tile known
+    kSlotsDone,         // ... and the block's slots written (before the second grid barrier)
+    kRouteBegin,        // set-up over (barriers, tensor memory, cluster barrier): the gate GEMM starts
+    kFirstOperands,     // first K slice of the gate GEMM has landed in shared memory (leader block)
+    kTopkPass1          // first pass over the logits (the K + 1 largest) done
 };
 
 // Cycles per block, tile stream only (a tuning aid, filled when Args::stalls is set).
@@ -513,6 +520,7 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         __syncthreads();
         cluster_sync_all();  // both blocks' barriers exist before anything remote touches them
         tc_fence_after();
+        if (stamp && tid == 0) stamp[kRouteBegin] = global_ns();
         const uint32_t tmem_r = ctl->tmem_base;
         const int n_clusters = (int)gridDim.x >> 1, cluster_id = (int)blockIdx.x >> 1;
         const int n_rt = (a.S + 2 * BM - 1) / (2 * BM);  // gate tiles of 256 tokens (128 per block)
@@ -570,6 +578,7 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                             break;
                         }
                         tc_fence_after();
+                        if (stamp && it == 0) stamp[kFirstOperands] = global_ns();
                         const uint32_t sa = smem_u32(tiles + s * SLICE_BYTES);
                         const uint64_t da = make_smem_desc(sa);
                         const uint64_t db = make_smem_desc(sa + A_STAGE_BYTES);
@@ -653,6 +662,7 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                         }
                     }
                 }
+                if (stamp && q == 0 && lane == 0) stamp[kTopkPass1] = global_ns();
                 const float m = val[0];
                 float d = 0.f;
 #pragma unroll 1
@@ -667,6 +677,7 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                     }
                 }
                 const float inv = 1.f / d;
+                if (stamp && q == 0 && lane == 0) stamp[kTopkDone] = global_ns();
                 float kth = 0.f, next = -INFINITY;
 #pragma unroll
                 for (int j = 0; j <= KC; ++j) {
@@ -774,6 +785,7 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                         }
                     }
                 }
+                if (stamp && q == 0 && lane == 0) stamp[kProbsDone] = global_ns();
                 if (valid) {
 #pragma unroll
                     for (int j = 0; j < KC; ++j)
@@ -824,44 +836,70 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         if (!*abort_flag) {
             // Slots in ascending token order (the reference hands them out in atomicAdd arrival
             // order, moe/gate.cuh:689-718): base slot of every expert for a tile of 128 tokens = sum of
-            // the earlier tiles' histograms, then each token's rank inside the tile; the last tile
-            // also has the totals and publishes them, one count flag per expert to its owner rank.
+            // the earlier tiles' histograms, then each token's rank inside the tile; the sum over all
+            // tiles is the expert's count, published with one count flag per expert to its owner rank.
             int* base = ctl->poff_s;                                // [E]
             int* part = ctl->own_s;                                 // [256]
             int (*wcount)[256] = reinterpret_cast<int (*)[256]>(ctl->stage_s);  // [8][256]
             const int n_tiles = a.S / BM;
+            int ep = 1;
+            while (ep < a.E) ep <<= 1;
+            // base[e] = tokens the tiles before `upto` sent to expert e: 256 / ep threads per expert
+            // share the tiles, each with sixteen loads in flight at a time (the histograms sit in
+            // L2, and one load after the other would cost a round trip per tile)
+            auto sum_tiles_before = [&](int upto) {
+                const int groups = 256 / ep;
+                const int e = tid % ep, grp = tid / ep;
+                int run = 0;
+                if (tid < 256 && e < a.E) {
+                    for (int t0 = grp; t0 < upto; t0 += 16 * groups) {
+                        int v[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int t = t0 + j * groups;
+                            v[j] = t < upto ? __ldcg(a.tile_hist + (size_t)t * a.E + e) : 0;
+                        }
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) run += v[j];
+                    }
+                }
+                if (tid < 256) part[tid] = run;
+                __syncthreads();
+                if (tid < a.E) {
+                    int sum = 0;
+                    for (int gi = 0; gi < groups; ++gi) sum += part[gi * ep + tid];
+                    base[tid] = sum;
+                }
+                __syncthreads();
+            };
+            // totals of every expert: unclamped count for this rank, clamped count to the owner
+            auto publish_counts = [&](int last_tile_too) {
+                for (int e = tid; e < a.E; e += kThreads) {
+                    int total = base[e];
+                    if (last_tile_too) total += __ldcg(a.tile_hist + (size_t)(n_tiles - 1) * a.E + e);
+                    a.counts[e] = (unsigned)total;
+                    const int owner = e / a.nLx, le = e - owner * a.nLx;
+                    st_release_sys(reinterpret_cast<unsigned long long*>(a.peers.arena[owner] + a.lay.cflag) +
+                                       ((size_t)a.rank * a.nLx + le),
+                                   make_flag(a.epoch, (unsigned)min(total, a.EC)));
+                }
+            };
+            // When the last block pair routed no tile it has nothing to do here: its second block
+            // adds up ALL tiles and publishes the counts, off the path of the blocks that write
+            // slots.  Otherwise the block of the last tile does it on top of its own work.
+            const bool spare = n_rt < n_clusters;
+            if (spare && blockIdx.x == gridDim.x - 1) {
+                sum_tiles_before(n_tiles);
+                publish_counts(0);
+            }
             for (int rt = cluster_id; rt < n_rt; rt += n_clusters) {
                 const int tile = rt * 2 + (int)cta_rank;
                 if (tile >= n_tiles) break;  // block-uniform
                 const int tok0 = tile * BM;
-                {
-                    int ep = 1;
-                    while (ep < a.E) ep <<= 1;
-                    const int groups = 256 / ep;
-                    const int e = tid % ep, grp = tid / ep;
-                    int run = 0;
-                    if (tid < 256 && e < a.E && grp < groups)
-                        for (int t = grp; t < tile; t += groups) run += __ldcg(a.tile_hist + (size_t)t * a.E + e);
-                    if (tid < 256) part[tid] = run;
-                    for (int i = tid; i < 8 * 256; i += kThreads) (&wcount[0][0])[i] = 0;
-                    __syncthreads();
-                    if (tid < a.E) {
-                        int sum = 0;
-                        for (int gi = 0; gi < groups; ++gi) sum += part[gi * ep + tid];
-                        base[tid] = sum;
-                    }
-                    __syncthreads();
-                }
-                if (tile == n_tiles - 1) {
-                    for (int e = tid; e < a.E; e += kThreads) {
-                        const int total = base[e] + __ldcg(a.tile_hist + (size_t)tile * a.E + e);
-                        a.counts[e] = (unsigned)total;
-                        const int owner = e / a.nLx, le = e - owner * a.nLx;
-                        st_release_sys(reinterpret_cast<unsigned long long*>(a.peers.arena[owner] + a.lay.cflag) +
-                                           ((size_t)a.rank * a.nLx + le),
-                                       make_flag(a.epoch, (unsigned)min(total, a.EC)));
-                    }
-                }
+                for (int i = tid; i < 8 * 256; i += kThreads) (&wcount[0][0])[i] = 0;
+                sum_tiles_before(tile);
+                if (stamp && tid == 0) stamp[kSlotBase] = global_ns();
+                if (!spare && tile == n_tiles - 1) publish_counts(1);
                 const int n_own = min(BM, a.S - tok0) * a.K;
                 for (int i0 = 0; i0 < n_own; i0 += 256) {
                     const int i = i0 + tid;
@@ -895,6 +933,7 @@ moe_flow_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 }
             }
         }
+        if (stamp && tid == 0) stamp[kSlotsDone] = global_ns();
         grid_barrier(1);
         if (stamp && tid == 0) stamp[kSlotted] = global_ns();
     }

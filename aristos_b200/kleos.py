@@ -27,7 +27,7 @@ EXPORTS = (
     "kleos_forward", "kleos_forward_bench", "kleos_forward_host", "kleos_forward_host_async",
     "kleos_host_sync", "kleos_get_rank",
     "kleos_local_experts", "kleos_get_info", "kleos_last_status", "kleos_clear_status", "kleos_debug_routing",
-    "kleos_phase_times", "kleos_flow_timeline", "kleos_debug_flow_stalls", "kleos_debug_tile_order", "kleos_launch_count", "kleos_debug_gemm_stats", "kleos_debug_suppress_return_flag", "kleos_gate_stats", "kleos_plan_placement", "kleos_placement_model", "kleos_route_static", "kleos_finalize", "kleos_error_string",
+    "kleos_phase_times", "kleos_flow_timeline", "kleos_debug_flow_stamps", "kleos_debug_flow_stalls", "kleos_debug_tile_order", "kleos_launch_count", "kleos_debug_gemm_stats", "kleos_debug_suppress_return_flag", "kleos_gate_stats", "kleos_plan_placement", "kleos_placement_model", "kleos_route_static", "kleos_finalize", "kleos_error_string",
 )
 
 PHASE_NAMES = ("route", "slots", "dispatch", "plan", "gemm1", "gemm2", "combine", "total")
@@ -207,7 +207,8 @@ def route_static(A, Wg, gate_bias, S, H, E, K, torch_dtype, probs, topk, mcw, st
 
 
 FLOW_MILESTONES = ("start", "planned", "first_tile", "last_gemm1_tile", "last_tile", "dispatched",
-                   "combined", "end", "routed", "slotted", "gate_logits", "gate_done")
+                   "combined", "end", "routed", "slotted", "gate_logits", "gate_done", "topk_done",
+                   "probs_done", "slot_base", "slots_done", "route_begin", "first_operands", "topk_pass1")
 
 
 def flow_timeline() -> dict:
@@ -218,6 +219,22 @@ def flow_timeline() -> dict:
     lib.kleos_flow_timeline.argtypes = [ctypes.POINTER(ctypes.c_float), ctypes.c_int]
     _check(lib.kleos_flow_timeline(buf, len(FLOW_MILESTONES)), "kleos_flow_timeline")
     return {n: float(buf[i]) for i, n in enumerate(FLOW_MILESTONES)}
+
+
+def flow_stamps():
+    """Milestones of every block of the persistent kernel in the last timed forward of
+    forward_host_bench: int64 array [blocks, milestones] of global-timer nanoseconds, 0 where a
+    block never passed the milestone (kleos_debug_flow_stamps)."""
+    import numpy as np
+    lib = load_library()
+    lib.kleos_debug_flow_stamps.argtypes = [ctypes.POINTER(ctypes.c_longlong), ctypes.c_int,
+                                            ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]
+    nb, per = ctypes.c_int(0), ctypes.c_int(0)
+    _check(lib.kleos_debug_flow_stamps(None, 0, ctypes.byref(nb), ctypes.byref(per)), "kleos_debug_flow_stamps")
+    out = np.zeros((nb.value, per.value), dtype=np.int64)
+    _check(lib.kleos_debug_flow_stamps(out.ctypes.data_as(ctypes.POINTER(ctypes.c_longlong)), out.size,
+                                       ctypes.byref(nb), ctypes.byref(per)), "kleos_debug_flow_stamps")
+    return out
 
 
 FLOW_STALLS = ("producer_wait_stage", "producer_wait_data", "producer_total", "mma_wait_accumulator",

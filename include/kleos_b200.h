@@ -147,10 +147,20 @@ int kleos_phase_times(float* ms, int n);
  * start, latest block each: [0] 0, [1] plan known, [2] first tile begins (earliest block),
  * [3] last GEMM1 tile done, [4] last tile done, [5] last row dispatched, [6] last token combined,
  * [7] last block ends, [8] routing done (first grid barrier), [9] slots done (second),
- * [10] gate logits of the last token tile complete, [11] ... and turned into choices.  n >= 12.
+ * [10] gate logits of the last token tile complete, [11] ... and turned into choices; with
+ * n >= 19 also the router's inner steps: [12] top-k and softmax sum known, [13] near-ties
+ * re-evaluated and probabilities stored, [14] base slots of the block's tile known, [15] slots
+ * written, [16] set-up over and gate GEMM begins, [17] first K slice of the gate GEMM in shared
+ * memory, [18] first pass over the logits done.  n >= 12.
  * KLEOS_E_STATE when the layer runs as separate launches (float and TF32 layers, the dense
  * layer, and every layer unless KLEOS_FLOW=1 is set). */
 int kleos_flow_timeline(float* ms, int n);
+
+/* The same stamps block by block, as written by the last timed forward of kleos_forward_bench:
+ * ns[b * per_block + k] = global-timer nanoseconds of milestone k in block b (0: that block never
+ * passed it).  *blocks and *per_block are always set; ns may be null to ask for the sizes only,
+ * otherwise capacity >= *blocks * *per_block.  A tuning aid with no counterpart in the reference. */
+int kleos_debug_flow_stamps(long long* ns, int capacity, int* blocks, int* per_block);
 
 /* Wait times of the persistent kernel's tile-stream roles in the LAST timed forward of
  * kleos_forward_bench, milliseconds averaged over the blocks that recorded a value:
