@@ -353,8 +353,13 @@ def test_persistent_kernel_reports_its_timeline(arrangement):
         kleos.forward_host_bench(iP, oP, skip=2, trials=4)
         tl = kleos.flow_timeline()
         ph = kleos.phase_times()
+        st = kleos.flow_stamps()
     finally:
         kleos.finalize()
+    # the same milestones block by block: every block starts and ends, in that order
+    assert st.ndim == 2 and st.shape[0] >= 2 and st.shape[1] >= len(kleos.FLOW_MILESTONES)
+    i0, i1 = kleos.FLOW_MILESTONES.index("start"), kleos.FLOW_MILESTONES.index("end")
+    assert (st[:, i0] > 0).all() and (st[:, i1] >= st[:, i0]).all()
     assert 0 < tl["planned"] <= tl["last_gemm1_tile"] <= tl["last_tile"] <= tl["end"]
     assert tl["first_tile"] <= tl["last_tile"] and tl["dispatched"] <= tl["end"] and tl["combined"] <= tl["end"]
     assert tl["end"] <= ph["total"] * 1.05 + 0.01
