@@ -112,6 +112,16 @@ def test_call_order_errors_without_initialise():
     assert lib.kleos_forward(None, None, None) == -2
     with pytest.raises(kleos.KleosError):
         kleos.finalize()
+    # the tuning accessors of the persistent kernel: argument errors first, then the call order
+    nb, per = ctypes.c_int(-1), ctypes.c_int(-1)
+    lib.kleos_debug_flow_stamps.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_int),
+                                            ctypes.POINTER(ctypes.c_int)]
+    assert lib.kleos_debug_flow_stamps(None, 0, None, None) == -8
+    assert lib.kleos_debug_flow_stamps(None, 0, ctypes.byref(nb), ctypes.byref(per)) == -2
+    buf = (ctypes.c_float * 32)()
+    lib.kleos_flow_timeline.argtypes = [ctypes.POINTER(ctypes.c_float), ctypes.c_int]
+    assert lib.kleos_flow_timeline(buf, 11) == -8  # fewer than twelve floats
+    assert lib.kleos_flow_timeline(buf, 32) == -2
 
 
 def test_no_gpu_means_loud_failure():
